@@ -1,0 +1,402 @@
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload at every N: the W4A16 decode GEMV sweep (uint4 weights, group 128, bf16 scales and zero
+points, W ~ N(0, 0.02), x ~ N(0, 1) bf16) over the Llama-8B-like shapes
+(K,N) in {(4096,4096), (4096,14336), (14336,4096), (4096,1024)} x M in {1,4,8,16}.  One step is one
+pass over those 16 problems.  The metric is weight GB/s: packed weight + scale + zero-point bytes
+of the 16 problems divided by the step time (the reference's "weights + aux" convention).  The
+weights are rotated through a pool larger than L2 so every launch streams from HBM.
+
+At N > 1 every layer is column-partitioned over N (rank r owns rows [r N/g, (r+1) N/g)), x is
+replicated, and the output slices are concatenated by an NCCL all-gather: strong scaling.
+
+`--impl reference` times the CPU restatement of the reference's own path for the same sweep on
+the host cores (rank 0 only).  It is the only mode that executes anything under oracle/, besides
+the cpu_baseline leg of the default mode.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096), (4096, 1024)]  # (K, N)
+MS = [1, 4, 8, 16]
+GROUP = 128
+METRIC = "w4a16_decode_gemv_weight_bandwidth"
+UNIT = "GB/s"
+L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_gemv_kernel launch from the committed
+# ncu capture (profiles/), or None while no capture backs it
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def weight_aux_bytes(k: int, n: int) -> int:
+    return n * k // 2 + 2 * (n * (k // GROUP)) * 2
+
+
+def algorithmic_bytes(k: int, n: int, m: int) -> int:
+    return weight_aux_bytes(k, n) + 2 * m * (k + n)
+
+
+def sweep_weight_bytes() -> int:
+    return sum(weight_aux_bytes(k, n) for k, n in SHAPES) * len(MS)
+
+
+def measured_peak() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return 6650.0, "fallback"
+
+
+def make_layer(k: int, n: int, seed: int):
+    """One synthetic layer on the CPU: canonical PackedWeight."""
+
+    from xqt_b200 import quantize
+
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    w = torch.randn((n, k), generator=gen) * 0.02
+    return quantize.quantize_w4_asymmetric(w, group_size=GROUP)
+
+
+def make_inputs(seed: int = 10):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    return {(k, m): torch.randn((m, k), generator=gen).to(torch.bfloat16) for k in {s[0] for s in SHAPES} for m in MS}
+
+
+# ------------------------------------------------------------------------------------ clocks
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost",
+    }
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001
+            self._nvml = None
+
+    def _loop(self) -> None:
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        return {
+            "sm_mhz": int(statistics.median(self.samples)) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ------------------------------------------------------------------------------------ CPU arm
+
+
+def cpu_sweep(layers, inputs, shapes, ms) -> float:
+    """One pass of the oracle over the given problems; returns seconds."""
+
+    from oracle import w4a16 as oracle  # the timed CPU baseline
+
+    start = time.perf_counter()
+    for (k, n) in shapes:
+        pw = layers[(k, n)]
+        for m in ms:
+            oracle.gemm(inputs[(k, m)], pw.qweight, pw.scales, pw.zero_points, group_size=GROUP, signed=False)
+    return time.perf_counter() - start
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    layers = {(k, n): make_layer(k, n, 10 + i) for i, (k, n) in enumerate(SHAPES)}
+    inputs = make_inputs()
+    shapes, ms, sample = SHAPES, MS, "full sweep: 4 shapes x M in {1,4,8,16}"
+    probe = cpu_sweep(layers, inputs, shapes, ms)
+    if probe * (args.steps + args.warmup) > 150.0:
+        shapes, sample = [(4096, 1024)], "bounded: shape (K,N)=(4096,1024) x M in {1,4,8,16} (full sweep would exceed the time budget)"
+    for _ in range(args.warmup):
+        cpu_sweep(layers, inputs, shapes, ms)
+    times = [cpu_sweep(layers, inputs, shapes, ms) for _ in range(args.steps)]
+    seconds = sum(times)
+    nbytes = sum(weight_aux_bytes(k, n) for k, n in shapes) * len(ms)
+    value = nbytes * args.steps / seconds / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * seconds / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "w4a16_decode_gemv_sweep", "shapes_kn": shapes, "m": ms, "group_size": GROUP},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+
+
+def run_gpu_arm(args) -> None:
+    import torch.distributed as dist
+
+    from xqt_b200.contracts import EpilogueSpec, GemmProblem, GemmSpec, PackedWeight
+    from xqt_b200.dispatch import dispatch_gemm
+    from xqt_b200.executors import install_b200_executors
+    from xqt_b200 import quantize
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    install_b200_executors()
+
+    # --- synthetic layers: POOL device copies of every (sharded) layer, rotated to defeat L2
+    cpu_layers = {(k, n): make_layer(k, n, 10 + i) for i, (k, n) in enumerate(SHAPES)}
+    inputs = make_inputs()
+
+    def shard(pw, n):
+        rows = n // world
+        sl = slice(rank * rows, (rank + 1) * rows)
+        meta = type(pw.metadata)(**{**{f: getattr(pw.metadata, f) for f in pw.metadata.__dataclass_fields__},
+                                     "logical_shape": (rows, pw.metadata.logical_shape[1]),
+                                     "local_shape": (rows, pw.metadata.logical_shape[1]), "shard_axis": 0})
+        return PackedWeight(qweight=pw.qweight[sl].contiguous(), scales=pw.scales[sl].contiguous(),
+                            zero_points=pw.zero_points[sl].contiguous(), metadata=meta)
+
+    local_layers = {key: (shard(pw, key[1]) if world > 1 else pw) for key, pw in cpu_layers.items()}
+    bytes_per_copy = sum(pw.qweight.numel() + 4 * pw.scales.numel() for pw in local_layers.values())
+    pool = max(2, -(-2 * L2_BYTES // bytes_per_copy))
+    dev_layers = []
+    for _ in range(pool):
+        dev_layers.append({
+            key: PackedWeight(qweight=pw.qweight.to(device).clone(), scales=pw.scales.to(device).clone(),
+                              zero_points=pw.zero_points.to(device).clone(), metadata=pw.metadata)
+            for key, pw in local_layers.items()})
+    dev_inputs = {key: x.to(device) for key, x in inputs.items()}
+    host_inputs = {key: x.pin_memory() for key, x in inputs.items()}
+    specs = {}
+    for (k, n) in SHAPES:
+        for m in MS:
+            specs[(k, n, m)] = GemmSpec(
+                problem=GemmProblem(m=m, n=n // world, k=k, phase="decode", device=str(device), sm=100),
+                quant=quantize.w4_spec(group_size=GROUP, symmetric=False), epilogue=EpilogueSpec(output_dtype="bf16"))
+    gathered = {(n, m): torch.empty((world, m, n // world), device=device, dtype=torch.bfloat16)
+                for _, n in SHAPES for m in MS} if world > 1 else {}
+    launches = 0
+
+    def one_problem(copy, k, n, m, x):
+        nonlocal launches
+        res = dispatch_gemm(x, dev_layers[copy][(k, n)], spec=specs[(k, n, m)])
+        launches += 1
+        if world > 1:
+            buf = gathered[(n, m)]
+            dist.all_gather_into_tensor(buf, res.output)
+            return buf.permute(1, 0, 2).reshape(m, n)
+        return res.output
+
+    def step(i):
+        copy = i % pool
+        out = None
+        for (k, n) in SHAPES:
+            for m in MS:
+                out = one_problem(copy, k, n, m, dev_inputs[(k, m)])
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    launches = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    with sampler:
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+        e1.record()
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+        timed_launches = launches
+        # keep the same load running until the clock sampler has seen at least ~0.5 s of it
+        t_end = time.perf_counter() + max(0.0, 0.5 - ms_total / 1e3)
+        i = 0
+        while time.perf_counter() < t_end:
+            step(i)
+            i += 1
+            torch.cuda.synchronize()
+    if world > 1:
+        t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    value = sweep_weight_bytes() / (ms_per_step * 1e-3) / 1e9
+
+    # --- end to end through the public API with host buffers
+    host_out = {(n, m): torch.empty((m, n), dtype=torch.bfloat16).pin_memory() for _, n in SHAPES for m in MS}
+    h2d = sum(inputs[(k, m)].numel() * 2 for k, _ in SHAPES for m in MS)
+    d2h = sum(m * n * 2 for _, n in SHAPES for m in MS)
+
+    def e2e_step(i):
+        copy = i % pool
+        for (k, n) in SHAPES:
+            for m in MS:
+                x = host_inputs[(k, m)].to(device, non_blocking=True)
+                y = one_problem(copy, k, n, m, x)
+                host_out[(n, m)].copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = sweep_weight_bytes() / (e2e_ms / args.steps * 1e-3) / 1e9
+
+    # --- per-problem detail: each kernel timed alone, weights rotated through the pool
+    peak, peak_kind = measured_peak()
+    detail = []
+    if rank == 0 or world > 1:
+        reps = 40
+        for (k, n) in SHAPES:
+            for m in MS:
+                for i in range(5):
+                    one_problem(i % pool, k, n, m, dev_inputs[(k, m)])
+                barrier()
+                e0.record()
+                for i in range(reps):
+                    one_problem(i % pool, k, n, m, dev_inputs[(k, m)])
+                e1.record()
+                barrier()
+                us = e0.elapsed_time(e1) * 1e3 / reps
+                nb = algorithmic_bytes(k, n // world, m) if world > 1 else algorithmic_bytes(k, n, m)
+                detail.append({"k": k, "n": n, "m": m, "us": round(us, 3), "gbs": round(nb / us / 1e3, 1),
+                               "frac": round(nb / us / 1e3 / peak, 4)})
+    alg_bytes_step = sum(algorithmic_bytes(k, n // world, m) for k, n in SHAPES for m in MS)
+    achieved = alg_bytes_step / (ms_per_step * 1e-3) / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": "w4a16_decode_gemv_sweep", "shapes_kn": SHAPES, "m": MS, "group_size": GROUP,
+            "weight_scheme": "uint4 RTN, bf16 scale+zero", "parallelism": "single" if world == 1 else f"column-parallel x{world} + all-gather",
+            "l2": f"weights rotated through a pool of {pool} copies ({pool * bytes_per_copy / 1e6:.0f} MB > 126 MB L2)",
+        },
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peak_kind}",
+            "kernel": "w4a16_gemv_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank)",
+        },
+        "clocks": sampler.summary(),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": timed_launches,
+        "detail": detail,
+    }
+    if world == 1:
+        torch.set_num_threads(os.cpu_count() or 1)
+        inputs_cpu = inputs
+        cpu_sweep(cpu_layers, inputs_cpu, SHAPES, MS)
+        times = [cpu_sweep(cpu_layers, inputs_cpu, SHAPES, MS) for _ in range(3)]
+        line["cpu_baseline"] = {
+            "value": sweep_weight_bytes() * len(times) / sum(times) / 1e9, "unit": UNIT,
+            "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "3 passes of the full sweep (16 problems) after 1 warm-up pass",
+        }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

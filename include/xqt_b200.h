@@ -1,0 +1,95 @@
+/*
+ * C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * Conventions (the same ones xqt's own native artifacts follow,
+ * xqt/kernels/jit/csrc/gemm/w4a16_sm89.cu:435-521 and
+ * xqt/kernels/jit/csrc/quantization/awq_w4a16_sm89_kernel.cu:728-911):
+ *   - plain pointers and sizes, no framework types;
+ *   - every function returns a cudaError_t as int: 0 on success,
+ *     cudaErrorInvalidValue (1) for a request outside the supported envelope,
+ *     otherwise the CUDA error of the launch (cudaGetLastError());
+ *   - all pointers are device pointers on the current device unless stated;
+ *   - work is enqueued on `stream`; no entry point synchronises the host;
+ *   - inputs are borrowed and never written; outputs are caller-allocated.
+ * Logical convention everywhere: Y[M,N] = A[M,K] * W[N,K]^T.
+ */
+#ifndef XQT_B200_H_
+#define XQT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* xqt_b200_stream_t; /* == cudaStream_t */
+
+/* element types of activations, outputs, scales and zero points */
+#define XQT_B200_FP16 0
+#define XQT_B200_BF16 1
+#define XQT_B200_FP32 2
+
+/* epilogue activation, xqt EpilogueSpec.activation (ops/gemm/contracts.py:308-326) */
+#define XQT_B200_ACT_NONE 0
+#define XQT_B200_ACT_RELU 1
+#define XQT_B200_ACT_GELU 2
+#define XQT_B200_ACT_SILU 3
+
+/* kernel choice for the *_run entry points */
+#define XQT_B200_VARIANT_AUTO 0
+#define XQT_B200_VARIANT_SIMT 1     /* generic CUDA-core kernel: any shape, any group size        */
+#define XQT_B200_VARIANT_GEMV 2     /* M <= 16: split-K tensor-core GEMV, HBM-bound                */
+#define XQT_B200_VARIANT_TCGEN05 3  /* M > 16: TMA + tcgen05.mma with TMEM accumulators            */
+
+/* Replaces xqt_w4a16_sm89_version / xqt_awq_w4a16_sm89_version
+ * (w4a16_sm89.cu:519-521, awq_w4a16_sm89_kernel.cu:909-911). */
+const char* xqt_b200_version(void);
+
+/* cudaGetErrorString for the codes returned below. */
+const char* xqt_b200_error_string(int code);
+
+/* 1 when `device` has compute capability 10.0, else 0 (the sm_89 bindings gate the same
+ * way on (8,9): _impl/gemm_backends/sm89/w4a16_sm89.py:265-267). */
+int xqt_b200_device_supported(int device);
+
+/* ------------------------------------------------------------------------------------------
+ * W4A16: group-wise int4 weights, fp16/bf16 activations.
+ *
+ * Replaces xqt_w4a16_sm89_{fp16,bf16}_run[_persistent] (w4a16_sm89.cu:435-517, bound by
+ * _impl/gemm_backends/sm89/w4a16_sm89.py:278-299), the fused variant
+ * (w4a16_cutlass_fused_sm89.cu:433-553) and the decode GEMV xqt_awq_w4a16_sm89_decode
+ * (awq_w4a16_sm89_kernel.cu:746-784).  Same argument meaning; the additions are the element
+ * type of scales/zero points (the sm_89 kernels take fp32 only), residual/activation, the
+ * caller-owned scratch buffer and the kernel choice.
+ *
+ *   activation  [M, K] act_dtype, row stride K
+ *   qweight     [N, ceil(padded_k/2)] uint8, canonical xqt_int4_nk_v1: low nibble = even k;
+ *               two's-complement nibbles when nibble_signed, codes 0..15 otherwise
+ *   scales      [N, padded_k/group_size] param_dtype;  zero_points same shape or NULL
+ *   bias        [N] fp32 or NULL;  residual [M, N] act_dtype or NULL
+ *   output      [M, N] act_dtype
+ *   W = (code - zero_point) * scale, fp32 accumulate, bias -> residual -> activation -> one cast
+ *   (xqt/kernels/ops/gemm/reference.py:263-271,362-390,527).
+ *   workspace   scratch of at least xqt_b200_w4a16_workspace_bytes(m, n, k) bytes; must be zero
+ *               before its first use (the kernels leave it zeroed where it matters); one
+ *               workspace must not be shared by launches that can overlap on the GPU.
+ * group_size in {32, 64, 128}; M >= 0 (M == 0 is a no-op).
+ */
+size_t xqt_b200_w4a16_workspace_bytes(int m, int n, int k);
+
+int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* scales,
+                       const void* zero_points, const float* bias, const void* residual,
+                       void* output, int m, int n, int k, int padded_k, int group_size,
+                       int nibble_signed, int act_dtype, int param_dtype, int epilogue_activation,
+                       void* workspace, size_t workspace_bytes, int variant,
+                       xqt_b200_stream_t stream);
+
+/* Kernel the AUTO variant would pick for this problem (one of XQT_B200_VARIANT_*). */
+int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_size,
+                                  int epilogue_activation, int has_residual);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XQT_B200_H_ */

@@ -1,0 +1,112 @@
+"""W4A16 CUDA kernels against the CPU oracle, through the C ABI.  Bar: rel-L2 <= 1e-3 (bf16/fp16
+output, fp32 accumulation); the golden cases additionally compare with the reference's own output."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import seeded
+from oracle import w4a16 as oracle
+from xqt_b200.ops.w4a16 import select_variant, w4a16_linear
+from xqt_b200 import quantize
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def _run(case_x, qw, s, z, *, group, signed, k=None, bias=None, residual=None, activation="none", variant="auto"):
+    dev = torch.device("cuda", 0)
+    mv = lambda t: None if t is None else t.to(dev)
+    out = w4a16_linear(mv(case_x), mv(qw), mv(s), mv(z), mv(bias), mv(residual), group_size=group,
+                       nibble_signed=signed, k=k, activation=activation, variant=variant)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+@pytest.mark.parametrize("case", ["u4_g128_bf16", "u4_g64_fp16_bias", "s4_g32_bf16", "s4_g128_padk"])
+def test_golden_cases_simt(golden, case):
+    g = golden("w4a16")[case]
+    out = _run(g["x"], g["qweight"], g["scales"], g["zeros"], group=int(g["group"]), signed=bool(g["signed"]),
+               k=int(g["k"]), bias=g["bias"], variant="simt")
+    assert out.dtype == g["out"].dtype
+    assert oracle.rel_l2(out, g["out"]) <= TOL
+
+
+def test_golden_case_gemv(golden):
+    g = golden("w4a16")["u4_g128_bf16"]
+    assert select_variant(5, 64, 256, 256, 128) == "gemv"
+    out = _run(g["x"], g["qweight"], g["scales"], g["zeros"], group=128, signed=False, variant="gemv")
+    assert oracle.rel_l2(out, g["out"]) <= TOL
+
+
+def _synthetic(n, k, m, *, seed, dtype=torch.bfloat16, symmetric=False, param_dtype=torch.bfloat16, group=128):
+    w = torch.randn((n, k), generator=seeded(seed)) * 0.02
+    x = torch.randn((m, k), generator=seeded(seed + 1)).to(dtype)
+    if symmetric:
+        pw = quantize.quantize_w4_symmetric(w, group_size=group)
+    else:
+        pw = quantize.quantize_w4_asymmetric(w, group_size=group, param_dtype=param_dtype)
+    return x, pw
+
+
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096), (4096, 14336), (14336, 4096), (200, 512), (64, 128)])
+def test_gemv_decode_shapes(m, n, k):
+    if (n, k) in {(4096, 14336), (14336, 4096)} and m not in (1, 16):
+        pytest.skip("large shapes: first and last M only")
+    x, pw = _synthetic(n, k, m, seed=100 + m)
+    out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=128, signed=False, variant="gemv")
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=False)
+    assert oracle.rel_l2(out, ref) <= TOL
+    # split-K is reduced in a fixed order: a second launch is bit-identical
+    again = _run(x, pw.qweight, pw.scales, pw.zero_points, group=128, signed=False, variant="gemv")
+    assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("symmetric", [False, True])
+def test_gemv_dtypes_signedness_bias_residual(dtype, symmetric):
+    n, k, m = 384, 1024, 7
+    x, pw = _synthetic(n, k, m, seed=7, dtype=dtype, symmetric=symmetric, param_dtype=torch.float32)
+    bias = torch.randn((n,), generator=seeded(8))
+    residual = torch.randn((m, n), generator=seeded(9)).to(dtype)
+    out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=128, signed=symmetric, bias=bias,
+               residual=residual, variant="gemv")
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=symmetric, bias=bias,
+                      residual=residual)
+    assert oracle.rel_l2(out, ref) <= TOL
+
+
+def test_simt_and_gemv_agree_and_config1():
+    # configuration 1 of the benchmark: x [16,4096], W [4096,4096], uint4 g128, bf16 scale/zero
+    x = torch.randn((16, 4096), generator=seeded(1)).to(torch.bfloat16)
+    w = torch.randn((4096, 4096), generator=seeded(2)) * 0.02
+    pw = quantize.quantize_w4_asymmetric(w, group_size=128)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=False)
+    fast = _run(x, pw.qweight, pw.scales, pw.zero_points, group=128, signed=False)
+    slow = _run(x, pw.qweight, pw.scales, pw.zero_points, group=128, signed=False, variant="simt")
+    assert oracle.rel_l2(fast, ref) <= TOL
+    assert oracle.rel_l2(slow, ref) <= TOL
+
+
+@pytest.mark.parametrize("activation", ["relu", "gelu", "silu"])
+def test_simt_epilogue_activations(activation):
+    x, pw = _synthetic(96, 256, 5, seed=21, group=64)
+    bias = torch.randn((96,), generator=seeded(22))
+    out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=64, signed=False, bias=bias, activation=activation)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=64, signed=False, bias=bias,
+                      activation=activation)
+    assert oracle.rel_l2(out, ref) <= 2e-3   # bf16 output of a gated value: one extra rounding step
+
+
+def test_empty_batch_and_bad_arguments():
+    from xqt_b200.errors import XQTBackendError
+    x, pw = _synthetic(64, 128, 0, seed=3)
+    out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=128, signed=False)
+    assert tuple(out.shape) == (0, 64)
+    x1, _ = _synthetic(64, 256, 2, seed=3)
+    with pytest.raises(XQTBackendError):
+        _run(x1, pw.qweight, pw.scales, pw.zero_points, group=128, signed=False)       # K mismatch
+    with pytest.raises(XQTBackendError):
+        _run(x1[:, :128].float(), pw.qweight, pw.scales, pw.zero_points, group=128, signed=False)   # fp32 act

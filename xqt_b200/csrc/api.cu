@@ -1,0 +1,72 @@
+// C-ABI entry points: argument validation and kernel selection.  No kernel code lives here.
+#include "common.cuh"
+
+namespace xqt_b200 {
+int w4a16_simt_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int,
+                      int, int, int, int, int, int, int, cudaStream_t);
+int w4a16_gemv_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int,
+                      int, int, int, int, void*, size_t, cudaStream_t);
+size_t w4a16_gemv_workspace_bytes(int n, int k);
+bool w4a16_gemv_supported(int m, int n, int k, int padded_k, int group_size);
+}  // namespace xqt_b200
+
+using namespace xqt_b200;
+
+extern "C" {
+
+const char* xqt_b200_version(void) { return "xqt-b200 0.1 (sm_100a)"; }
+
+const char* xqt_b200_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
+
+int xqt_b200_device_supported(int device) {
+  int major = 0, minor = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device) != cudaSuccess) return 0;
+  return (major == 10 && minor == 0) ? 1 : 0;
+}
+
+size_t xqt_b200_w4a16_workspace_bytes(int m, int n, int k) {
+  (void)m;
+  if (n <= 0 || k <= 0) return 0;
+  return w4a16_gemv_workspace_bytes(n, k);
+}
+
+int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_size, int epilogue_activation,
+                                  int has_residual) {
+  (void)has_residual;
+  if (epilogue_activation == XQT_B200_ACT_NONE && w4a16_gemv_supported(m, n, k, padded_k, group_size))
+    return XQT_B200_VARIANT_GEMV;
+  return XQT_B200_VARIANT_SIMT;
+}
+
+int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* scales, const void* zero_points,
+                       const float* bias, const void* residual, void* output, int m, int n, int k, int padded_k,
+                       int group_size, int nibble_signed, int act_dtype, int param_dtype, int epilogue_activation,
+                       void* workspace, size_t workspace_bytes, int variant, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(m >= 0 && n > 0 && k > 0 && padded_k >= k);
+  XQT_REQUIRE(group_size == 32 || group_size == 64 || group_size == 128);
+  XQT_REQUIRE(padded_k % group_size == 0);
+  XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
+  XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
+  XQT_REQUIRE(epilogue_activation >= XQT_B200_ACT_NONE && epilogue_activation <= XQT_B200_ACT_SILU);
+  if (m == 0) return 0;
+  XQT_REQUIRE(activation != nullptr && qweight != nullptr && scales != nullptr && output != nullptr);
+  if (variant == XQT_B200_VARIANT_AUTO)
+    variant = xqt_b200_w4a16_select_variant(m, n, k, padded_k, group_size, epilogue_activation, residual != nullptr);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (variant) {
+    case XQT_B200_VARIANT_SIMT:
+      return w4a16_simt_launch(activation, qweight, scales, zero_points, bias, residual, output, m, n, k, padded_k,
+                               group_size, nibble_signed, act_dtype, param_dtype, epilogue_activation, s);
+    case XQT_B200_VARIANT_GEMV:
+      XQT_REQUIRE(epilogue_activation == XQT_B200_ACT_NONE);
+      XQT_REQUIRE(w4a16_gemv_supported(m, n, k, padded_k, group_size));
+      XQT_REQUIRE(((uintptr_t)activation & 15) == 0 && ((uintptr_t)qweight & 15) == 0);
+      return w4a16_gemv_launch(activation, qweight, scales, zero_points, bias, residual, output, m, n, k,
+                               nibble_signed, act_dtype, param_dtype, workspace, workspace_bytes, s);
+    default:
+      return (int)cudaErrorInvalidValue;
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,119 @@
+"""GEMM-registry executors backed by the sm_100a kernels, and their installer.
+
+An executor has xqt's executor signature (xqt/kernels/ops/gemm/dispatch.py:239-250):
+``executor(activation, weight, *, spec, weight_scales, activation_scales, weight_zero_points,
+activation_zero_points, bias, residual, **kwargs) -> Tensor``; it allocates and returns the
+output on ``activation.device``, never mutates its inputs, enqueues on torch's current stream and
+raises ``XQTBackendError`` for anything outside its envelope (same checks, same wording pattern,
+as ``sm89_w4a16_dequant_executor``, _impl/gemm_backends/sm89/w4a16_sm89.py:198-300).  Only
+attributes are read from ``weight`` / ``spec``, so xqt's own ``PackedWeight`` / ``GemmSpec``
+objects work as well as this package's mirrors; ``install_b200_executors`` therefore also accepts
+xqt's ``GemmKernelRegistry`` (anything with ``register/replace/get``).
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import replace as _dc_replace
+
+import torch
+
+from . import native
+from .errors import XQTBackendError
+from .layout import validate_w4a16_packed_weight
+from .registry import B200_W4A16, GemmKernelRegistry, b200_rows
+
+_TORCH = {"fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+def _require_b200(device: torch.device) -> None:
+    if os.environ.get("XQT_DISABLE_B200", "") not in {"", "0"}:
+        raise XQTBackendError("B200 backend disabled by XQT_DISABLE_B200")
+    if device.type != "cuda":
+        raise XQTBackendError("B200 executors need CUDA tensors")
+    major, minor = torch.cuda.get_device_capability(device)
+    if (major, minor) != (10, 0):
+        raise XQTBackendError(f"B200 executor received sm_{major}{minor}")
+
+
+def b200_w4a16_executor(activation, weight, *, spec, weight_scales=None, activation_scales=None,
+                        weight_zero_points=None, activation_zero_points=None, bias=None, residual=None,
+                        variant: str = "auto", output: torch.Tensor | None = None) -> torch.Tensor:
+    """W4A16 on the canonical ``xqt_int4_nk_v1`` PackedWeight, fp16 or bf16, any M."""
+
+    from .ops.w4a16 import w4a16_linear
+
+    if not hasattr(weight, "metadata"):
+        raise XQTBackendError("B200 W4A16 requires a canonical PackedWeight")
+    quant, problem = spec.quant, spec.problem
+    if quant.activation_dtype not in _TORCH:
+        raise XQTBackendError("B200 W4A16 supports fp16 or bf16 activations")
+    if quant.output_dtype != quant.activation_dtype:
+        raise XQTBackendError("B200 W4A16 requires output dtype equal to activation dtype")
+    if activation_scales is not None or activation_zero_points is not None:
+        raise XQTBackendError("W4A16 does not accept activation quantization scales")
+    try:
+        validate_w4a16_packed_weight(weight, spec=quant, logical_shape=(problem.n, problem.k))
+    except (TypeError, ValueError) as exc:
+        raise XQTBackendError(f"B200 W4A16 packed weight rejected: {exc}") from exc
+    if weight_scales is not None and weight_scales is not weight.scales and not torch.equal(weight_scales, weight.scales):
+        raise XQTBackendError("external weight_scales disagree with PackedWeight.scales")
+    if (weight_zero_points is not None and weight_zero_points is not weight.zero_points
+            and not torch.equal(weight_zero_points, weight.zero_points)):
+        raise XQTBackendError("external weight_zero_points disagree with PackedWeight.zero_points")
+    if not isinstance(activation, torch.Tensor) or activation.ndim != 2 or not activation.is_cuda:
+        raise XQTBackendError("B200 W4A16 activation must be CUDA rank-2")
+    _require_b200(activation.device)
+    if activation.dtype != _TORCH[quant.activation_dtype]:
+        raise XQTBackendError("B200 W4A16 activation dtype disagrees with QuantSpec")
+    if tuple(activation.shape) != (problem.m, problem.k):
+        raise XQTBackendError("B200 W4A16 activation shape does not match GemmProblem")
+    if spec.epilogue.has_bias and bias is None:
+        raise XQTBackendError("W4A16 epilogue declares bias but no bias was supplied")
+    if spec.epilogue.has_residual and residual is None:
+        raise XQTBackendError("W4A16 epilogue declares residual but no residual was supplied")
+    if bias is not None and tuple(bias.shape) not in {(problem.n,), (1, problem.n)}:
+        raise XQTBackendError("B200 W4A16 bias must have shape [N] or [1,N]")
+    scales, zeros = weight.scales, weight.zero_points
+    if zeros is not None and zeros.dtype != scales.dtype:
+        zeros = zeros.to(scales.dtype)
+    return w4a16_linear(
+        activation.contiguous(), weight.qweight, scales.contiguous(), None if zeros is None else zeros.contiguous(),
+        bias, None if residual is None else residual.contiguous(), group_size=int(weight.metadata.group_size),
+        nibble_signed=bool(weight.metadata.nibble_signed), k=problem.k, activation=spec.epilogue.activation,
+        variant=variant, out=output,
+    )
+
+
+_EXECUTORS = {B200_W4A16: b200_w4a16_executor}
+
+
+def install_b200_executors(registry: GemmKernelRegistry | None = None, *, require_native: bool = True) -> tuple[str, ...]:
+    """Register the B200 rows (if absent) and promote those with an executor to ``executable``.
+
+    Returns the names promoted.  With ``require_native`` (default) a missing or stale shared
+    library raises ``NativeLibraryError`` instead of silently leaving rows metadata-only.
+    """
+
+    from .registry import default_registry
+
+    registry = default_registry() if registry is None else registry
+    if require_native:
+        native.library()
+    elif not native.available():
+        return ()
+    promoted = []
+    for row in b200_rows():
+        try:
+            registry.get(row.name)
+        except KeyError:
+            registry.register(row)
+        executor = _EXECUTORS.get(row.name)
+        if executor is None:
+            continue
+        registry.replace(_dc_replace(registry.get(row.name), maturity="executable", executor=executor))
+        promoted.append(row.name)
+    return tuple(promoted)
+
+
+__all__ = ["b200_w4a16_executor", "install_b200_executors"]

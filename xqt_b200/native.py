@@ -1,0 +1,123 @@
+"""ctypes binding of the C-ABI shared library (``include/xqt_b200.h``).
+
+The library is built in-tree by :mod:`xqt_b200.build` as ``xqt_b200/libxqt_b200.so``.
+There is no fallback: if the library is missing or a symbol is absent the call
+raises :class:`NativeLibraryError`; a non-zero return code raises
+:class:`CudaCallError`.  Both derive from ``XQTBackendError`` so xqt's GEMM
+dispatcher records them and walks on to its next candidate
+(xqt/kernels/ops/gemm/dispatch.py:253-257), exactly as for its sm_89 artifacts
+(xqt/kernels/ops/_impl/gemm_backends/sm89/w4a16_sm89.py:61-78).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import pathlib
+import threading
+
+import torch
+
+from .errors import CudaCallError, NativeLibraryError
+
+LIBRARY_PATH = pathlib.Path(__file__).resolve().parent / "libxqt_b200.so"
+
+FP16, BF16, FP32 = 0, 1, 2
+ACT = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
+VARIANT = {"auto": 0, "simt": 1, "gemv": 2, "tcgen05": 3}
+VARIANT_NAMES = {value: key for key, value in VARIANT.items()}
+DTYPE_CODE = {torch.float16: FP16, torch.bfloat16: BF16, torch.float32: FP32}
+
+_P, _I, _Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+
+# symbol -> (restype, argtypes); must list every function include/xqt_b200.h declares
+SIGNATURES: dict[str, tuple] = {
+    "xqt_b200_version": (ctypes.c_char_p, []),
+    "xqt_b200_error_string": (ctypes.c_char_p, [_I]),
+    "xqt_b200_device_supported": (_I, [_I]),
+    "xqt_b200_w4a16_workspace_bytes": (_Z, [_I, _I, _I]),
+    "xqt_b200_w4a16_select_variant": (_I, [_I] * 7),
+    "xqt_b200_w4a16_run": (_I, [_P] * 7 + [_I] * 9 + [_P, _Z, _I, _P]),
+}
+
+_lock = threading.Lock()
+_library: ctypes.CDLL | None = None
+
+
+def library() -> ctypes.CDLL:
+    """Load (once) and return the shared library with typed prototypes."""
+
+    global _library
+    if _library is not None:
+        return _library
+    with _lock:
+        if _library is not None:
+            return _library
+        if not LIBRARY_PATH.exists():
+            raise NativeLibraryError(
+                f"{LIBRARY_PATH} is missing: build it with `python -m xqt_b200.build` (needs nvcc)"
+            )
+        try:
+            handle = ctypes.CDLL(str(LIBRARY_PATH))
+        except OSError as exc:
+            raise NativeLibraryError(f"cannot load {LIBRARY_PATH}: {exc}") from exc
+        for name, (restype, argtypes) in SIGNATURES.items():
+            try:
+                function = getattr(handle, name)
+            except AttributeError as exc:
+                raise NativeLibraryError(f"{LIBRARY_PATH} lacks symbol {name}; rebuild it") from exc
+            function.restype = restype
+            function.argtypes = argtypes
+        _library = handle
+        return handle
+
+
+def available() -> bool:
+    """True when the library loads.  Says nothing about a GPU being present."""
+
+    try:
+        library()
+    except NativeLibraryError:
+        return False
+    return True
+
+
+def version() -> str:
+    return library().xqt_b200_version().decode()
+
+
+def check(code: int, symbol: str) -> None:
+    if code != 0:
+        detail = library().xqt_b200_error_string(int(code))
+        raise CudaCallError(symbol, code, detail.decode() if detail else "")
+
+
+def ptr(tensor: torch.Tensor | None) -> int:
+    return 0 if tensor is None else tensor.data_ptr()
+
+
+def stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# One scratch buffer per (device, stream): launches on one stream are ordered, so they may share
+# it; launches on different streams may overlap and must not.
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch of at least ``nbytes`` for the current stream of ``device``."""
+
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, stream_handle(device))
+    buffer = _workspaces.get(key)
+    if buffer is None or buffer.numel() < nbytes:
+        size = max(int(nbytes), 1 << 20)
+        buffer = torch.zeros(size, dtype=torch.uint8, device=torch.device("cuda", index))
+        _workspaces[key] = buffer
+    return buffer
+
+
+__all__ = [
+    "ACT", "BF16", "DTYPE_CODE", "FP16", "FP32", "LIBRARY_PATH", "SIGNATURES", "VARIANT", "VARIANT_NAMES",
+    "available", "check", "library", "ptr", "stream_handle", "version", "workspace",
+]
