@@ -40,7 +40,7 @@ GROUP = 128
 METRIC = "w4a16_decode_gemv_weight_bandwidth"
 UNIT = "GB/s"
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_gemv_kernel launch from the committed
+# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_kernel launch from the committed
 # ncu capture (profiles/), or None while no capture backs it
 NCU_TRAFFIC_BYTES_PER_LAUNCH = None
 
@@ -193,10 +193,9 @@ def run_reference_arm(args) -> None:
 def run_gpu_arm(args) -> None:
     import torch.distributed as dist
 
-    from xqt_b200.contracts import EpilogueSpec, GemmProblem, GemmSpec, PackedWeight
-    from xqt_b200.dispatch import dispatch_gemm
-    from xqt_b200.executors import install_b200_executors
-    from xqt_b200 import quantize
+    from xqt_b200.contracts import PackedWeight
+    from xqt_b200 import prepack
+    from xqt_b200.ops.w4a16 import bind_w4a16_decode
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -207,7 +206,6 @@ def run_gpu_arm(args) -> None:
     torch.cuda.set_device(device)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    install_b200_executors()
 
     # --- synthetic layers: POOL device copies of every (sharded) layer, rotated to defeat L2
     cpu_layers = {(k, n): make_layer(k, n, 10 + i) for i, (k, n) in enumerate(SHAPES)}
@@ -225,41 +223,66 @@ def run_gpu_arm(args) -> None:
     local_layers = {key: (shard(pw, key[1]) if world > 1 else pw) for key, pw in cpu_layers.items()}
     bytes_per_copy = sum(pw.qweight.numel() + 4 * pw.scales.numel() for pw in local_layers.values())
     pool = max(2, -(-2 * L2_BYTES // bytes_per_copy))
+    # the decode kernel runs on the tile-ordered execution layout derived once from the canonical weight
     dev_layers = []
     for _ in range(pool):
-        dev_layers.append({
-            key: PackedWeight(qweight=pw.qweight.to(device).clone(), scales=pw.scales.to(device).clone(),
-                              zero_points=pw.zero_points.to(device).clone(), metadata=pw.metadata)
-            for key, pw in local_layers.items()})
+        copy_layers = {}
+        for key, pw in local_layers.items():
+            copy_layers[key] = prepack.tile_w4(
+                pw.qweight.to(device), pw.scales.to(device), pw.zero_points.to(device), group_size=GROUP,
+                nibble_signed=False)
+        dev_layers.append(copy_layers)
     dev_inputs = {key: x.to(device) for key, x in inputs.items()}
     host_inputs = {key: x.pin_memory() for key, x in inputs.items()}
-    specs = {}
-    for (k, n) in SHAPES:
-        for m in MS:
-            specs[(k, n, m)] = GemmSpec(
-                problem=GemmProblem(m=m, n=n // world, k=k, phase="decode", device=str(device), sm=100),
-                quant=quantize.w4_spec(group_size=GROUP, symmetric=False), epilogue=EpilogueSpec(output_dtype="bf16"))
+    # hot-callables bound once per (pool copy, layer, M): the per-call host work is one C-ABI call
+    bound = {}
+    for copy in range(pool):
+        for (k, n) in SHAPES:
+            for m in MS:
+                bound[(copy, k, n, m)] = bind_w4a16_decode(dev_layers[copy][(k, n)], rows=m, dtype=torch.bfloat16)
+    outputs = {(n, m): torch.empty((m, n // world), device=device, dtype=torch.bfloat16) for _, n in SHAPES for m in MS}
     gathered = {(n, m): torch.empty((world, m, n // world), device=device, dtype=torch.bfloat16)
                 for _, n in SHAPES for m in MS} if world > 1 else {}
     launches = 0
 
     def one_problem(copy, k, n, m, x):
         nonlocal launches
-        res = dispatch_gemm(x, dev_layers[copy][(k, n)], spec=specs[(k, n, m)])
+        y = bound[(copy, k, n, m)](x, outputs[(n, m)])
         launches += 1
         if world > 1:
             buf = gathered[(n, m)]
-            dist.all_gather_into_tensor(buf, res.output)
+            dist.all_gather_into_tensor(buf, y)
             return buf.permute(1, 0, 2).reshape(m, n)
-        return res.output
+        return y
 
-    def step(i):
+    def eager_step(i):
         copy = i % pool
         out = None
         for (k, n) in SHAPES:
             for m in MS:
                 out = one_problem(copy, k, n, m, dev_inputs[(k, m)])
         return out
+
+    # the launch-bound step (16 kernels of a few microseconds) is captured in CUDA graphs, one per
+    # pool copy; the timed region replays them
+    side = torch.cuda.Stream(device)
+    graphs = []
+    with torch.cuda.stream(side):
+        for i in range(pool):
+            eager_step(i)
+        side.synchronize()
+        for i in range(pool):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                eager_step(i)
+            graphs.append(graph)
+    torch.cuda.synchronize()
+    launches_per_step = len(SHAPES) * len(MS)
+
+    def step(i):
+        nonlocal launches
+        graphs[i % pool].replay()
+        launches += launches_per_step
 
     def barrier():
         if world > 1:
@@ -327,20 +350,24 @@ def run_gpu_arm(args) -> None:
     # --- per-problem detail: each kernel timed alone, weights rotated through the pool
     peak, peak_kind = measured_peak()
     detail = []
-    if rank == 0 or world > 1:
-        reps = 40
+    reps = 10
+    with torch.cuda.stream(side):
         for (k, n) in SHAPES:
             for m in MS:
-                for i in range(5):
-                    one_problem(i % pool, k, n, m, dev_inputs[(k, m)])
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(pool):
+                        one_problem(i, k, n, m, dev_inputs[(k, m)])
+                for _ in range(3):
+                    graph.replay()
                 barrier()
                 e0.record()
-                for i in range(reps):
-                    one_problem(i % pool, k, n, m, dev_inputs[(k, m)])
+                for _ in range(reps):
+                    graph.replay()
                 e1.record()
                 barrier()
-                us = e0.elapsed_time(e1) * 1e3 / reps
-                nb = algorithmic_bytes(k, n // world, m) if world > 1 else algorithmic_bytes(k, n, m)
+                us = e0.elapsed_time(e1) * 1e3 / (reps * pool)
+                nb = algorithmic_bytes(k, n // world, m)
                 detail.append({"k": k, "n": n, "m": m, "us": round(us, 3), "gbs": round(nb / us / 1e3, 1),
                                "frac": round(nb / us / 1e3 / peak, 4)})
     alg_bytes_step = sum(algorithmic_bytes(k, n // world, m) for k, n in SHAPES for m in MS)
@@ -362,7 +389,7 @@ def run_gpu_arm(args) -> None:
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peak_kind}",
-            "kernel": "w4a16_gemv_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank)",
+            "kernel": "w4a16_decode_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank)",
         },
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -385,14 +412,48 @@ def run_gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+def run_single_problem(args) -> None:
+    """One decode problem, `steps` eager launches over a weight pool larger than L2."""
+
+    from xqt_b200 import prepack
+    from xqt_b200.ops.w4a16 import bind_w4a16_decode
+
+    k, n, m = (int(v) for v in args.problem.split(","))
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    pw = make_layer(k, n, 10)
+    pool = max(2, -(-2 * L2_BYTES // weight_aux_bytes(k, n)))
+    tiled = [prepack.tile_w4(pw.qweight.to(device).clone(), pw.scales.to(device), pw.zero_points.to(device),
+                             group_size=GROUP, nibble_signed=False) for _ in range(pool)]
+    x = torch.randn((m, k), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(device)
+    runs = [bind_w4a16_decode(t, rows=m, dtype=torch.bfloat16) for t in tiled]
+    out = torch.empty((m, n), device=device, dtype=torch.bfloat16)
+    for i in range(max(args.warmup, 3)):
+        runs[i % pool](x, out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        runs[i % pool](x, out)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    print(json.dumps({"problem": [k, n, m], "us_per_launch_eager": us, "pool": pool,
+                      "gbs": algorithmic_bytes(k, n, m) / us / 1e3}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--problem", default=None,
+                        help="K,N,M: run only this decode problem, eagerly (the small case used for ncu captures)")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.problem is not None:
+        run_single_problem(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

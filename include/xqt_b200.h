@@ -89,6 +89,65 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
 int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_size,
                                   int epilogue_activation, int has_residual);
 
+/* ------------------------------------------------------------------------------------------
+ * W4A16 decode (M <= 16) on the tile-ordered execution layout b200_w4_tile128_v1.
+ *
+ * Replaces the decode entry xqt_awq_w4a16_sm89_decode and its pack step
+ * xqt_awq_w4a16_sm89_pack (awq_w4a16_sm89_kernel.cu:728-784), which also run on a
+ * backend-private interleaved layout derived once from the canonical weight
+ * (_impl/gemm_backends/sm89/awq_w4a16_decode_sm89.py:16-98).
+ *
+ *   tiled_weights  uint8 [ceil(N/128)][K/128][16][32][16]   (xqt_b200/prepack.py: tile_w4)
+ *   tiled_params   param_dtype [ceil(N/128)][K/128][128/group_size][128][2] = (scale, zero point)
+ *   K a multiple of 256; group_size in {32, 64, 128}; 1 <= M <= 16.
+ *   workspace      at least xqt_b200_w4a16_decode_workspace_bytes() bytes, zero before first use;
+ *                  its first 32-bit word is a status word (0 = ok) that a kernel whose bounded
+ *                  wait ran out sets to a non-zero code; read it with xqt_b200_workspace_status.
+ */
+size_t xqt_b200_w4a16_decode_workspace_bytes(void);
+int xqt_b200_w4a16_decode_supported(int m, int n, int k, int group_size);
+int xqt_b200_w4a16_decode_tiled(const void* activation, const void* tiled_weights,
+                                const void* tiled_params, const float* bias, const void* residual,
+                                void* output, int m, int n, int k, int group_size,
+                                int nibble_signed, int has_zero_point, int act_dtype,
+                                int param_dtype, void* workspace, size_t workspace_bytes,
+                                xqt_b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Activation prologue shared by the W8A8 and W4A4 linears: block-diagonal Hadamard rotation,
+ * one rounding to the activation dtype, dynamic symmetric quantisation.
+ *
+ * Replaces xqt_convrot_w8a8_sm89_quantize_rotated_act / _small_quantize
+ * (convrot_w8a8_sm89_kernel.cu:57-504) and the rotate + quantise half of
+ * quantize_w4a4_act_fuse_lora (svdq_w4a4_sm89_kernel.cu:24-328).
+ *
+ *   activation    [M, K] act_dtype
+ *   rot_kind      0 none, 1 regular Hadamard (rot_block a power of 4), 2 Sylvester (power of 2)
+ *   column_scale  [rot_block] fp32 = signs / sqrt(rot_block) (NULL when rot_kind == 0)
+ *   quant_bits    8: per-token scale max(amax,1e-8)/127, codes in [-128,127], scales [M]
+ *                 4: per (token, group_size) scale max(amax/7,1e-6), codes in [-8,7], scales [M, K/group_size]
+ *   codes         int8 [M, K] in both modes;  rotated: [M, K] act_dtype or NULL (the rotated, rounded
+ *                 activation, input of the W4A4 low-rank branch)
+ */
+int xqt_b200_rotate_quantize(const void* activation, const float* column_scale, void* codes,
+                             float* scales, void* rotated, int m, int k, int rot_kind, int rot_block,
+                             int quant_bits, int group_size, int act_dtype, xqt_b200_stream_t stream);
+
+/* W8A8 GEMM: output[m,n] = int32(sum_k a[m,k] w[n,k]) * act_scale[m] * weight_scale[n] (+ bias[n]).
+ * Replaces xqt_convrot_w8a8_sm89_gemm / _small_gemm (convrot_w8a8_sm89_kernel.cu:506-755; the
+ * Nunchaku main loop jit/include/nunchaku/gemm_w8a8.cuh:11-61).  act_codes int8 [M,K], weight_codes
+ * int8 [N,K] (both K-major), K a multiple of 16, N a multiple of 8, output [M,N] out_dtype.
+ * workspace: at least 256 bytes, zero before first use (status word). */
+int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const float* act_scale,
+                       const float* weight_scale, const float* bias, void* output, int m, int n,
+                       int k, int out_dtype, void* workspace, size_t workspace_bytes,
+                       xqt_b200_stream_t stream);
+
+/* Copies the status word of `workspace` to *host_status (host pointer) and synchronises `stream`.
+ * No counterpart in the reference, whose kernels have no device-side waits. */
+int xqt_b200_workspace_status(const void* workspace, unsigned int* host_status,
+                              xqt_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

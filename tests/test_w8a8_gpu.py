@@ -1,0 +1,87 @@
+"""ConvRot W8A8 on the GPU against the CPU oracle: activation codes and scales bit-exact, output
+rel-L2 <= 1e-3 against the reference's dequantise-then-matmul form."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import seeded
+from oracle import rotation as orot
+from oracle import w4a16 as o16
+from oracle import w8a8 as oracle
+from xqt_b200 import native, quantize
+from xqt_b200.ops.activation import rotate_quantize
+from xqt_b200.ops.w8a8 import convrot_w8a8_linear, pack_convrot_w8a8_linear, w8a8_gemm
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+
+
+def _layer(n, k, seed, rot):
+    w = torch.randn((n, k), generator=seeded(seed)) * 0.02
+    q, s = quantize.quantize_w8_per_channel(rot.apply(w))
+    return q, s
+
+
+@pytest.mark.parametrize("kind,block", [("regular", 256), ("regular", 64), ("regular", 16), ("sylvester", 128),
+                                        ("sylvester", 32), (None, 0)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_rotation_and_int8_codes_bit_exact(kind, block, dtype):
+    m, k = 37, 1024
+    x = (torch.randn((m, k), generator=seeded(3)) * 1.7).to(dtype)
+    if kind is None:
+        rot, x_rot = None, x
+    else:
+        rot = quantize.Rotation(kind, block, orot.random_signs(block, 5) if kind == "sylvester" else None)
+        x_rot = orot.rotate_fht(x, kind=kind, block=block, signs=rot.signs)
+    q_ref, s_ref = oracle.quantize_act_per_token(x_rot)
+    codes, scales, rotated = rotate_quantize(x.to(DEV), rot, bits=8, return_rotated=True)
+    torch.cuda.synchronize()
+    assert torch.equal(rotated.cpu(), x_rot)
+    assert torch.equal(scales.cpu(), s_ref.reshape(-1))
+    assert torch.equal(codes.cpu(), q_ref)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 256, 512), (100, 136, 272), (2048, 4096, 4096),
+                                   (1, 64, 128), (300, 384, 1040)])
+def test_w8a8_gemm_integer_exact(m, n, k):
+    # random int8 operands, unit scales: the tensor-core accumulation must be exact
+    a = torch.randint(-128, 128, (m, k), generator=seeded(m + n), dtype=torch.int64).to(torch.int8)
+    w = torch.randint(-127, 128, (n, k), generator=seeded(k), dtype=torch.int64).to(torch.int8)
+    sa = torch.rand((m,), generator=seeded(1)) * 1e-2 + 1e-3
+    sw = torch.rand((n,), generator=seeded(2)) * 1e-3 + 1e-4
+    packed = pack_convrot_w8a8_linear(w.t().contiguous().to(DEV), sw.to(DEV), None, dtype=torch.bfloat16)
+    out = w8a8_gemm(a.to(DEV), sa.to(DEV), packed)
+    torch.cuda.synchronize()
+    assert native.workspace_status(DEV) == 0
+    ref = oracle.gemm_integer(a, sa, w, sw)
+    assert o16.rel_l2(out.cpu(), ref) <= 1e-3
+    mismatch = (out.cpu() != ref).float().mean().item()
+    assert mismatch < 0.01          # same fp32 value rounded once to bf16; isolated ulp flips only
+
+
+def test_config4_full_forward():
+    # x [2048,4096] ~ N(0,1) bf16, regular Hadamard 256, W [4096,4096] ~ N(0,0.02) per-channel int8
+    m, n, k = 2048, 4096, 4096
+    rot = quantize.regular_rotation(256)
+    x = torch.randn((m, k), generator=seeded(5)).to(torch.bfloat16)
+    q, s = _layer(n, k, 6, rot)
+    bias = torch.randn((n,), generator=seeded(7))
+    packed = pack_convrot_w8a8_linear(q.t().contiguous().to(DEV), s.to(DEV), bias.to(DEV), dtype=torch.bfloat16)
+    out = convrot_w8a8_linear(x.to(DEV), packed, rot_size=256)
+    torch.cuda.synchronize()
+    ref = oracle.linear(x, q, s, rot_block=256, rot_kind="regular", bias=bias)
+    assert o16.rel_l2(out.cpu(), ref) <= 1e-3
+    assert native.workspace_status(DEV) == 0
+
+
+def test_batched_input_and_fp16():
+    rot = quantize.regular_rotation(64)
+    x = torch.randn((3, 5, 256), generator=seeded(11)).to(torch.float16)
+    q, s = _layer(72, 256, 12, rot)
+    packed = pack_convrot_w8a8_linear(q.t().contiguous().to(DEV), s.to(DEV), None, dtype=torch.float16)
+    out = convrot_w8a8_linear(x.to(DEV), packed, rot_size=64)
+    assert tuple(out.shape) == (3, 5, 72)
+    ref = oracle.linear(x.reshape(15, 256), q, s, rot_block=64, rot_kind="regular")
+    assert o16.rel_l2(out.cpu().reshape(15, 72), ref) <= 1e-3

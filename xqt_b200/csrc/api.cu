@@ -8,6 +8,13 @@ int w4a16_gemv_launch(const void*, const void*, const void*, const void*, const 
                       int, int, int, int, void*, size_t, cudaStream_t);
 size_t w4a16_gemv_workspace_bytes(int n, int k);
 bool w4a16_gemv_supported(int m, int n, int k, int padded_k, int group_size);
+int w4a16_decode_launch(const void*, const void*, const void*, const float*, const void*, void*, int, int, int, int, int,
+                        int, int, int, void*, size_t, cudaStream_t);
+size_t w4a16_decode_workspace_bytes();
+bool w4a16_decode_supported(int m, int n, int k, int group_size);
+int rotate_quant_launch(const void*, const float*, void*, float*, void*, int, int, int, int, int, int, int, cudaStream_t);
+int gemm_i8_launch(const void*, const void*, const float*, const float*, const float*, void*, int, int, int, int,
+                   unsigned int*, cudaStream_t);
 }  // namespace xqt_b200
 
 using namespace xqt_b200;
@@ -67,6 +74,51 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
     default:
       return (int)cudaErrorInvalidValue;
   }
+}
+
+size_t xqt_b200_w4a16_decode_workspace_bytes(void) { return w4a16_decode_workspace_bytes(); }
+
+int xqt_b200_w4a16_decode_supported(int m, int n, int k, int group_size) {
+  return w4a16_decode_supported(m, n, k, group_size) ? 1 : 0;
+}
+
+int xqt_b200_w4a16_decode_tiled(const void* activation, const void* tiled_weights, const void* tiled_params,
+                                const float* bias, const void* residual, void* output, int m, int n, int k,
+                                int group_size, int nibble_signed, int has_zero_point, int act_dtype, int param_dtype,
+                                void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(m >= 0 && n > 0 && k > 0);
+  XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
+  XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
+  if (m == 0) return 0;
+  XQT_REQUIRE(activation != nullptr && tiled_weights != nullptr && tiled_params != nullptr && output != nullptr);
+  return w4a16_decode_launch(activation, tiled_weights, tiled_params, bias, residual, output, m, n, k, group_size,
+                             nibble_signed, has_zero_point, act_dtype, param_dtype, workspace, workspace_bytes,
+                             (cudaStream_t)stream);
+}
+
+int xqt_b200_rotate_quantize(const void* activation, const float* column_scale, void* codes, float* scales,
+                             void* rotated, int m, int k, int rot_kind, int rot_block, int quant_bits, int group_size,
+                             int act_dtype, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(activation != nullptr && codes != nullptr && scales != nullptr);
+  return rotate_quant_launch(activation, column_scale, codes, scales, rotated, m, k, rot_kind, rot_block, quant_bits,
+                             group_size, act_dtype, (cudaStream_t)stream);
+}
+
+int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const float* act_scale,
+                       const float* weight_scale, const float* bias, void* output, int m, int n, int k, int out_dtype,
+                       void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
+  return gemm_i8_launch(act_codes, weight_codes, act_scale, weight_scale, bias, output, m, n, k, out_dtype,
+                        reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
+}
+
+int xqt_b200_workspace_status(const void* workspace, unsigned int* host_status, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(workspace != nullptr && host_status != nullptr);
+  XQT_CUDA(cudaMemcpyAsync(host_status, workspace, sizeof(unsigned int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  XQT_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return 0;
 }
 
 }  // extern "C"

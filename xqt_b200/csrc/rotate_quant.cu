@@ -1,0 +1,140 @@
+// Activation prologue of the W8A8 / W4A4 linears: block-diagonal Hadamard rotation followed by
+// dynamic symmetric quantisation, one CTA per token.
+//
+// Rotation (xqt/compression/quant/quantizers/convrot_4bit.py:85-229, xqt/model/minicpm5_quarot.py:54-93):
+// every `block` consecutive features are multiplied by H / sqrt(block) * signs, H the regular
+// Hadamard matrix (orders 4^k) or the Sylvester matrix (orders 2^k).  It is evaluated as a fast
+// Hadamard transform in fp32 with a FIXED butterfly order so the result is reproducible bit for
+// bit on any machine: stages run from the smallest stride up; a regular stage maps (a,b,c,d) at
+// distance `stride` to (p+t, p-t, q+r, r-q) with p=a+b, q=a-b, r=c+d, t=c-d; a Sylvester stage maps
+// (a,b) to (a+b, a-b).  Then one multiply by column_scale[j] = signs[j]/sqrt(block) and one rounding
+// to the activation dtype, the dtype every reference variant quantises the rotated activation in
+// (convrot_int8.py:432-452, convrot_w8a8_sm89_kernel.cu:57-333).
+//
+// Quantisation, IEEE division and round-half-to-even throughout:
+//   mode 8: per token,  scale = max(amax, 1e-8) / 127, q = clamp(rint(x/scale), -128, 127)
+//           (xqt/kernels/ops/gemm/quantize.py:75-107)
+//   mode 4: per (token, group), scale = max(amax/7, 1e-6), q = clamp(rint(x/scale), -8, 7)
+//           (convrot_4bit.py:669-679 at the group granularity of gemm_w4a4.cuh:534-624)
+// Codes are written as int8 in both modes (the int4 GEMM consumes int8 operands: Blackwell has no
+// int4 MMA).
+#include "common.cuh"
+
+namespace xqt_b200 {
+
+constexpr int kRqThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kRqThreads)
+rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_scale, int8_t* __restrict__ codes,
+                    float* __restrict__ scales, T* __restrict__ x_rot, int k, int rot_kind, int rot_block, int mode,
+                    int group) {
+  extern __shared__ float v[];  // [k]
+  __shared__ float s_red[kRqThreads / 32];
+  __shared__ float s_scale;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const T* xr = x + (size_t)row * k;
+  for (int i = tid; i < k; i += kRqThreads) v[i] = to_float<T>(xr[i]);
+  __syncthreads();
+  if (rot_kind == 1) {
+    for (int stride = 1; stride < rot_block; stride *= 4) {
+      for (int b = tid; b < k / 4; b += kRqThreads) {
+        const int base = (b / stride) * 4 * stride + (b % stride);
+        const float a = v[base], bb = v[base + stride], c = v[base + 2 * stride], d = v[base + 3 * stride];
+        const float p = __fadd_rn(a, bb), q = __fsub_rn(a, bb), r = __fadd_rn(c, d), t = __fsub_rn(c, d);
+        v[base] = __fadd_rn(p, t);
+        v[base + stride] = __fsub_rn(p, t);
+        v[base + 2 * stride] = __fadd_rn(q, r);
+        v[base + 3 * stride] = __fsub_rn(r, q);
+      }
+      __syncthreads();
+    }
+  } else if (rot_kind == 2) {
+    for (int stride = 1; stride < rot_block; stride *= 2) {
+      for (int b = tid; b < k / 2; b += kRqThreads) {
+        const int base = (b / stride) * 2 * stride + (b % stride);
+        const float a = v[base], bb = v[base + stride];
+        v[base] = __fadd_rn(a, bb);
+        v[base + stride] = __fsub_rn(a, bb);
+      }
+      __syncthreads();
+    }
+  }
+  // normalise, round once to T (kept in fp32 registers/shared memory as the rounded value)
+  float amax = 0.f;
+  for (int i = tid; i < k; i += kRqThreads) {
+    float r = v[i];
+    if (rot_kind != 0) r = __fmul_rn(r, column_scale[i % rot_block]);
+    const T rounded = from_float<T>(r);
+    if (x_rot != nullptr) x_rot[(size_t)row * k + i] = rounded;
+    r = to_float<T>(rounded);
+    v[i] = r;
+    amax = fmaxf(amax, fabsf(r));
+  }
+  if (mode == 8) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((tid & 31) == 0) s_red[tid >> 5] = amax;
+    __syncthreads();
+    if (tid == 0) {
+      float mx = 0.f;
+      for (int w = 0; w < kRqThreads / 32; ++w) mx = fmaxf(mx, s_red[w]);
+      const float sc = __fdiv_rn(fmaxf(mx, 1e-8f), 127.0f);
+      s_scale = sc;
+      scales[row] = sc;
+    }
+    __syncthreads();
+    const float sc = fmaxf(s_scale, 1e-8f);
+    for (int i = tid; i < k; i += kRqThreads) {
+      const float q = fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), -128.f), 127.f);
+      codes[(size_t)row * k + i] = (int8_t)(int)q;
+    }
+  } else {
+    __syncthreads();
+    const int groups = k / group;
+    for (int gi = tid; gi < groups; gi += kRqThreads) {
+      float mx = 0.f;
+      for (int e = 0; e < group; ++e) mx = fmaxf(mx, fabsf(v[gi * group + e]));
+      const float sc = fmaxf(__fdiv_rn(mx, 7.0f), 1e-6f);
+      scales[(size_t)row * groups + gi] = sc;
+      for (int e = 0; e < group; ++e) {
+        const float q = fminf(fmaxf(rintf(__fdiv_rn(v[gi * group + e], sc)), -8.f), 7.f);
+        codes[(size_t)row * k + gi * group + e] = (int8_t)(int)q;
+      }
+    }
+  }
+}
+
+int rotate_quant_launch(const void* x, const float* column_scale, void* codes, float* scales, void* x_rot, int m, int k,
+                        int rot_kind, int rot_block, int mode, int group, int act_dtype, cudaStream_t stream) {
+  XQT_REQUIRE(m > 0 && k > 0 && (mode == 8 || mode == 4));
+  XQT_REQUIRE(rot_kind >= 0 && rot_kind <= 2);
+  if (rot_kind != 0) {
+    XQT_REQUIRE(rot_block >= 1 && k % rot_block == 0 && column_scale != nullptr);
+    int v = rot_block;
+    const int base = rot_kind == 1 ? 4 : 2;
+    while (v % base == 0) v /= base;
+    XQT_REQUIRE(v == 1);
+  }
+  if (mode == 4) XQT_REQUIRE(group > 0 && k % group == 0);
+  XQT_REQUIRE(act_dtype == XQT_B200_BF16 || act_dtype == XQT_B200_FP16);
+  const size_t smem = (size_t)k * sizeof(float);
+  XQT_REQUIRE(smem <= 200 * 1024);
+#define XQT_RQ(TT)                                                                                               \
+  do {                                                                                                           \
+    auto kern = rotate_quant_kernel<TT>;                                                                         \
+    static bool configured = false;                                                                              \
+    if (!configured) {                                                                                           \
+      XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));             \
+      configured = true;                                                                                         \
+    }                                                                                                            \
+    kern<<<m, kRqThreads, smem, stream>>>((const TT*)x, column_scale, (int8_t*)codes, scales, (TT*)x_rot, k,     \
+                                          rot_kind, rot_block, mode, group);                                     \
+  } while (0)
+  if (act_dtype == XQT_B200_BF16) XQT_RQ(__nv_bfloat16);
+  else XQT_RQ(__half);
+#undef XQT_RQ
+  return launch_status();
+}
+
+}  // namespace xqt_b200

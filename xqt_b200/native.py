@@ -37,6 +37,12 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_workspace_bytes": (_Z, [_I, _I, _I]),
     "xqt_b200_w4a16_select_variant": (_I, [_I] * 7),
     "xqt_b200_w4a16_run": (_I, [_P] * 7 + [_I] * 9 + [_P, _Z, _I, _P]),
+    "xqt_b200_w4a16_decode_workspace_bytes": (_Z, []),
+    "xqt_b200_w4a16_decode_supported": (_I, [_I] * 4),
+    "xqt_b200_w4a16_decode_tiled": (_I, [_P] * 6 + [_I] * 8 + [_P, _Z, _P]),
+    "xqt_b200_rotate_quantize": (_I, [_P] * 5 + [_I] * 7 + [_P]),
+    "xqt_b200_w8a8_gemm": (_I, [_P] * 6 + [_I] * 4 + [_P, _Z, _P]),
+    "xqt_b200_workspace_status": (_I, [_P, ctypes.POINTER(ctypes.c_uint), _P]),
 }
 
 _lock = threading.Lock()
@@ -117,7 +123,20 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return buffer
 
 
+def workspace_status(device: torch.device) -> int:
+    """Status word of the current stream's scratch buffer (0 = every bounded wait completed)."""
+
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    buffer = _workspaces.get((index, stream_handle(device)))
+    if buffer is None:
+        return 0
+    value = ctypes.c_uint(0)
+    check(library().xqt_b200_workspace_status(buffer.data_ptr(), ctypes.byref(value), stream_handle(device)),
+          "xqt_b200_workspace_status")
+    return int(value.value)
+
+
 __all__ = [
     "ACT", "BF16", "DTYPE_CODE", "FP16", "FP32", "LIBRARY_PATH", "SIGNATURES", "VARIANT", "VARIANT_NAMES",
-    "available", "check", "library", "ptr", "stream_handle", "version", "workspace",
+    "available", "check", "library", "ptr", "stream_handle", "version", "workspace", "workspace_status",
 ]

@@ -1,0 +1,53 @@
+"""Activation prologue: rotation + dynamic quantisation (one C-ABI call)."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import native
+from ..errors import XQTBackendError
+from ..quantize import Rotation
+
+_KIND = {None: 0, "regular": 1, "sylvester": 2}
+_scale_cache: dict[tuple, torch.Tensor] = {}
+
+
+def _column_scale(rotation: Rotation, device: torch.device) -> torch.Tensor:
+    key = (rotation.kind, rotation.block, None if rotation.signs is None else tuple(rotation.signs.tolist()), str(device))
+    cached = _scale_cache.get(key)
+    if cached is None:
+        cached = rotation.column_scale.to(device).contiguous()
+        _scale_cache[key] = cached
+    return cached
+
+
+def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, group_size: int = 64,
+                    return_rotated: bool = False):
+    """-> (codes int8 ``[M,K]``, scales fp32 ``[M]`` (bits=8) or ``[M, K/group]`` (bits=4)[, rotated x])."""
+
+    if x.ndim != 2 or x.dtype not in (torch.float16, torch.bfloat16) or not x.is_cuda:
+        raise XQTBackendError("rotate_quantize expects a CUDA rank-2 fp16/bf16 activation")
+    if bits not in (4, 8):
+        raise XQTBackendError("rotate_quantize supports 8-bit per-token or 4-bit per-group codes")
+    x = x.contiguous()
+    m, k = int(x.shape[0]), int(x.shape[1])
+    device = x.device
+    if rotation is not None and k % rotation.block:
+        raise XQTBackendError("the rotated dimension must be a multiple of the rotation block")
+    if bits == 4 and k % group_size:
+        raise XQTBackendError("K must be a multiple of the activation group size")
+    codes = torch.empty((m, k), device=device, dtype=torch.int8)
+    scales = torch.empty((m,) if bits == 8 else (m, k // group_size), device=device, dtype=torch.float32)
+    rotated = torch.empty_like(x) if return_rotated else None
+    if m:
+        cs = None if rotation is None else _column_scale(rotation, device)
+        with torch.cuda.device(device):
+            code = native.library().xqt_b200_rotate_quantize(
+                x.data_ptr(), native.ptr(cs), codes.data_ptr(), scales.data_ptr(), native.ptr(rotated), m, k,
+                _KIND[None if rotation is None else rotation.kind], 0 if rotation is None else rotation.block,
+                bits, int(group_size), native.DTYPE_CODE[x.dtype], native.stream_handle(device))
+        native.check(code, "xqt_b200_rotate_quantize")
+    return (codes, scales, rotated) if return_rotated else (codes, scales)
+
+
+__all__ = ["rotate_quantize"]

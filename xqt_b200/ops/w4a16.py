@@ -13,8 +13,6 @@ import torch
 from .. import native
 from ..errors import XQTBackendError
 
-_GEMV_MAX_M = 16
-
 
 def _check_cuda(name: str, tensor: torch.Tensor | None, device: torch.device) -> None:
     if tensor is None:
@@ -90,22 +88,127 @@ def w4a16_linear(
     stream = native.stream_handle(device)
     act_code, param_code = native.DTYPE_CODE[x.dtype], native.DTYPE_CODE[scales.dtype]
 
-    def run(xs, res, dst, rows, which):
-        code = lib.xqt_b200_w4a16_run(
-            xs.data_ptr(), qweight.data_ptr(), scales.data_ptr(), native.ptr(zero_points), native.ptr(bias),
-            native.ptr(res), dst.data_ptr(), rows, n, k, padded_k, int(group_size), int(bool(nibble_signed)),
-            act_code, param_code, native.ACT[activation], scratch.data_ptr(), scratch.numel(),
-            native.VARIANT[which], stream)
-        native.check(code, "xqt_b200_w4a16_run")
-
     with torch.cuda.device(device):
-        run(x, residual, out, m, variant)
+        code = lib.xqt_b200_w4a16_run(
+            x.data_ptr(), qweight.data_ptr(), scales.data_ptr(), native.ptr(zero_points), native.ptr(bias),
+            native.ptr(residual), out.data_ptr(), m, n, k, padded_k, int(group_size), int(bool(nibble_signed)),
+            act_code, param_code, native.ACT[activation], scratch.data_ptr(), scratch.numel(),
+            native.VARIANT[variant], stream)
+    native.check(code, "xqt_b200_w4a16_run")
     return out
 
 
-def _fake(x, qweight, scales, zero_points=None, bias=None, residual=None, *, group_size, nibble_signed,
-          k=None, activation="none", variant="auto", out=None):
-    return x.new_empty((x.shape[0], qweight.shape[0]))
+def bind_w4a16_linear(
+    qweight: torch.Tensor,
+    scales: torch.Tensor,
+    zero_points: torch.Tensor | None = None,
+    *,
+    rows: int,
+    dtype: torch.dtype,
+    group_size: int,
+    nibble_signed: bool,
+    k: int | None = None,
+    bias: torch.Tensor | None = None,
+    variant: str = "auto",
+):
+    """Validate the static tensors once and return ``run(x, out=None) -> Tensor`` for a fixed
+    row count, the way ``bind_awq_w4a16_decode`` does for the sm_89 decode kernel
+    (xqt/kernels/ops/_impl/cuda/awq_w4a16_sm89.py:217-302): the closure only checks the
+    activation and makes one C-ABI call.  The scratch buffer is the one of the stream that is
+    current when the closure runs for the first time."""
+
+    device = qweight.device
+    probe = torch.empty((rows, int(qweight.shape[1]) * 2 if k is None else int(k)), device=device, dtype=dtype)
+    w4a16_linear(probe[:0], qweight, scales, zero_points, bias, None, group_size=group_size,
+                 nibble_signed=nibble_signed, k=k, variant=variant)          # argument validation only
+    n, padded_k = int(qweight.shape[0]), int(qweight.shape[1]) * 2
+    kk = padded_k if k is None else int(k)
+    lib = native.library()
+    fn = lib.xqt_b200_w4a16_run
+    bias32 = None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous()
+    nbytes = lib.xqt_b200_w4a16_workspace_bytes(rows, n, kk)
+    static = (qweight.data_ptr(), scales.data_ptr(), native.ptr(zero_points), native.ptr(bias32), 0)
+    tail = (rows, n, kk, padded_k, int(group_size), int(bool(nibble_signed)), native.DTYPE_CODE[dtype],
+            native.DTYPE_CODE[scales.dtype], 0)
+    variant_code = native.VARIANT[variant]
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    keep = (qweight, scales, zero_points, bias32)  # noqa: F841 - the closure owns references
+
+    def run(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        if x.dtype != dtype or x.ndim != 2 or x.shape[0] != rows or x.shape[1] != kk or not x.is_contiguous() \
+                or x.device != device:
+            raise XQTBackendError("bound B200 W4A16 call: activation shape, dtype, device or layout mismatch")
+        if torch.cuda.current_device() != index:
+            raise XQTBackendError("bound B200 W4A16 call: make the weight's device current before calling")
+        if out is None:
+            out = torch.empty((rows, n), device=device, dtype=dtype)
+        scratch = native.workspace(device, nbytes)
+        code = fn(x.data_ptr(), *static, out.data_ptr(), *tail, scratch.data_ptr(), scratch.numel(),
+                  variant_code, torch.cuda.current_stream(device).cuda_stream)
+        if code != 0:
+            native.check(code, "xqt_b200_w4a16_run")
+        return out
+
+    return run
+
+
+def decode_supported(m: int, n: int, k: int, group_size: int) -> bool:
+    return bool(native.library().xqt_b200_w4a16_decode_supported(int(m), int(n), int(k), int(group_size)))
+
+
+def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None = None):
+    """Hot-callable for the decode kernel on a :class:`xqt_b200.prepack.TiledW4` layer:
+    ``run(x, out=None, residual=None) -> Tensor`` for a fixed row count (1..16).  Static tensors are
+    validated here, once; each call checks the activation and makes one C-ABI call
+    (cf. ``bind_awq_w4a16_decode``, xqt/kernels/ops/_impl/cuda/awq_w4a16_sm89.py:217-302)."""
+
+    device = tiled.weights.device
+    if device.type != "cuda":
+        raise XQTBackendError("B200 W4A16 decode needs the tiled layer on a CUDA device")
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise XQTBackendError("B200 W4A16 decode supports fp16 or bf16 activations")
+    n, k = tiled.n, tiled.k
+    if not decode_supported(rows, n, k, tiled.group_size):
+        raise XQTBackendError(f"B200 W4A16 decode does not cover M={rows}, N={n}, K={k}, group={tiled.group_size}")
+    if tiled.params.dtype not in native.DTYPE_CODE or not tiled.weights.is_contiguous() or not tiled.params.is_contiguous():
+        raise XQTBackendError("B200 W4A16 decode: tiled tensors must be contiguous, params fp16/bf16/fp32")
+    lib = native.library()
+    fn = lib.xqt_b200_w4a16_decode_tiled
+    bias32 = None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous()
+    if bias32 is not None and bias32.numel() != n:
+        raise XQTBackendError("B200 W4A16 bias must have N elements")
+    nbytes = lib.xqt_b200_w4a16_decode_workspace_bytes()
+    head = (tiled.weights.data_ptr(), tiled.params.data_ptr(), native.ptr(bias32))
+    tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), int(tiled.has_zero_point),
+            native.DTYPE_CODE[dtype], native.DTYPE_CODE[tiled.params.dtype])
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    keep = (tiled, bias32)  # noqa: F841 - the closure owns references
+
+    def run(x: torch.Tensor, out: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
+        if x.dtype != dtype or x.ndim != 2 or x.shape[0] != rows or x.shape[1] != k or not x.is_contiguous() \
+                or x.device != device:
+            raise XQTBackendError("bound B200 W4A16 decode: activation shape, dtype, device or layout mismatch")
+        if torch.cuda.current_device() != index:
+            raise XQTBackendError("bound B200 W4A16 decode: make the weight's device current before calling")
+        if out is None:
+            out = torch.empty((rows, n), device=device, dtype=dtype)
+        if residual is not None and (residual.dtype != dtype or tuple(residual.shape) != (rows, n)
+                                     or not residual.is_contiguous()):
+            raise XQTBackendError("bound B200 W4A16 decode: residual must be contiguous [M,N] in the activation dtype")
+        scratch = native.workspace(device, nbytes)
+        code = fn(x.data_ptr(), *head, native.ptr(residual), out.data_ptr(), *tail, scratch.data_ptr(),
+                  scratch.numel(), torch.cuda.current_stream(device).cuda_stream)
+        if code != 0:
+            native.check(code, "xqt_b200_w4a16_decode_tiled")
+        return out
+
+    return run
+
+
+def w4a16_decode_tiled(x: torch.Tensor, tiled, bias=None, residual=None, out=None) -> torch.Tensor:
+    """One-shot form of :func:`bind_w4a16_decode`."""
+
+    return bind_w4a16_decode(tiled, rows=int(x.shape[0]), dtype=x.dtype, bias=bias)(x, out, residual)
 
 
 def _register() -> None:
@@ -134,4 +237,5 @@ def _custom_op_fake(x, qweight, scales, zero_points, bias, residual, group_size,
 
 _register()
 
-__all__ = ["select_variant", "w4a16_linear"]
+__all__ = ["bind_w4a16_decode", "bind_w4a16_linear", "decode_supported", "select_variant", "w4a16_decode_tiled",
+           "w4a16_linear"]
