@@ -113,6 +113,34 @@ int xqt_b200_w4a16_decode_tiled(const void* activation, const void* tiled_weight
                                 int param_dtype, void* workspace, size_t workspace_bytes,
                                 xqt_b200_stream_t stream);
 
+/* W4A16 decode with the scratch built into the library: same operation, arguments and result as
+ * xqt_b200_w4a16_decode_tiled, minus the workspace pair.  It has no counterpart in the reference.
+ *
+ * Who it is for: code that may launch kernels but must not allocate device memory at the point
+ * of the call -- an inference server whose memory pool was handed out in full at start-up, a
+ * plugin running inside a host application that owns the allocator, a real-time loop that
+ * forbids allocator calls (they can synchronise the device or fail late).  Such callers pass
+ * their pre-existing input and output buffers and nothing else.
+ *
+ * How: the tickets, partial sums and status word live in a file-scope __device__ array of
+ * xqt_b200_w4a16_decode_static_scratch_bytes() bytes (about 2.6 MB) that every GPU using the
+ * library holds until the process exits.  The entry point calls no cudaMalloc / cudaFree and no
+ * allocating library routine; it enqueues one memset of its tickets and the kernel.
+ *   - Limit: N <= xqt_b200_w4a16_decode_static_max_n() (131072); beyond it the call returns
+ *     cudaErrorInvalidValue and launches nothing.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current) and caches it; make that first call before any stream capture begins.
+ *   - All calls on a device share the one array: two calls that can overlap on the GPU (different
+ *     streams without an ordering between them) race on it.  Serialise them.
+ */
+int xqt_b200_w4a16_decode_tiled_static(const void* activation, const void* tiled_weights,
+                                       const void* tiled_params, const float* bias,
+                                       const void* residual, void* output, int m, int n, int k,
+                                       int group_size, int nibble_signed, int has_zero_point,
+                                       int act_dtype, int param_dtype, xqt_b200_stream_t stream);
+size_t xqt_b200_w4a16_decode_static_scratch_bytes(void);
+int xqt_b200_w4a16_decode_static_max_n(void);
+
 /* ------------------------------------------------------------------------------------------
  * Activation prologue shared by the W8A8 and W4A4 linears: block-diagonal Hadamard rotation,
  * one rounding to the activation dtype, dynamic symmetric quantisation.

@@ -458,4 +458,83 @@ int w4a16_decode_launch(const void* x, const void* wt, const void* sz, const flo
   return decode_launch_tp<__half, float>(p, gp, (int)grid, smem_bytes, sg, zp, stream);
 }
 
+// ------------------------------------------------------------------------- allocation-free variant
+//
+// Scratch for callers that cannot allocate device memory (see xqt_b200_w4a16_decode_tiled_static in
+// include/xqt_b200.h).  The array lives in the library image: every GPU that loads the library holds
+// these bytes until the process exits.  Layout: status word @0, tickets @256, partials after them.
+namespace decode_static {
+constexpr int kMaxTiles = 1024;   // N <= 131072 output channels
+constexpr int kMaxGrid = 160;     // CTAs (a B200 has 148 SMs)
+constexpr size_t kTicketBytes = (size_t)kMaxTiles * sizeof(unsigned int);
+constexpr size_t kBytes = 256 + kTicketBytes + (size_t)kMaxGrid * 2 * decode::kPartialFloats * sizeof(float);
+}  // namespace decode_static
+
+static __device__ __align__(256) unsigned char g_decode_static_scratch[decode_static::kBytes];
+
+// In host code the array's name is only a stand-in for the symbol, not a device address: the
+// address is asked for once per device, with that device current, and cached.
+static int decode_static_scratch(unsigned char** out) {
+  static unsigned char* cache[64] = {nullptr};
+  int dev = 0;
+  XQT_CUDA(cudaGetDevice(&dev));
+  XQT_REQUIRE(dev >= 0 && dev < 64);
+  if (cache[dev] == nullptr) {
+    void* ptr = nullptr;
+    XQT_CUDA(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+    cache[dev] = reinterpret_cast<unsigned char*>(ptr);
+  }
+  *out = cache[dev];
+  return 0;
+}
+
+size_t w4a16_decode_static_scratch_bytes() { return decode_static::kBytes; }
+int w4a16_decode_static_max_n() { return decode_static::kMaxTiles * decode::kTileRows; }
+
+int w4a16_decode_launch_static(const void* x, const void* wt, const void* sz, const float* bias, const void* residual,
+                               void* out, int m, int n, int k, int group_size, int nibble_signed, int has_zp,
+                               int act_dtype, int param_dtype, cudaStream_t stream) {
+  using namespace decode;
+  XQT_REQUIRE(w4a16_decode_supported(m, n, k, group_size));
+  XQT_REQUIRE(ceil_div(n, kTileRows) <= decode_static::kMaxTiles);   // beyond the scratch built into the library
+  XQT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)wt & 15) == 0 && ((uintptr_t)sz & 15) == 0);
+  unsigned char* ws = nullptr;
+  {
+    const int rc = decode_static_scratch(&ws);
+    if (rc != 0) return rc;
+  }
+  const int gp = kKBlock / group_size;
+  const int psize = param_dtype == XQT_B200_FP32 ? 4 : 2;
+  DecodeParams p;
+  p.x = x; p.wt = (const uint8_t*)wt; p.sz = (const uint8_t*)sz; p.bias = bias; p.residual = residual; p.out = out;
+  p.m = m; p.n = n; p.k = k;
+  p.tiles = ceil_div(n, kTileRows);
+  p.spt = k / kStageK;
+  p.total = (long long)p.tiles * p.spt;
+  p.sz_stage_bytes = kKS * gp * kTileRows * 2 * psize;
+  p.stage_bytes = (kWBytes + kXBytes + p.sz_stage_bytes + 127) / 128 * 128;
+  int ns = (kSmemBudget - kRedBytes) / p.stage_bytes;
+  p.nstages = ns > kMaxStages ? kMaxStages : ns;
+  XQT_REQUIRE(p.nstages >= 2);
+  p.status = reinterpret_cast<unsigned int*>(ws);
+  p.tickets = reinterpret_cast<unsigned int*>(ws + 256);
+  p.partials = reinterpret_cast<float*>(ws + 256 + decode_static::kTicketBytes);
+  // Every call shares the array and finds what the last one left: the tickets and the status word
+  // must start at zero (a memset on the stream allocates nothing); partials are overwritten before use.
+  XQT_CUDA(cudaMemsetAsync(ws, 0, 256 + (size_t)p.tiles * sizeof(unsigned int), stream));
+  long long grid = decode_sm_count();
+  if (grid > decode_static::kMaxGrid) grid = decode_static::kMaxGrid;
+  if (grid > p.total) grid = p.total;
+  const size_t smem_bytes = (size_t)p.nstages * p.stage_bytes + kRedBytes;
+  const bool sg = nibble_signed != 0, zp = has_zp != 0;
+  if (act_dtype == XQT_B200_BF16) {
+    if (param_dtype == XQT_B200_BF16) return decode_launch_tp<__nv_bfloat16, __nv_bfloat16>(p, gp, (int)grid, smem_bytes, sg, zp, stream);
+    if (param_dtype == XQT_B200_FP16) return decode_launch_tp<__nv_bfloat16, __half>(p, gp, (int)grid, smem_bytes, sg, zp, stream);
+    return decode_launch_tp<__nv_bfloat16, float>(p, gp, (int)grid, smem_bytes, sg, zp, stream);
+  }
+  if (param_dtype == XQT_B200_BF16) return decode_launch_tp<__half, __nv_bfloat16>(p, gp, (int)grid, smem_bytes, sg, zp, stream);
+  if (param_dtype == XQT_B200_FP16) return decode_launch_tp<__half, __half>(p, gp, (int)grid, smem_bytes, sg, zp, stream);
+  return decode_launch_tp<__half, float>(p, gp, (int)grid, smem_bytes, sg, zp, stream);
+}
+
 }  // namespace xqt_b200

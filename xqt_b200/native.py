@@ -40,6 +40,9 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_decode_workspace_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_supported": (_I, [_I] * 4),
     "xqt_b200_w4a16_decode_tiled": (_I, [_P] * 6 + [_I] * 8 + [_P, _Z, _P]),
+    "xqt_b200_w4a16_decode_tiled_static": (_I, [_P] * 6 + [_I] * 8 + [_P]),
+    "xqt_b200_w4a16_decode_static_scratch_bytes": (_Z, []),
+    "xqt_b200_w4a16_decode_static_max_n": (_I, []),
     "xqt_b200_rotate_quantize": (_I, [_P] * 5 + [_I] * 7 + [_P]),
     "xqt_b200_w8a8_gemm": (_I, [_P] * 6 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_workspace_status": (_I, [_P, ctypes.POINTER(ctypes.c_uint), _P]),
