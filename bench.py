@@ -40,7 +40,7 @@ GROUP = 128
 METRIC = "w4a16_decode_gemv_weight_bandwidth"
 UNIT = "GB/s"
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_kernel launch from the committed
+# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_tc_kernel launch from the committed
 # ncu capture (profiles/), or None while no capture backs it
 NCU_TRAFFIC_BYTES_PER_LAUNCH = None
 
@@ -194,8 +194,7 @@ def run_gpu_arm(args) -> None:
     import torch.distributed as dist
 
     from xqt_b200.contracts import PackedWeight
-    from xqt_b200 import prepack
-    from xqt_b200.ops.w4a16 import bind_w4a16_decode
+    from xqt_b200.ops.w4a16 import bind_w4a16_decode, prepare_decode
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -228,7 +227,7 @@ def run_gpu_arm(args) -> None:
     for _ in range(pool):
         copy_layers = {}
         for key, pw in local_layers.items():
-            copy_layers[key] = prepack.tile_w4(
+            copy_layers[key] = prepare_decode(
                 pw.qweight.to(device), pw.scales.to(device), pw.zero_points.to(device), group_size=GROUP,
                 nibble_signed=False)
         dev_layers.append(copy_layers)
@@ -389,7 +388,7 @@ def run_gpu_arm(args) -> None:
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peak_kind}",
-            "kernel": "w4a16_decode_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank)",
+            "kernel": "w4a16_decode_tc_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank)",
         },
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -415,16 +414,15 @@ def run_gpu_arm(args) -> None:
 def run_single_problem(args) -> None:
     """One decode problem, `steps` eager launches over a weight pool larger than L2."""
 
-    from xqt_b200 import prepack
-    from xqt_b200.ops.w4a16 import bind_w4a16_decode
+    from xqt_b200.ops.w4a16 import bind_w4a16_decode, prepare_decode
 
     k, n, m = (int(v) for v in args.problem.split(","))
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     pw = make_layer(k, n, 10)
     pool = max(2, -(-2 * L2_BYTES // weight_aux_bytes(k, n)))
-    tiled = [prepack.tile_w4(pw.qweight.to(device).clone(), pw.scales.to(device), pw.zero_points.to(device),
-                             group_size=GROUP, nibble_signed=False) for _ in range(pool)]
+    tiled = [prepare_decode(pw.qweight.to(device).clone(), pw.scales.to(device), pw.zero_points.to(device),
+                            group_size=GROUP, nibble_signed=False) for _ in range(pool)]
     x = torch.randn((m, k), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(device)
     runs = [bind_w4a16_decode(t, rows=m, dtype=torch.bfloat16) for t in tiled]
     out = torch.empty((m, n), device=device, dtype=torch.bfloat16)

@@ -113,6 +113,19 @@ int xqt_b200_w4a16_decode_tiled(const void* activation, const void* tiled_weight
                                 int param_dtype, void* workspace, size_t workspace_bytes,
                                 xqt_b200_stream_t stream);
 
+/* W4A16 decode (M <= 16) on tcgen05, execution layout b200_w4_rows128_v1:
+ *   row_weights   uint8 [ceil(N/128)][K/128][4 chunks of 32 K][128 channels][16]   (prepack.py: rows_w4)
+ *   tiled_params  as above.  Zero points must be integers in [0, 119]; group_size in {64, 128};
+ *   K a multiple of 256.  Same replaced reference entry points, arithmetic, workspace and status
+ *   rules as xqt_b200_w4a16_decode_tiled; the inner product runs as tcgen05.mma with the
+ *   dequantised weights in tensor memory. */
+size_t xqt_b200_w4a16_decode_tc_workspace_bytes(void);
+int xqt_b200_w4a16_decode_tc_supported(int m, int n, int k, int group_size);
+int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, const void* tiled_params,
+                             const float* bias, const void* residual, void* output, int m, int n,
+                             int k, int group_size, int nibble_signed, int act_dtype, int param_dtype,
+                             void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream);
+
 /* W4A16 decode with the scratch built into the library: same operation, arguments and result as
  * xqt_b200_w4a16_decode_tiled, minus the workspace pair.  It has no counterpart in the reference.
  *

@@ -165,3 +165,49 @@ def test_decode_tiled_prepack_round_trip_on_device():
                             nibble_signed=False)
     q, s, z = prepack.untile_w4(tiled)
     assert torch.equal(q.cpu(), pw.qweight) and torch.equal(s.cpu(), pw.scales) and torch.equal(z.cpu(), pw.zero_points)
+
+
+# ---------------------------------------------------------------------------- tcgen05 decode kernel
+
+
+def _tc_run(x, pw, *, bias=None, residual=None):
+    from xqt_b200 import native, prepack
+    from xqt_b200.ops.w4a16 import w4a16_decode_tiled
+
+    dev = torch.device("cuda", 0)
+    mv = lambda t: None if t is None else t.to(dev)
+    tiled = prepack.rows_w4(mv(pw.qweight), mv(pw.scales), mv(pw.zero_points), group_size=pw.metadata.group_size,
+                            nibble_signed=pw.metadata.nibble_signed)
+    assert tiled.layout == "rows128" and tiled.integer_zero_points
+    out = w4a16_decode_tiled(mv(x), tiled, bias=mv(bias), residual=mv(residual))
+    torch.cuda.synchronize()
+    assert native.workspace_status(dev) == 0
+    return out.cpu()
+
+
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+@pytest.mark.parametrize("n,k", [(128, 256), (4096, 4096), (1024, 4096), (4096, 14336), (14336, 4096), (200, 512),
+                                 (72, 768)])
+def test_decode_tc_shapes(m, n, k):
+    if (n, k) in {(4096, 14336), (14336, 4096)} and m not in (1, 16):
+        pytest.skip("large shapes: first and last M only")
+    x, pw = _synthetic(n, k, m, seed=500 + m)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=False)
+    out = _tc_run(x, pw)
+    assert oracle.rel_l2(out, ref) <= TOL
+    assert torch.equal(out, _tc_run(x, pw))
+
+
+@pytest.mark.parametrize("group", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("symmetric", [False, True])
+def test_decode_tc_groups_dtypes_epilogue(group, dtype, symmetric):
+    n, k, m = 392, 1280, 13
+    x, pw = _synthetic(n, k, m, seed=60 + group, dtype=dtype, symmetric=symmetric, group=group,
+                       param_dtype=torch.float32 if group == 64 else torch.bfloat16)
+    bias = torch.randn((n,), generator=seeded(8))
+    residual = torch.randn((m, n), generator=seeded(9)).to(dtype)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=group, signed=symmetric, bias=bias,
+                      residual=residual)
+    out = _tc_run(x, pw, bias=bias, residual=residual)
+    assert oracle.rel_l2(out, ref) <= TOL

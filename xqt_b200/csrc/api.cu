@@ -16,6 +16,10 @@ int w4a16_decode_launch_static(const void*, const void*, const void*, const floa
                                int, int, int, int, int, cudaStream_t);
 size_t w4a16_decode_static_scratch_bytes();
 int w4a16_decode_static_max_n();
+int w4a16_decode_tc_launch(const void*, const void*, const void*, const float*, const void*, void*, int, int, int, int,
+                           int, int, int, void*, size_t, cudaStream_t);
+size_t w4a16_decode_tc_workspace_bytes();
+bool w4a16_decode_tc_supported(int m, int n, int k, int group_size);
 int rotate_quant_launch(const void*, const float*, void*, float*, void*, int, int, int, int, int, int, int, cudaStream_t);
 int gemm_i8_launch(const void*, const void*, const float*, const float*, const float*, void*, int, int, int, int,
                    unsigned int*, cudaStream_t);
@@ -98,6 +102,26 @@ int xqt_b200_w4a16_decode_tiled(const void* activation, const void* tiled_weight
   return w4a16_decode_launch(activation, tiled_weights, tiled_params, bias, residual, output, m, n, k, group_size,
                              nibble_signed, has_zero_point, act_dtype, param_dtype, workspace, workspace_bytes,
                              (cudaStream_t)stream);
+}
+
+size_t xqt_b200_w4a16_decode_tc_workspace_bytes(void) { return w4a16_decode_tc_workspace_bytes(); }
+
+int xqt_b200_w4a16_decode_tc_supported(int m, int n, int k, int group_size) {
+  return w4a16_decode_tc_supported(m, n, k, group_size) ? 1 : 0;
+}
+
+int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, const void* tiled_params,
+                             const float* bias, const void* residual, void* output, int m, int n, int k,
+                             int group_size, int nibble_signed, int act_dtype, int param_dtype, void* workspace,
+                             size_t workspace_bytes, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(m >= 0 && n > 0 && k > 0);
+  XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
+  XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
+  if (m == 0) return 0;
+  XQT_REQUIRE(activation != nullptr && row_weights != nullptr && tiled_params != nullptr && output != nullptr);
+  return w4a16_decode_tc_launch(activation, row_weights, tiled_params, bias, residual, output, m, n, k, group_size,
+                                nibble_signed, act_dtype, param_dtype, workspace, workspace_bytes,
+                                (cudaStream_t)stream);
 }
 
 int xqt_b200_w4a16_decode_tiled_static(const void* activation, const void* tiled_weights, const void* tiled_params,

@@ -19,7 +19,10 @@ import torch
 
 from .errors import CudaCallError, NativeLibraryError
 
-LIBRARY_PATH = pathlib.Path(__file__).resolve().parent / "libxqt_b200.so"
+import os
+
+# XQT_B200_LIBRARY points at an alternative build of the same ABI (e.g. an instrumented one)
+LIBRARY_PATH = pathlib.Path(os.environ.get("XQT_B200_LIBRARY") or pathlib.Path(__file__).resolve().parent / "libxqt_b200.so")
 
 FP16, BF16, FP32 = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
@@ -40,6 +43,9 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_decode_workspace_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_supported": (_I, [_I] * 4),
     "xqt_b200_w4a16_decode_tiled": (_I, [_P] * 6 + [_I] * 8 + [_P, _Z, _P]),
+    "xqt_b200_w4a16_decode_tc_workspace_bytes": (_Z, []),
+    "xqt_b200_w4a16_decode_tc_supported": (_I, [_I] * 4),
+    "xqt_b200_w4a16_decode_tc": (_I, [_P] * 6 + [_I] * 7 + [_P, _Z, _P]),
     "xqt_b200_w4a16_decode_tiled_static": (_I, [_P] * 6 + [_I] * 8 + [_P]),
     "xqt_b200_w4a16_decode_static_scratch_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_static_max_n": (_I, []),

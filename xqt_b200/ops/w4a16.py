@@ -168,19 +168,32 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
     if dtype not in (torch.float16, torch.bfloat16):
         raise XQTBackendError("B200 W4A16 decode supports fp16 or bf16 activations")
     n, k = tiled.n, tiled.k
-    if not decode_supported(rows, n, k, tiled.group_size):
+    lib = native.library()
+    use_tc = tiled.layout == "rows128"
+    if use_tc:
+        if not tiled.integer_zero_points:
+            raise XQTBackendError("the tcgen05 decode kernel needs integer zero points in [0, 119]")
+        supported = bool(lib.xqt_b200_w4a16_decode_tc_supported(rows, n, k, tiled.group_size))
+    else:
+        supported = decode_supported(rows, n, k, tiled.group_size)
+    if not supported:
         raise XQTBackendError(f"B200 W4A16 decode does not cover M={rows}, N={n}, K={k}, group={tiled.group_size}")
     if tiled.params.dtype not in native.DTYPE_CODE or not tiled.weights.is_contiguous() or not tiled.params.is_contiguous():
         raise XQTBackendError("B200 W4A16 decode: tiled tensors must be contiguous, params fp16/bf16/fp32")
-    lib = native.library()
-    fn = lib.xqt_b200_w4a16_decode_tiled
     bias32 = None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous()
     if bias32 is not None and bias32.numel() != n:
         raise XQTBackendError("B200 W4A16 bias must have N elements")
-    nbytes = lib.xqt_b200_w4a16_decode_workspace_bytes()
     head = (tiled.weights.data_ptr(), tiled.params.data_ptr(), native.ptr(bias32))
-    tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), int(tiled.has_zero_point),
-            native.DTYPE_CODE[dtype], native.DTYPE_CODE[tiled.params.dtype])
+    if use_tc:
+        fn, symbol = lib.xqt_b200_w4a16_decode_tc, "xqt_b200_w4a16_decode_tc"
+        nbytes = lib.xqt_b200_w4a16_decode_tc_workspace_bytes()
+        tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), native.DTYPE_CODE[dtype],
+                native.DTYPE_CODE[tiled.params.dtype])
+    else:
+        fn, symbol = lib.xqt_b200_w4a16_decode_tiled, "xqt_b200_w4a16_decode_tiled"
+        nbytes = lib.xqt_b200_w4a16_decode_workspace_bytes()
+        tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), int(tiled.has_zero_point),
+                native.DTYPE_CODE[dtype], native.DTYPE_CODE[tiled.params.dtype])
     index = device.index if device.index is not None else torch.cuda.current_device()
     keep = (tiled, bias32)  # noqa: F841 - the closure owns references
 
@@ -199,10 +212,24 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
         code = fn(x.data_ptr(), *head, native.ptr(residual), out.data_ptr(), *tail, scratch.data_ptr(),
                   scratch.numel(), torch.cuda.current_stream(device).cuda_stream)
         if code != 0:
-            native.check(code, "xqt_b200_w4a16_decode_tiled")
+            native.check(code, symbol)
         return out
 
     return run
+
+
+def prepare_decode(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tensor | None, *,
+                   group_size: int, nibble_signed: bool, k: int | None = None):
+    """Build the decode execution layout of a canonical W4 layer: the tcgen05 layout when the
+    layer qualifies (group 64/128, integer zero points), else the mma.sync layout."""
+
+    from .. import prepack
+
+    if group_size in (64, 128):
+        tiled = prepack.rows_w4(qweight, scales, zero_points, group_size=group_size, nibble_signed=nibble_signed, k=k)
+        if tiled.integer_zero_points:
+            return tiled
+    return prepack.tile_w4(qweight, scales, zero_points, group_size=group_size, nibble_signed=nibble_signed, k=k)
 
 
 def w4a16_decode_tiled(x: torch.Tensor, tiled, bias=None, residual=None, out=None) -> torch.Tensor:
@@ -237,5 +264,6 @@ def _custom_op_fake(x, qweight, scales, zero_points, bias, residual, group_size,
 
 _register()
 
-__all__ = ["bind_w4a16_decode", "bind_w4a16_linear", "decode_supported", "select_variant", "w4a16_decode_tiled",
+__all__ = ["bind_w4a16_decode", "bind_w4a16_linear", "decode_supported", "prepare_decode", "select_variant",
+           "w4a16_decode_tiled",
            "w4a16_linear"]

@@ -32,7 +32,12 @@ _NIBBLE_E = (0, 2, 4, 6, 1, 3, 5, 7)
 
 @dataclass(frozen=True)
 class TiledW4:
-    """Decode execution layout of one W4 layer (see module docstring)."""
+    """Decode execution layout of one W4 layer (see module docstring).
+
+    ``layout`` is ``"tile128"`` (weights ``[tiles, kblocks, 16, 32, 16]``, lane-major, for the
+    mma.sync decode kernel) or ``"rows128"`` (weights ``[tiles, kblocks, 4, 128, 16]``, one 16-byte
+    chunk of 32 K per channel, for the tcgen05 decode kernel whose threads each own a channel).
+    """
 
     weights: torch.Tensor      # uint8 [tiles, kblocks, 16, 32, 16]
     params: torch.Tensor       # [tiles, kblocks, 128/group, 128, 2]
@@ -41,6 +46,8 @@ class TiledW4:
     group_size: int
     nibble_signed: bool
     has_zero_point: bool
+    layout: str = "tile128"
+    integer_zero_points: bool = True
 
     @property
     def tiles(self) -> int:
@@ -90,11 +97,39 @@ def tile_w4(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tens
                    nibble_signed=bool(nibble_signed), has_zero_point=zero_points is not None)
 
 
+def rows_w4(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tensor | None, *,
+            group_size: int, nibble_signed: bool, k: int | None = None) -> TiledW4:
+    """canonical tensors -> ``b200_w4_rows128_v1``: weights ``[tile][kblock][chunk][channel][16 B]``.
+
+    Chunk ``c`` of channel ``r`` holds ``k = 128*kblock + 32*c .. +31``; inside each 32-bit word the
+    nibble positions carry ``e = 0,2,4,6,1,3,5,7`` (as in ``tile_w4``), so the pair extracted by
+    ``(word >> 4i) & 0x000f000f`` is one 32-bit tensor-memory column of the tcgen05 A operand.
+    """
+
+    base = tile_w4(qweight, scales, zero_points, group_size=group_size, nibble_signed=nibble_signed, k=k)
+    tiles, kblocks = base.tiles, base.k // KBLOCK
+    # tile128 lane order is [ntile j][g][t] with words w; word w of lane (g,t) covers k = 32w + 8t + e.
+    w = base.weights.reshape(tiles, kblocks, 16, 8, 4, 4, 4)          # [tile, kb, j, g, t, w, byte]
+    # rows layout wants, per channel (8j+g), chunk c = 32-K run, inside it word index = t' (8-K runs in order)
+    w = w.permute(0, 1, 5, 2, 3, 4, 6)                                 # [tile, kb, w(=chunk), j, g, t(=word), byte]
+    weights = w.reshape(tiles, kblocks, 4, TILE_ROWS, 16).contiguous()
+    integer = True
+    if zero_points is not None:
+        z = zero_points.to(torch.float32)
+        integer = bool((z == z.round()).all()) and bool((z >= 0).all()) and bool((z <= 119).all())
+    return TiledW4(weights=weights, params=base.params, n=base.n, k=base.k, group_size=base.group_size,
+                   nibble_signed=base.nibble_signed, has_zero_point=base.has_zero_point, layout="rows128",
+                   integer_zero_points=integer)
+
+
 def untile_w4(tiled: TiledW4) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
     """Inverse of :func:`tile_w4` (used by the round-trip test and by checkpoint export)."""
 
     tiles, kblocks = tiled.tiles, tiled.k // KBLOCK
-    w = tiled.weights.reshape(tiles, kblocks, 16, 8, 4, 4, 4)     # [tile, kblock, ntile, g, t, w, byte]
+    weights = tiled.weights
+    if tiled.layout == "rows128":
+        weights = weights.reshape(tiles, kblocks, 4, 16, 8, 4, 4).permute(0, 1, 3, 4, 5, 2, 6)
+    w = weights.reshape(tiles, kblocks, 16, 8, 4, 4, 4)           # [tile, kblock, ntile, g, t, w, byte]
     w = w.permute(0, 2, 3, 1, 5, 4, 6)                            # [tile, ntile, g, kblock, w, t, byte]
     nib = torch.stack((w & 0x0F, w >> 4), dim=-1).reshape(*w.shape[:-1], 8)   # nibble positions 0..7
     inverse = [list(_NIBBLE_E).index(e) for e in range(8)]
@@ -106,4 +141,4 @@ def untile_w4(tiled: TiledW4) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor 
     return qweight, scales, zeros
 
 
-__all__ = ["KBLOCK", "TILE_ROWS", "TiledW4", "tile_w4", "untile_w4"]
+__all__ = ["KBLOCK", "TILE_ROWS", "TiledW4", "rows_w4", "tile_w4", "untile_w4"]
