@@ -40,7 +40,9 @@ typedef struct CUstream_st* xqt_b200_stream_t; /* == cudaStream_t */
 #define XQT_B200_VARIANT_AUTO 0
 #define XQT_B200_VARIANT_SIMT 1     /* generic CUDA-core kernel: any shape, any group size        */
 #define XQT_B200_VARIANT_GEMV 2     /* M <= 16: split-K tensor-core GEMV, HBM-bound                */
-#define XQT_B200_VARIANT_TCGEN05 3  /* M > 16: TMA + tcgen05.mma with TMEM accumulators            */
+#define XQT_B200_VARIANT_TCGEN05 3  /* M > 16: TMA + tcgen05.mma with TMEM accumulators; needs group  */
+                                    /* size 64/128, K % 64 == 0, N % 8 == 0 and INTEGER zero points   */
+                                    /* (AUTO picks it only when zero_points is NULL)                  */
 
 /* Replaces xqt_w4a16_sm89_version / xqt_awq_w4a16_sm89_version
  * (w4a16_sm89.cu:519-521, awq_w4a16_sm89_kernel.cu:909-911). */

@@ -211,3 +211,42 @@ def test_decode_tc_groups_dtypes_epilogue(group, dtype, symmetric):
                       residual=residual)
     out = _tc_run(x, pw, bias=bias, residual=residual)
     assert oracle.rel_l2(out, ref) <= TOL
+
+
+# ---------------------------------------------------------------------------- tcgen05 GEMM (M > 16)
+
+
+@pytest.mark.parametrize("m,n,k", [(17, 128, 128), (128, 256, 256), (300, 392, 1280), (512, 4096, 4096),
+                                   (1000, 14336, 4096), (4096, 4096, 14336)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_tcgen05_shapes(m, n, k, dtype):
+    if m >= 1000 and dtype == torch.float16:
+        pytest.skip("large shapes in bf16 only")
+    x, pw = _synthetic(n, k, m, seed=700 + m, dtype=dtype)
+    assert select_variant(m, n, k, k, 128) == "tcgen05"
+    out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=128, signed=False)      # auto -> tcgen05
+    torch.set_num_threads(16)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=False)
+    assert oracle.rel_l2(out, ref) <= TOL
+
+
+@pytest.mark.parametrize("group,symmetric", [(64, False), (64, True), (128, True)])
+def test_gemm_tcgen05_groups_signed_epilogue(group, symmetric):
+    m, n, k = 200, 264, 768
+    x, pw = _synthetic(n, k, m, seed=33, symmetric=symmetric, group=group, param_dtype=torch.float32)
+    bias = torch.randn((n,), generator=seeded(8))
+    residual = torch.randn((m, n), generator=seeded(9)).to(torch.bfloat16)
+    out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=group, signed=symmetric, bias=bias,
+               residual=residual, variant="tcgen05")
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=group, signed=symmetric, bias=bias,
+                      residual=residual)
+    assert oracle.rel_l2(out, ref) <= TOL
+
+
+def test_gemm_non_integer_zero_points_take_the_exact_path():
+    m, n, k = 64, 128, 256
+    x, pw = _synthetic(n, k, m, seed=44, param_dtype=torch.float32)
+    zeros = pw.zero_points + 0.25
+    out = _run(x, pw.qweight, pw.scales, zeros, group=128, signed=False)     # auto must not pick tcgen05
+    ref = oracle.gemm(x, pw.qweight, pw.scales, zeros, group_size=128, signed=False)
+    assert oracle.rel_l2(out, ref) <= TOL

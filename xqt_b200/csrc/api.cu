@@ -20,6 +20,10 @@ int w4a16_decode_tc_launch(const void*, const void*, const void*, const float*, 
                            int, int, int, void*, size_t, cudaStream_t);
 size_t w4a16_decode_tc_workspace_bytes();
 bool w4a16_decode_tc_supported(int m, int n, int k, int group_size);
+int w4a16_gemm_tc_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int,
+                         int, int, int, int, int, void*, size_t, cudaStream_t);
+size_t w4a16_gemm_tc_workspace_bytes(int m, int k);
+bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size);
 int rotate_quant_launch(const void*, const float*, void*, float*, void*, int, int, int, int, int, int, int, cudaStream_t);
 int gemm_i8_launch(const void*, const void*, const float*, const float*, const float*, void*, int, int, int, int,
                    unsigned int*, cudaStream_t);
@@ -41,9 +45,10 @@ int xqt_b200_device_supported(int device) {
 }
 
 size_t xqt_b200_w4a16_workspace_bytes(int m, int n, int k) {
-  (void)m;
   if (n <= 0 || k <= 0) return 0;
-  return w4a16_gemv_workspace_bytes(n, k);
+  const size_t a = w4a16_gemv_workspace_bytes(n, k);
+  const size_t b = m > 16 ? w4a16_gemm_tc_workspace_bytes(m, k) : 0;   // fp16 copy of bf16 activations
+  return a > b ? a : b;
 }
 
 int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_size, int epilogue_activation,
@@ -51,6 +56,8 @@ int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_s
   (void)has_residual;
   if (epilogue_activation == XQT_B200_ACT_NONE && w4a16_gemv_supported(m, n, k, padded_k, group_size))
     return XQT_B200_VARIANT_GEMV;
+  if (epilogue_activation == XQT_B200_ACT_NONE && m > 16 && w4a16_gemm_tc_supported(m, n, k, padded_k, group_size))
+    return XQT_B200_VARIANT_TCGEN05;
   return XQT_B200_VARIANT_SIMT;
 }
 
@@ -66,8 +73,12 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
   XQT_REQUIRE(epilogue_activation >= XQT_B200_ACT_NONE && epilogue_activation <= XQT_B200_ACT_SILU);
   if (m == 0) return 0;
   XQT_REQUIRE(activation != nullptr && qweight != nullptr && scales != nullptr && output != nullptr);
-  if (variant == XQT_B200_VARIANT_AUTO)
+  if (variant == XQT_B200_VARIANT_AUTO) {
     variant = xqt_b200_w4a16_select_variant(m, n, k, padded_k, group_size, epilogue_activation, residual != nullptr);
+    // the tensor-core GEMM folds the zero point into an exact integer subtraction: only a caller who
+    // knows its zero points are integers may ask for it; AUTO takes it for symmetric weights only
+    if (variant == XQT_B200_VARIANT_TCGEN05 && zero_points != nullptr) variant = XQT_B200_VARIANT_SIMT;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   switch (variant) {
     case XQT_B200_VARIANT_SIMT:
@@ -79,6 +90,13 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
       XQT_REQUIRE(((uintptr_t)activation & 15) == 0 && ((uintptr_t)qweight & 15) == 0);
       return w4a16_gemv_launch(activation, qweight, scales, zero_points, bias, residual, output, m, n, k,
                                nibble_signed, act_dtype, param_dtype, workspace, workspace_bytes, s);
+    case XQT_B200_VARIANT_TCGEN05:
+      XQT_REQUIRE(epilogue_activation == XQT_B200_ACT_NONE);
+      XQT_REQUIRE(w4a16_gemm_tc_supported(m, n, k, padded_k, group_size));
+      XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
+      XQT_REQUIRE(((uintptr_t)activation & 15) == 0 && ((uintptr_t)qweight & 15) == 0);
+      return w4a16_gemm_tc_launch(activation, qweight, scales, zero_points, bias, residual, output, m, n, k,
+                                  group_size, nibble_signed, act_dtype, param_dtype, workspace, workspace_bytes, s);
     default:
       return (int)cudaErrorInvalidValue;
   }

@@ -23,6 +23,25 @@ def _check_cuda(name: str, tensor: torch.Tensor | None, device: torch.device) ->
         raise XQTBackendError(f"B200 W4A16 {name} must be contiguous")
 
 
+_integral_cache: dict[tuple[int, int], bool] = {}
+
+
+def _integer_zero_points(zero_points: torch.Tensor | None) -> bool:
+    """True when every zero point is an integer in [0, 1000] (cached per tensor: one device sync
+    the first time a weight is seen).  The tensor-core GEMM folds the zero point into an exact
+    integer subtraction and is only valid then."""
+
+    if zero_points is None:
+        return True
+    key = (zero_points.data_ptr(), zero_points._version)
+    hit = _integral_cache.get(key)
+    if hit is None:
+        z = zero_points.to(torch.float32)
+        hit = bool(((z == z.round()) & (z >= 0) & (z <= 1000)).all().item())
+        _integral_cache[key] = hit
+    return hit
+
+
 def select_variant(m: int, n: int, k: int, padded_k: int, group_size: int, activation: str = "none",
                    has_residual: bool = False) -> str:
     code = native.library().xqt_b200_w4a16_select_variant(
@@ -84,6 +103,10 @@ def w4a16_linear(
     if m == 0:
         return out
     lib = native.library()
+    if variant == "auto":
+        variant = select_variant(m, n, k, padded_k, int(group_size), activation, residual is not None)
+        if variant == "tcgen05" and not _integer_zero_points(zero_points):
+            variant = "simt"
     scratch = native.workspace(device, lib.xqt_b200_w4a16_workspace_bytes(m, n, k))
     stream = native.stream_handle(device)
     act_code, param_code = native.DTYPE_CODE[x.dtype], native.DTYPE_CODE[scales.dtype]
