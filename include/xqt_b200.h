@@ -186,6 +186,29 @@ int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const fl
                        int k, int out_dtype, void* workspace, size_t workspace_bytes,
                        xqt_b200_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * W4A4 SVDQuant / ConvRot linear: after xqt_b200_rotate_quantize(quant_bits = 4, group 64)
+ *   la     = rotated [M,K] * down[32,K]^T                              (xqt_b200_lowrank_down)
+ *   output = sum_g a_s[m,g] w_s[n,g] int32(sum_{k in g} a_q w_q) + la * up^T + bias   (xqt_b200_w4a4_gemm)
+ * Replaces xqt_svdq_w4a4_sm89_quantize_act_fuse_lora / _gemm_lora (svdq_w4a4_sm89_kernel.cu:330-572,
+ * Nunchaku main loop gemm_w4a4.cuh:833-1101, low-rank branch lora.cuh:110-243); accumulation across
+ * groups is fp32 here (half precision there).
+ *   act_codes   int8 [M,K] in [-8,7];  act_scales fp32 [M, K/64]
+ *   qweight     canonical signed-nibble storage uint8 [N, K/2] (the composite artifact's packed_residual)
+ *   aux         per 128-channel tile t, xqt_b200_w4a4_aux_tile_bytes(K) bytes: fp32 [K/64][128] = w_scale/16
+ *               (transposed), then fp32 [128][32] = up factors (rank padded with zeros to 32)
+ *   down        act_dtype [32, K] (rows past the rank are zero);  la fp32 [ceil(M/128)*128, 32]
+ *   K a multiple of 128, N a multiple of 8, rank <= 32.  workspace >= 256 bytes (status word).
+ */
+int xqt_b200_lowrank_down(const void* rotated, const void* down, float* la, int m, int k, int act_dtype,
+                          xqt_b200_stream_t stream);
+size_t xqt_b200_w4a4_aux_tile_bytes(int k);
+int xqt_b200_w4a4_supported(int m, int n, int k);
+int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const void* qweight,
+                       const void* aux, const float* la, const float* bias, void* output, int m, int n,
+                       int k, int out_dtype, void* workspace, size_t workspace_bytes,
+                       xqt_b200_stream_t stream);
+
 /* Copies the status word of `workspace` to *host_status (host pointer) and synchronises `stream`.
  * No counterpart in the reference, whose kernels have no device-side waits. */
 int xqt_b200_workspace_status(const void* workspace, unsigned int* host_status,

@@ -24,6 +24,11 @@ int w4a16_gemm_tc_launch(const void*, const void*, const void*, const void*, con
                          int, int, int, int, int, void*, size_t, cudaStream_t);
 size_t w4a16_gemm_tc_workspace_bytes(int m, int k);
 bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size);
+int lowrank_down_launch(const void*, const void*, float*, int, int, int, cudaStream_t);
+int w4a4_gemm_launch(const void*, const float*, const void*, const void*, const float*, const float*, void*, int, int, int,
+                     int, unsigned int*, cudaStream_t);
+size_t w4a4_aux_tile_bytes(int k);
+bool w4a4_gemm_supported(int m, int n, int k);
 int rotate_quant_launch(const void*, const float*, void*, float*, void*, int, int, int, int, int, int, int, cudaStream_t);
 int gemm_i8_launch(const void*, const void*, const float*, const float*, const float*, void*, int, int, int, int,
                    unsigned int*, cudaStream_t);
@@ -176,6 +181,27 @@ int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const fl
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
   return gemm_i8_launch(act_codes, weight_codes, act_scale, weight_scale, bias, output, m, n, k, out_dtype,
                         reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
+}
+
+int xqt_b200_lowrank_down(const void* rotated, const void* down, float* la, int m, int k, int act_dtype,
+                          xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(rotated != nullptr && down != nullptr && la != nullptr);
+  XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
+  return lowrank_down_launch(rotated, down, la, m, k, act_dtype, (cudaStream_t)stream);
+}
+
+size_t xqt_b200_w4a4_aux_tile_bytes(int k) { return k > 0 && k % 64 == 0 ? w4a4_aux_tile_bytes(k) : 0; }
+
+int xqt_b200_w4a4_supported(int m, int n, int k) { return w4a4_gemm_supported(m, n, k) ? 1 : 0; }
+
+int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const void* qweight, const void* aux,
+                       const float* la, const float* bias, void* output, int m, int n, int k, int out_dtype,
+                       void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
+  return w4a4_gemm_launch(act_codes, act_scales, qweight, aux, la, bias, output, m, n, k, out_dtype,
+                          reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
 }
 
 int xqt_b200_workspace_status(const void* workspace, unsigned int* host_status, xqt_b200_stream_t stream) {

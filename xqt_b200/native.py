@@ -51,6 +51,10 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_decode_static_max_n": (_I, []),
     "xqt_b200_rotate_quantize": (_I, [_P] * 5 + [_I] * 7 + [_P]),
     "xqt_b200_w8a8_gemm": (_I, [_P] * 6 + [_I] * 4 + [_P, _Z, _P]),
+    "xqt_b200_lowrank_down": (_I, [_P] * 3 + [_I] * 3 + [_P]),
+    "xqt_b200_w4a4_aux_tile_bytes": (_Z, [_I]),
+    "xqt_b200_w4a4_supported": (_I, [_I] * 3),
+    "xqt_b200_w4a4_gemm": (_I, [_P] * 7 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_workspace_status": (_I, [_P, ctypes.POINTER(ctypes.c_uint), _P]),
 }
 

@@ -1,0 +1,162 @@
+"""W4A4 SVDQuant / ConvRot linear on B200.
+
+Python surface of xqt's native op (xqt/kernels/ops/_impl/cute/svdq_w4a4_sm89.py:379-557,963-1318):
+``pack_svdq_w4a4_linear`` -> ``PackedSVDQW4A4Linear``, ``svdq_w4a4_linear(inputs, packed,
+workspace=None, lora_scale=1.0)``, ``bind_svdq_w4a4_linear``, ``convrot_w4a4_linear`` (no low-rank
+branch).  The packed contents are backend-private: here the weight stays in the composite artifact's
+own canonical signed-nibble bytes (``packed_residual``, xqt/contracts/composite.py:92-227) -- the
+artifact's integer codes are consumed as they are, not re-quantised from a dequantised copy as the
+sm_89 path does (xqt/runtime/modules/composite_add_w4a4.py:198-216) -- plus a small per-tile block of
+transposed scales and up factors.
+
+Per call: rotate + round + group-64 int4 quantisation (one kernel), rank-R down projection (one
+kernel), tcgen05 ``kind::i8`` GEMM with per-slab fp32 scaling, rank-R up projection and bias in the
+epilogue (one kernel).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import native
+from ..errors import XQTBackendError
+from ..quantize import Rotation, quantize_residual_int4
+from .activation import rotate_quantize
+
+GROUP = 64
+RANK_PAD = 32
+TILE = 128
+
+
+@dataclass(frozen=True)
+class PackedSVDQW4A4Linear:
+    qweight: torch.Tensor          # uint8 [N, K/2] canonical signed nibbles
+    aux: torch.Tensor              # fp32 [ceil(N/128), K/64*128 + 128*32]
+    weight_scales: torch.Tensor    # fp32 [N, K/64] (kept for inspection / export)
+    down: torch.Tensor             # dtype [32, K], rows past the rank are zero
+    bias: torch.Tensor | None      # fp32 [N]
+    input_features: int
+    output_features: int
+    padded_input_features: int
+    rank: int
+    dtype: torch.dtype
+    rotation: Rotation | None = None
+
+    @property
+    def padded_rank(self) -> int:
+        return RANK_PAD
+
+
+def pack_svdq_w4a4_linear(
+    residual_weight: torch.Tensor | None,
+    down_weight: torch.Tensor | None,
+    up_weight: torch.Tensor | None,
+    bias: torch.Tensor | None = None,
+    *,
+    packed_residual: torch.Tensor | None = None,
+    residual_scale: torch.Tensor | None = None,
+    dtype: torch.dtype = torch.bfloat16,
+    rotation: Rotation | None = None,
+    device: torch.device | None = None,
+) -> PackedSVDQW4A4Linear:
+    """Build the B200 layout.  Pass the artifact's ``packed_residual`` / ``residual_scale``
+    (group 64) to keep its integer codes bit for bit; otherwise ``residual_weight`` ``[N,K]`` is
+    quantised with the artifact's own rule (scale = absmax/7, xqt/compression/quant/quantizers/svd.py:92-128).
+    ``down_weight`` is ``[r,K]``, ``up_weight`` ``[N,r]`` (None for a layer without low-rank branch)."""
+
+    if packed_residual is None:
+        if residual_weight is None:
+            raise XQTBackendError("pack_svdq_w4a4_linear needs residual_weight or packed_residual")
+        packed_residual, residual_scale, _ = quantize_residual_int4(residual_weight, group_size=GROUP)
+    if residual_scale is None:
+        raise XQTBackendError("packed_residual needs its residual_scale")
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise XQTBackendError("SVDQ W4A4 supports fp16 or bf16 activations")
+    device = packed_residual.device if device is None else device
+    n, k = int(packed_residual.shape[0]), int(packed_residual.shape[1]) * 2
+    groups = k // GROUP
+    if packed_residual.dtype != torch.uint8 or tuple(residual_scale.shape) != (n, groups):
+        raise XQTBackendError(f"SVDQ W4A4 residual must be uint8 [N,K/2] with group-64 scales [{n},{groups}]")
+    if not native.library().xqt_b200_w4a4_supported(1, n, k):
+        raise XQTBackendError("SVDQ W4A4 on B200 needs K % 128 == 0 and N % 8 == 0")
+    rank = 0 if down_weight is None else int(down_weight.shape[0])
+    if rank > RANK_PAD:
+        raise XQTBackendError(f"SVDQ W4A4 on B200 supports rank <= {RANK_PAD}")
+    if (down_weight is None) != (up_weight is None):
+        raise XQTBackendError("down_weight and up_weight come together")
+    tiles = -(-n // TILE)
+    scale = residual_scale.to(device=device, dtype=torch.float32)
+    sw = torch.zeros((tiles * TILE, groups), device=device, dtype=torch.float32)
+    sw[:n] = scale / 16.0                     # the kernel feeds 16*w to the tensor core
+    up = torch.zeros((tiles * TILE, RANK_PAD), device=device, dtype=torch.float32)
+    down = torch.zeros((RANK_PAD, k), device=device, dtype=dtype)
+    if rank:
+        if tuple(down_weight.shape) != (rank, k) or tuple(up_weight.shape) != (n, rank):
+            raise XQTBackendError("low-rank factors must be down [r,K] and up [N,r]")
+        up[:n, :rank] = up_weight.to(device=device, dtype=dtype).to(torch.float32)
+        down[:rank] = down_weight.to(device=device, dtype=dtype)
+    aux = torch.cat((sw.reshape(tiles, TILE, groups).transpose(1, 2).reshape(tiles, -1),
+                     up.reshape(tiles, -1)), dim=1).contiguous()
+    return PackedSVDQW4A4Linear(
+        qweight=packed_residual.to(device).contiguous(), aux=aux, weight_scales=scale.contiguous(), down=down,
+        bias=None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous(),
+        input_features=k, output_features=n, padded_input_features=k, rank=rank, dtype=dtype, rotation=rotation)
+
+
+def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, workspace=None, lora_scale: float = 1.0,
+                     return_parts: bool = False):
+    """Full forward: rotation (``packed.rotation``; None = input already rotated), int4 activations
+    per (token, 64-K), integer GEMM with per-group scales, low-rank branch, bias."""
+
+    del workspace
+    if inputs.shape[-1] != packed.input_features or inputs.dtype != packed.dtype:
+        raise XQTBackendError("SVDQ W4A4 input trailing dimension or dtype does not match the packed layer")
+    x = inputs.reshape(-1, packed.input_features).contiguous()
+    m, k, n = int(x.shape[0]), packed.input_features, packed.output_features
+    device = x.device
+    out = torch.empty((m, n), device=device, dtype=packed.dtype)
+    if m == 0:
+        return out.reshape(*inputs.shape[:-1], n)
+    lib = native.library()
+    codes, scales, rotated = rotate_quantize(x, packed.rotation, bits=4, group_size=GROUP, return_rotated=True)
+    la = torch.zeros((-(-m // TILE) * TILE, RANK_PAD), device=device, dtype=torch.float32)
+    stream = native.stream_handle(device)
+    with torch.cuda.device(device):
+        if packed.rank:
+            native.check(lib.xqt_b200_lowrank_down(rotated.data_ptr(), packed.down.data_ptr(), la.data_ptr(), m, k,
+                                                   native.DTYPE_CODE[packed.dtype], stream), "xqt_b200_lowrank_down")
+            if lora_scale != 1.0:
+                la.mul_(float(lora_scale))
+        scratch = native.workspace(device, 256)
+        native.check(lib.xqt_b200_w4a4_gemm(
+            codes.data_ptr(), scales.data_ptr(), packed.qweight.data_ptr(), packed.aux.data_ptr(), la.data_ptr(),
+            native.ptr(packed.bias), out.data_ptr(), m, n, k, native.DTYPE_CODE[packed.dtype], scratch.data_ptr(),
+            scratch.numel(), stream), "xqt_b200_w4a4_gemm")
+    out = out.reshape(*inputs.shape[:-1], n)
+    if return_parts:
+        return out, {"codes": codes, "scales": scales, "rotated": rotated, "la": la[:m]}
+    return out
+
+
+def convrot_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, rot_size: int | None = None,
+                        workspace=None) -> torch.Tensor:
+    """ConvRot W4A4 (no low-rank branch): same kernels with an empty rank-R term."""
+
+    if rot_size is not None and packed.rotation is not None and int(rot_size) != packed.rotation.block:
+        raise XQTBackendError("rot_size disagrees with the rotation the layer was packed with")
+    return svdq_w4a4_linear(inputs, packed, workspace=workspace)
+
+
+def bind_svdq_w4a4_linear(packed: PackedSVDQW4A4Linear, workspace=None, *, rows: int, lora_scale: float = 1.0):
+    def run(inputs: torch.Tensor) -> torch.Tensor:
+        if inputs.reshape(-1, packed.input_features).shape[0] != rows:
+            raise XQTBackendError("bound SVDQ W4A4 call: row count mismatch")
+        return svdq_w4a4_linear(inputs, packed, lora_scale=lora_scale)
+
+    return run
+
+
+__all__ = ["PackedSVDQW4A4Linear", "bind_svdq_w4a4_linear", "convrot_w4a4_linear", "pack_svdq_w4a4_linear",
+           "svdq_w4a4_linear"]
