@@ -240,7 +240,7 @@ def run_gpu_arm(args) -> None:
             for m in MS:
                 bound[(copy, k, n, m)] = bind_w4a16_decode(dev_layers[copy][(k, n)], rows=m, dtype=torch.bfloat16)
     outputs = {(n, m): torch.empty((m, n // world), device=device, dtype=torch.bfloat16) for _, n in SHAPES for m in MS}
-    gathered = {(n, m): torch.empty((world, m, n // world), device=device, dtype=torch.bfloat16)
+    gathered = {(n, m): torch.empty((world * m, n // world), device=device, dtype=torch.bfloat16)
                 for _, n in SHAPES for m in MS} if world > 1 else {}
     launches = 0
 
@@ -251,7 +251,7 @@ def run_gpu_arm(args) -> None:
         if world > 1:
             buf = gathered[(n, m)]
             dist.all_gather_into_tensor(buf, y)
-            return buf.permute(1, 0, 2).reshape(m, n)
+            return buf.reshape(world, m, n // world).permute(1, 0, 2).reshape(m, n)
         return y
 
     def eager_step(i):

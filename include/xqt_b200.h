@@ -70,7 +70,8 @@ int xqt_b200_device_supported(int device);
  *               two's-complement nibbles when nibble_signed, codes 0..15 otherwise
  *   scales      [N, padded_k/group_size] param_dtype;  zero_points same shape or NULL
  *   bias        [N] fp32 or NULL;  residual [M, N] act_dtype or NULL
- *   output      [M, N] act_dtype
+ *   output      [M, N] out_dtype: act_dtype, or XQT_B200_FP32 for the unrounded partial sums of a
+ *               K-sharded (row-parallel) layer (then no residual; tensor-core GEMM only)
  *   W = (code - zero_point) * scale, fp32 accumulate, bias -> residual -> activation -> one cast
  *   (xqt/kernels/ops/gemm/reference.py:263-271,362-390,527).
  *   workspace   scratch of at least xqt_b200_w4a16_workspace_bytes(m, n, k) bytes; must be zero
@@ -83,8 +84,8 @@ size_t xqt_b200_w4a16_workspace_bytes(int m, int n, int k);
 int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* scales,
                        const void* zero_points, const float* bias, const void* residual,
                        void* output, int m, int n, int k, int padded_k, int group_size,
-                       int nibble_signed, int act_dtype, int param_dtype, int epilogue_activation,
-                       void* workspace, size_t workspace_bytes, int variant,
+                       int nibble_signed, int act_dtype, int param_dtype, int out_dtype,
+                       int epilogue_activation, void* workspace, size_t workspace_bytes, int variant,
                        xqt_b200_stream_t stream);
 
 /* Kernel the AUTO variant would pick for this problem (one of XQT_B200_VARIANT_*). */
@@ -126,7 +127,8 @@ int xqt_b200_w4a16_decode_tc_supported(int m, int n, int k, int group_size);
 int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, const void* tiled_params,
                              const float* bias, const void* residual, void* output, int m, int n,
                              int k, int group_size, int nibble_signed, int act_dtype, int param_dtype,
-                             void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream);
+                             int out_dtype, void* workspace, size_t workspace_bytes,
+                             xqt_b200_stream_t stream);
 
 /* W4A16 decode with the scratch built into the library: same operation, arguments and result as
  * xqt_b200_w4a16_decode_tiled, minus the workspace pair.  It has no counterpart in the reference.
@@ -208,6 +210,12 @@ int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const voi
                        const void* aux, const float* la, const float* bias, void* output, int m, int n,
                        int k, int out_dtype, void* workspace, size_t workspace_bytes,
                        xqt_b200_stream_t stream);
+
+/* SwiGLU gating between the projections of an MLP: output[m, i] = silu(gate_up[m, i]) * gate_up[m, inter + i],
+ * evaluated in fp32 and rounded once.  gate_up is [M, 2*inter] (the gate and up projections fused
+ * horizontally into one linear), output [M, inter].  Replaces xqt_convrot_w8a8_sm89_fused_swiglu
+ * (convrot_w8a8_sm89_kernel.cu:756-837). */
+int xqt_b200_swiglu(const void* gate_up, void* output, int m, int inter, int dtype, xqt_b200_stream_t stream);
 
 /* Copies the status word of `workspace` to *host_status (host pointer) and synchronises `stream`.
  * No counterpart in the reference, whose kernels have no device-side waits. */

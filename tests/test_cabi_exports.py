@@ -39,9 +39,9 @@ def test_argument_checks_need_no_gpu():
     assert lib.xqt_b200_w4a16_select_variant(16, 4096, 4096, 4096, 128, 0, 0) == native.VARIANT["gemv"]
     assert lib.xqt_b200_w4a16_select_variant(16, 4096, 4096, 4096, 64, 0, 0) == native.VARIANT["simt"]
     # invalid group size is rejected before any CUDA call
-    code = lib.xqt_b200_w4a16_run(0, 0, 0, 0, 0, 0, 0, 4, 8, 64, 64, 48, 0, 1, 1, 0, 0, 0, 0, 0)
+    code = lib.xqt_b200_w4a16_run(0, 0, 0, 0, 0, 0, 0, 4, 8, 64, 64, 48, 0, 1, 1, 1, 0, 0, 0, 0, 0)
     assert code == 1
     with pytest.raises(native.CudaCallError):
         native.check(code, "xqt_b200_w4a16_run")
     # M == 0 is a successful no-op
-    assert lib.xqt_b200_w4a16_run(0, 0, 0, 0, 0, 0, 0, 0, 8, 64, 64, 64, 0, 1, 1, 0, 0, 0, 0, 0) == 0
+    assert lib.xqt_b200_w4a16_run(0, 0, 0, 0, 0, 0, 0, 0, 8, 64, 64, 64, 0, 1, 1, 1, 0, 0, 0, 0, 0) == 0

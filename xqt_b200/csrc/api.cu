@@ -17,11 +17,12 @@ int w4a16_decode_launch_static(const void*, const void*, const void*, const floa
 size_t w4a16_decode_static_scratch_bytes();
 int w4a16_decode_static_max_n();
 int w4a16_decode_tc_launch(const void*, const void*, const void*, const float*, const void*, void*, int, int, int, int,
-                           int, int, int, void*, size_t, cudaStream_t);
+                           int, int, int, int, void*, size_t, cudaStream_t);
 size_t w4a16_decode_tc_workspace_bytes();
 bool w4a16_decode_tc_supported(int m, int n, int k, int group_size);
 int w4a16_gemm_tc_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int,
-                         int, int, int, int, int, void*, size_t, cudaStream_t);
+                         int, int, int, int, int, int, void*, size_t, cudaStream_t);
+int swiglu_launch(const void*, void*, int, int, int, cudaStream_t);
 size_t w4a16_gemm_tc_workspace_bytes(int m, int k);
 bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size);
 int lowrank_down_launch(const void*, const void*, float*, int, int, int, cudaStream_t);
@@ -68,16 +69,24 @@ int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_s
 
 int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* scales, const void* zero_points,
                        const float* bias, const void* residual, void* output, int m, int n, int k, int padded_k,
-                       int group_size, int nibble_signed, int act_dtype, int param_dtype, int epilogue_activation,
-                       void* workspace, size_t workspace_bytes, int variant, xqt_b200_stream_t stream) {
+                       int group_size, int nibble_signed, int act_dtype, int param_dtype, int out_dtype,
+                       int epilogue_activation, void* workspace, size_t workspace_bytes, int variant,
+                       xqt_b200_stream_t stream) {
   XQT_REQUIRE(m >= 0 && n > 0 && k > 0 && padded_k >= k);
   XQT_REQUIRE(group_size == 32 || group_size == 64 || group_size == 128);
   XQT_REQUIRE(padded_k % group_size == 0);
   XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
   XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
   XQT_REQUIRE(epilogue_activation >= XQT_B200_ACT_NONE && epilogue_activation <= XQT_B200_ACT_SILU);
+  XQT_REQUIRE(out_dtype == act_dtype || out_dtype == XQT_B200_FP32);
+  const int out_f32 = out_dtype == XQT_B200_FP32 && act_dtype != XQT_B200_FP32 ? 1 : 0;
   if (m == 0) return 0;
   XQT_REQUIRE(activation != nullptr && qweight != nullptr && scales != nullptr && output != nullptr);
+  if (out_f32) {
+    // fp32 partial sums (K-sharded layers) are produced by the tensor-core GEMM only
+    XQT_REQUIRE(variant == XQT_B200_VARIANT_AUTO || variant == XQT_B200_VARIANT_TCGEN05);
+    variant = XQT_B200_VARIANT_TCGEN05;
+  }
   if (variant == XQT_B200_VARIANT_AUTO) {
     variant = xqt_b200_w4a16_select_variant(m, n, k, padded_k, group_size, epilogue_activation, residual != nullptr);
     // the tensor-core GEMM folds the zero point into an exact integer subtraction: only a caller who
@@ -101,7 +110,8 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
       XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
       XQT_REQUIRE(((uintptr_t)activation & 15) == 0 && ((uintptr_t)qweight & 15) == 0);
       return w4a16_gemm_tc_launch(activation, qweight, scales, zero_points, bias, residual, output, m, n, k,
-                                  group_size, nibble_signed, act_dtype, param_dtype, workspace, workspace_bytes, s);
+                                  group_size, nibble_signed, act_dtype, param_dtype, out_f32, workspace,
+                                  workspace_bytes, s);
     default:
       return (int)cudaErrorInvalidValue;
   }
@@ -135,16 +145,17 @@ int xqt_b200_w4a16_decode_tc_supported(int m, int n, int k, int group_size) {
 
 int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, const void* tiled_params,
                              const float* bias, const void* residual, void* output, int m, int n, int k,
-                             int group_size, int nibble_signed, int act_dtype, int param_dtype, void* workspace,
-                             size_t workspace_bytes, xqt_b200_stream_t stream) {
+                             int group_size, int nibble_signed, int act_dtype, int param_dtype, int out_dtype,
+                             void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
   XQT_REQUIRE(m >= 0 && n > 0 && k > 0);
   XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
   XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
   if (m == 0) return 0;
   XQT_REQUIRE(activation != nullptr && row_weights != nullptr && tiled_params != nullptr && output != nullptr);
+  XQT_REQUIRE(out_dtype == act_dtype || out_dtype == XQT_B200_FP32);
   return w4a16_decode_tc_launch(activation, row_weights, tiled_params, bias, residual, output, m, n, k, group_size,
-                                nibble_signed, act_dtype, param_dtype, workspace, workspace_bytes,
-                                (cudaStream_t)stream);
+                                nibble_signed, act_dtype, param_dtype, out_dtype == XQT_B200_FP32 ? 1 : 0, workspace,
+                                workspace_bytes, (cudaStream_t)stream);
 }
 
 int xqt_b200_w4a16_decode_tiled_static(const void* activation, const void* tiled_weights, const void* tiled_params,
@@ -202,6 +213,13 @@ int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const voi
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
   return w4a4_gemm_launch(act_codes, act_scales, qweight, aux, la, bias, output, m, n, k, out_dtype,
                           reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
+}
+
+int xqt_b200_swiglu(const void* gate_up, void* output, int m, int inter, int dtype, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(gate_up != nullptr && output != nullptr && inter > 0 && inter % 8 == 0);
+  XQT_REQUIRE(dtype == XQT_B200_FP16 || dtype == XQT_B200_BF16);
+  return swiglu_launch(gate_up, output, m, inter, dtype, (cudaStream_t)stream);
 }
 
 int xqt_b200_workspace_status(const void* workspace, unsigned int* host_status, xqt_b200_stream_t stream) {

@@ -39,7 +39,7 @@ enum Status : unsigned int { kTimeout = 48 };
 struct W4GemmParams {
   int m, n, k, group_size, groups;
   int mtiles, ntiles, kblocks, stages;
-  int param_dtype, nibble_signed;
+  int param_dtype, nibble_signed, out_f32;
   const uint8_t* qweight;   // canonical [N, K/2]
   const void* scales;
   const void* zeros;
@@ -224,7 +224,13 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_a, const W4GemmParams p
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v[e] += rv[e];
               }
-              w4_store8<T>(out + (size_t)row * p.n + col, v);
+              if (p.out_f32) {
+                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)row * p.n + col);
+                dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+                dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+              } else {
+                w4_store8<T>(out + (size_t)row * p.n + col, v);
+              }
             }
           }
         }
@@ -350,7 +356,8 @@ static int launch_w4gemm(const void* x, const void* qw, W4GemmParams p, cudaStre
 
 int w4a16_gemm_tc_launch(const void* x, const void* qw, const void* scales, const void* zeros, const float* bias,
                          const void* residual, void* out, int m, int n, int k, int group_size, int nibble_signed,
-                         int act_dtype, int param_dtype, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                         int act_dtype, int param_dtype, int out_f32, void* workspace, size_t workspace_bytes,
+                         cudaStream_t stream) {
   XQT_REQUIRE(w4a16_gemm_tc_supported(m, n, k, k, group_size));
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256 && ((uintptr_t)out & 15) == 0);
   unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
@@ -364,7 +371,8 @@ int w4a16_gemm_tc_launch(const void* x, const void* qw, const void* scales, cons
   }
   W4GemmParams p{};
   p.m = m; p.n = n; p.k = k; p.group_size = group_size; p.groups = k / group_size;
-  p.param_dtype = param_dtype; p.nibble_signed = nibble_signed;
+  p.param_dtype = param_dtype; p.nibble_signed = nibble_signed; p.out_f32 = out_f32;
+  XQT_REQUIRE(!out_f32 || residual == nullptr);
   p.scales = scales; p.zeros = zeros; p.bias = bias; p.residual = residual; p.out = out; p.status = status;
   const bool wide = n % 256 == 0 && (long long)ceil_div(m, 128) * (n / 256) >= 148;
   if (act_dtype == XQT_B200_BF16)

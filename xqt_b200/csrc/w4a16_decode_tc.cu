@@ -68,6 +68,7 @@ struct DecodeTcParams {
   const void* residual;
   void* out;
   int m, n, k;
+  int out_f32;         // 1: output is fp32 [M,N] (partial sums of a K-sharded layer), else T
   int tiles, spt;
   long long total;
   int nstages, stage_bytes, sz_stage_bytes;
@@ -386,7 +387,8 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
               float v = acc[i] + b;
               const size_t o = (size_t)i * p.n + chn;
               if (res != nullptr) v += to_float<T>(res[o]);
-              out[o] = from_float<T>(v);
+              if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = v;
+              else out[o] = from_float<T>(v);
             }
           }
         }
@@ -473,7 +475,7 @@ static int dtc_launch(const CUtensorMap& tm, const DecodeTcParams& p, int group_
 
 int w4a16_decode_tc_launch(const void* x, const void* wt, const void* sz, const float* bias, const void* residual,
                            void* out, int m, int n, int k, int group_size, int nibble_signed, int act_dtype,
-                           int param_dtype, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                           int param_dtype, int out_f32, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   using namespace dtc;
   XQT_REQUIRE(w4a16_decode_tc_supported(m, n, k, group_size));
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= w4a16_decode_tc_workspace_bytes());
@@ -486,7 +488,8 @@ int w4a16_decode_tc_launch(const void* x, const void* wt, const void* sz, const 
   const int psize = param_dtype == XQT_B200_FP32 ? 4 : 2;
   DecodeTcParams p;
   p.wt = (const uint8_t*)wt; p.sz = (const uint8_t*)sz; p.bias = bias; p.residual = residual; p.out = out;
-  p.m = m; p.n = n; p.k = k;
+  p.m = m; p.n = n; p.k = k; p.out_f32 = out_f32;
+  XQT_REQUIRE(!out_f32 || residual == nullptr);
   p.tiles = ceil_div(n, kTileRows);
   p.spt = k / kStageK;
   p.total = (long long)p.tiles * p.spt;

@@ -39,13 +39,13 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_device_supported": (_I, [_I]),
     "xqt_b200_w4a16_workspace_bytes": (_Z, [_I, _I, _I]),
     "xqt_b200_w4a16_select_variant": (_I, [_I] * 7),
-    "xqt_b200_w4a16_run": (_I, [_P] * 7 + [_I] * 9 + [_P, _Z, _I, _P]),
+    "xqt_b200_w4a16_run": (_I, [_P] * 7 + [_I] * 10 + [_P, _Z, _I, _P]),
     "xqt_b200_w4a16_decode_workspace_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_supported": (_I, [_I] * 4),
     "xqt_b200_w4a16_decode_tiled": (_I, [_P] * 6 + [_I] * 8 + [_P, _Z, _P]),
     "xqt_b200_w4a16_decode_tc_workspace_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_tc_supported": (_I, [_I] * 4),
-    "xqt_b200_w4a16_decode_tc": (_I, [_P] * 6 + [_I] * 7 + [_P, _Z, _P]),
+    "xqt_b200_w4a16_decode_tc": (_I, [_P] * 6 + [_I] * 8 + [_P, _Z, _P]),
     "xqt_b200_w4a16_decode_tiled_static": (_I, [_P] * 6 + [_I] * 8 + [_P]),
     "xqt_b200_w4a16_decode_static_scratch_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_static_max_n": (_I, []),
@@ -55,6 +55,7 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a4_aux_tile_bytes": (_Z, [_I]),
     "xqt_b200_w4a4_supported": (_I, [_I] * 3),
     "xqt_b200_w4a4_gemm": (_I, [_P] * 7 + [_I] * 4 + [_P, _Z, _P]),
+    "xqt_b200_swiglu": (_I, [_P, _P, _I, _I, _I, _P]),
     "xqt_b200_workspace_status": (_I, [_P, ctypes.POINTER(ctypes.c_uint), _P]),
 }
 

@@ -1,0 +1,120 @@
+"""W4A16 SwiGLU MLP block on B200: ``y = down(silu(gate x) * up x)``.
+
+The block shape is xqt's toy SwiGLU MLP (xqt/kernels/nn/fixtures/toy_models.py:87-121); the fusion
+choices follow its ConvRot W8A8 backend, which fuses gate and up horizontally into one linear and
+gates with one vectorised kernel (xqt/kernels/ops/_impl/cute/convrot_w8a8_sm89.py:664-917,
+convrot_w8a8_sm89_kernel.cu:756-837).
+
+Per call and rank: one linear for the concatenated ``[gate; up]`` shard, one SwiGLU kernel, one
+linear for the down shard; at M <= 16 the linears are the tcgen05 decode kernel, above it the
+tcgen05 GEMM.  With more than one rank gate/up are split over N, down over K, and the fp32 partial
+sums of down are added with one NCCL all-reduce and rounded once.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import native
+from ..contracts import PackedWeight, PackedWeightMetadata
+from ..errors import XQTBackendError
+from ..parallel import shard_packed_weight
+from .w4a16 import bind_w4a16_decode, prepare_decode, w4a16_linear
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``[M, 2I] -> [M, I]``: ``silu(gate_up[:, :I]) * gate_up[:, I:]`` in fp32, rounded once."""
+
+    if gate_up.ndim != 2 or gate_up.shape[1] % 16 or gate_up.dtype not in (torch.float16, torch.bfloat16):
+        raise XQTBackendError("swiglu expects a rank-2 fp16/bf16 tensor [M, 2*inter] with inter % 8 == 0")
+    if not gate_up.is_cuda or not gate_up.is_contiguous():
+        raise XQTBackendError("swiglu expects a contiguous CUDA tensor")
+    m, inter = int(gate_up.shape[0]), int(gate_up.shape[1]) // 2
+    if out is None:
+        out = torch.empty((m, inter), device=gate_up.device, dtype=gate_up.dtype)
+    if m:
+        with torch.cuda.device(gate_up.device):
+            native.check(native.library().xqt_b200_swiglu(
+                gate_up.data_ptr(), out.data_ptr(), m, inter, native.DTYPE_CODE[gate_up.dtype],
+                native.stream_handle(gate_up.device)), "xqt_b200_swiglu")
+    return out
+
+
+def _concat_rows(a: PackedWeight, b: PackedWeight) -> PackedWeight:
+    ma, mb = a.metadata, b.metadata
+    if (ma.logical_shape[1], ma.group_size, ma.nibble_signed) != (mb.logical_shape[1], mb.group_size, mb.nibble_signed):
+        raise XQTBackendError("gate and up must share K, group size and signedness to be fused")
+    if (a.zero_points is None) != (b.zero_points is None):
+        raise XQTBackendError("gate and up must both carry zero points or neither")
+    n = ma.logical_shape[0] + mb.logical_shape[0]
+    values = {f: getattr(ma, f) for f in PackedWeightMetadata.__dataclass_fields__}
+    values.update(logical_shape=(n, ma.logical_shape[1]), local_shape=None if ma.local_shape is None else (n, ma.logical_shape[1]))
+    return PackedWeight(
+        qweight=torch.cat((a.qweight, b.qweight)), scales=torch.cat((a.scales, b.scales)),
+        zero_points=None if a.zero_points is None else torch.cat((a.zero_points, b.zero_points)),
+        metadata=PackedWeightMetadata(**values))
+
+
+class _Linear:
+    """One W4A16 layer on a device with both execution forms: decode layout and canonical bytes."""
+
+    def __init__(self, weight: PackedWeight, device: torch.device, dtype: torch.dtype) -> None:
+        meta = weight.metadata
+        self.n, self.k = meta.logical_shape
+        self.group, self.signed, self.dtype = int(meta.group_size), bool(meta.nibble_signed), dtype
+        self.qweight = weight.qweight.to(device).contiguous()
+        self.scales = weight.scales.to(device).contiguous()
+        self.zeros = None if weight.zero_points is None else weight.zero_points.to(device).contiguous()
+        self.tiled = prepare_decode(self.qweight, self.scales, self.zeros, group_size=self.group, nibble_signed=self.signed)
+        self._bound: dict[tuple[int, torch.dtype], object] = {}
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        m = int(x.shape[0])
+        odt = self.dtype if out_dtype is None else out_dtype
+        if m <= 16 and (odt == self.dtype or self.tiled.layout == "rows128"):
+            run = self._bound.get((m, odt))
+            if run is None:
+                run = bind_w4a16_decode(self.tiled, rows=m, dtype=self.dtype, out_dtype=odt)
+                self._bound[(m, odt)] = run
+            return run(x)
+        return w4a16_linear(x, self.qweight, self.scales, self.zeros, group_size=self.group,
+                            nibble_signed=self.signed, k=self.k, out_dtype=odt)
+
+
+class W4A16SwiGLUMLP:
+    """The MLP block of one rank.  ``gate`` / ``up`` are canonical ``[inter, hidden]`` weights,
+    ``down`` is ``[hidden, inter]``; they are sharded here for ``rank`` of ``world``."""
+
+    def __init__(self, gate: PackedWeight, up: PackedWeight, down: PackedWeight, *, device: torch.device,
+                 dtype: torch.dtype = torch.bfloat16, rank: int = 0, world: int = 1, group=None) -> None:
+        if world > 1:
+            gate = shard_packed_weight(gate, world=world, rank=rank, axis=0)
+            up = shard_packed_weight(up, world=world, rank=rank, axis=0)
+            down = shard_packed_weight(down, world=world, rank=rank, axis=1)
+        self.world, self.group, self.dtype = world, group, dtype
+        self.gate_up = _Linear(_concat_rows(gate, up), device, dtype)
+        self.down = _Linear(down, device, dtype)
+        self.hidden, self.inter_local = self.down.n, self.down.k
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        h = swiglu(self.gate_up(x))
+        if self.world == 1:
+            return self.down(h)
+        partial = self.down(h, out_dtype=torch.float32)
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+        return partial.to(self.dtype)
+
+    def execution_metadata(self) -> dict:
+        """Which kernels serve this block (the report xqt's runtime modules expose,
+        xqt/runtime/modules/composite_add_w4a4.py:304-318)."""
+
+        return {
+            "implementation": "b200_w4a16_swiglu_mlp", "world": self.world,
+            "decode_layout": self.gate_up.tiled.layout, "hidden": self.hidden, "inter_local": self.inter_local,
+            "kernels": {"m<=16": "w4a16_decode_tc_kernel" if self.gate_up.tiled.layout == "rows128" else "w4a16_decode_kernel",
+                        "m>16": "gemm_w4a16_kernel", "gating": "swiglu_kernel"},
+        }
+
+
+__all__ = ["W4A16SwiGLUMLP", "swiglu"]

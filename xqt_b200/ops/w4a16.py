@@ -63,8 +63,12 @@ def w4a16_linear(
     activation: str = "none",
     variant: str = "auto",
     out: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
 ) -> torch.Tensor:
     """``y = x @ dequant(qweight).T (+bias) (+residual)`` with fp32 accumulation.
+
+    ``out_dtype=torch.float32`` returns the unrounded sums (what a K-sharded layer reduces across
+    ranks); it needs M > 16-style shapes the tensor-core GEMM covers and no residual.
 
     x ``[M,K]`` fp16/bf16; qweight ``uint8 [N, padded_K/2]``; scales / zero_points ``[N, G]``
     fp16/bf16/fp32 (same dtype); bias ``[N]`` (converted to fp32); residual ``[M,N]`` of x's dtype.
@@ -96,13 +100,20 @@ def w4a16_linear(
     for name, tensor in (("activation", x), ("qweight", qweight), ("scales", scales),
                          ("zero_points", zero_points), ("residual", residual)):
         _check_cuda(name, tensor, device)
+    odt = x.dtype if out_dtype is None else out_dtype
+    if odt not in (x.dtype, torch.float32):
+        raise XQTBackendError("B200 W4A16 out_dtype must be the activation dtype or float32")
     if out is None:
-        out = torch.empty((m, n), device=device, dtype=x.dtype)
-    elif out.dtype != x.dtype or tuple(out.shape) != (m, n) or not out.is_contiguous() or out.device != device:
-        raise XQTBackendError("B200 W4A16 out must be a contiguous [M,N] tensor in the activation dtype")
+        out = torch.empty((m, n), device=device, dtype=odt)
+    elif out.dtype != odt or tuple(out.shape) != (m, n) or not out.is_contiguous() or out.device != device:
+        raise XQTBackendError("B200 W4A16 out must be a contiguous [M,N] tensor of the output dtype")
     if m == 0:
         return out
     lib = native.library()
+    if odt == torch.float32:
+        if not _integer_zero_points(zero_points):
+            raise XQTBackendError("fp32 partial sums need the tensor-core GEMM, i.e. integer zero points")
+        variant = "tcgen05"
     if variant == "auto":
         variant = select_variant(m, n, k, padded_k, int(group_size), activation, residual is not None)
         if variant == "tcgen05" and not _integer_zero_points(zero_points):
@@ -115,7 +126,7 @@ def w4a16_linear(
         code = lib.xqt_b200_w4a16_run(
             x.data_ptr(), qweight.data_ptr(), scales.data_ptr(), native.ptr(zero_points), native.ptr(bias),
             native.ptr(residual), out.data_ptr(), m, n, k, padded_k, int(group_size), int(bool(nibble_signed)),
-            act_code, param_code, native.ACT[activation], scratch.data_ptr(), scratch.numel(),
+            act_code, param_code, native.DTYPE_CODE[odt], native.ACT[activation], scratch.data_ptr(), scratch.numel(),
             native.VARIANT[variant], stream)
     native.check(code, "xqt_b200_w4a16_run")
     return out
@@ -152,7 +163,7 @@ def bind_w4a16_linear(
     nbytes = lib.xqt_b200_w4a16_workspace_bytes(rows, n, kk)
     static = (qweight.data_ptr(), scales.data_ptr(), native.ptr(zero_points), native.ptr(bias32), 0)
     tail = (rows, n, kk, padded_k, int(group_size), int(bool(nibble_signed)), native.DTYPE_CODE[dtype],
-            native.DTYPE_CODE[scales.dtype], 0)
+            native.DTYPE_CODE[scales.dtype], native.DTYPE_CODE[dtype], 0)
     variant_code = native.VARIANT[variant]
     index = device.index if device.index is not None else torch.cuda.current_device()
     keep = (qweight, scales, zero_points, bias32)  # noqa: F841 - the closure owns references
@@ -179,7 +190,8 @@ def decode_supported(m: int, n: int, k: int, group_size: int) -> bool:
     return bool(native.library().xqt_b200_w4a16_decode_supported(int(m), int(n), int(k), int(group_size)))
 
 
-def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None = None):
+def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None = None,
+                      out_dtype: torch.dtype | None = None):
     """Hot-callable for the decode kernel on a :class:`xqt_b200.prepack.TiledW4` layer:
     ``run(x, out=None, residual=None) -> Tensor`` for a fixed row count (1..16).  Static tensors are
     validated here, once; each call checks the activation and makes one C-ABI call
@@ -191,6 +203,9 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
     if dtype not in (torch.float16, torch.bfloat16):
         raise XQTBackendError("B200 W4A16 decode supports fp16 or bf16 activations")
     n, k = tiled.n, tiled.k
+    odt = dtype if out_dtype is None else out_dtype
+    if odt not in (dtype, torch.float32):
+        raise XQTBackendError("B200 W4A16 decode out_dtype must be the activation dtype or float32")
     lib = native.library()
     use_tc = tiled.layout == "rows128"
     if use_tc:
@@ -211,8 +226,10 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
         fn, symbol = lib.xqt_b200_w4a16_decode_tc, "xqt_b200_w4a16_decode_tc"
         nbytes = lib.xqt_b200_w4a16_decode_tc_workspace_bytes()
         tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), native.DTYPE_CODE[dtype],
-                native.DTYPE_CODE[tiled.params.dtype])
+                native.DTYPE_CODE[tiled.params.dtype], native.DTYPE_CODE[odt])
     else:
+        if odt != dtype:
+            raise XQTBackendError("fp32 output needs the tcgen05 decode layout (rows128)")
         fn, symbol = lib.xqt_b200_w4a16_decode_tiled, "xqt_b200_w4a16_decode_tiled"
         nbytes = lib.xqt_b200_w4a16_decode_workspace_bytes()
         tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), int(tiled.has_zero_point),
@@ -227,7 +244,7 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
         if torch.cuda.current_device() != index:
             raise XQTBackendError("bound B200 W4A16 decode: make the weight's device current before calling")
         if out is None:
-            out = torch.empty((rows, n), device=device, dtype=dtype)
+            out = torch.empty((rows, n), device=device, dtype=odt)
         if residual is not None and (residual.dtype != dtype or tuple(residual.shape) != (rows, n)
                                      or not residual.is_contiguous()):
             raise XQTBackendError("bound B200 W4A16 decode: residual must be contiguous [M,N] in the activation dtype")

@@ -1,0 +1,149 @@
+"""Column / row partitioning of quantized linears over the GPUs of one node (NCCL over NVLink).
+
+xqt has no multi-device execution; it only declares where a shard would be recorded
+(``PackedWeightMetadata.local_shape / shard_axis``, xqt/kernels/ops/gemm/contracts.py:379-402).  This
+module fills and consumes those fields:
+
+* column-parallel (``shard_axis=0``): rank r owns output channels ``[r N/g, (r+1) N/g)`` -- contiguous
+  row slices of ``qweight``, ``scales`` and ``zero_points``; the activation is replicated; outputs
+  are concatenated with an all-gather (or left sharded when the next layer is row-parallel);
+* row-parallel (``shard_axis=1``): rank r owns input features ``[r K/g, (r+1) K/g)`` -- the byte
+  columns ``[r K/2g, ...)`` of ``qweight`` and the group columns of the scales; every rank produces
+  an fp32 partial ``[M, N]`` which is summed with an all-reduce and rounded once.
+
+One process per GPU, ``torch.distributed`` for the plumbing; collectives run on the current stream
+after the kernels that feed them.  The local computation is injected (``local_linear``), so the
+partition arithmetic and the collective wiring are tested on CPU ranks with the gloo backend.
+No TMA multicast and no load from a peer's memory is used: peers' data arrive through NCCL only.
+"""
+
+from __future__ import annotations
+
+from dataclasses import fields
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+from .contracts import PackedWeight, PackedWeightMetadata
+from .errors import XQTBackendError
+
+
+def shard_packed_weight(weight: PackedWeight, *, world: int, rank: int, axis: int) -> PackedWeight:
+    """Slice a canonical W4 ``PackedWeight`` for ``rank`` of ``world``.  ``axis`` 0 = over N
+    (column-parallel), 1 = over K (row-parallel).  Shards keep the canonical byte layout."""
+
+    meta = weight.metadata
+    n, k = meta.logical_shape
+    group = int(meta.group_size)
+    if not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    if meta.padded_k != k:
+        raise XQTBackendError("sharding needs K == padded_K")
+    if axis == 0:
+        if n % world:
+            raise XQTBackendError(f"N={n} is not divisible by {world} ranks")
+        rows = n // world
+        sl = slice(rank * rows, (rank + 1) * rows)
+        q, s = weight.qweight[sl], weight.scales[sl]
+        z = None if weight.zero_points is None else weight.zero_points[sl]
+        local = (rows, k)
+    elif axis == 1:
+        if k % (world * group) or (k // world) % 2:
+            raise XQTBackendError(f"K={k} must split into {world} whole groups of {group}")
+        cols = k // world
+        q = weight.qweight[:, rank * cols // 2:(rank + 1) * cols // 2]
+        gs = slice(rank * cols // group, (rank + 1) * cols // group)
+        s = weight.scales[:, gs]
+        z = None if weight.zero_points is None else weight.zero_points[:, gs]
+        local = (n, cols)
+    else:
+        raise ValueError("axis must be 0 (N) or 1 (K)")
+    values = {f.name: getattr(meta, f.name) for f in fields(PackedWeightMetadata)}
+    values.update(logical_shape=local, padded_k=local[1], local_shape=local, shard_axis=axis)
+    return PackedWeight(
+        qweight=q.contiguous(), scales=s.contiguous(), zero_points=None if z is None else z.contiguous(),
+        metadata=PackedWeightMetadata(**values))
+
+
+LocalLinear = Callable[..., torch.Tensor]
+
+
+def _default_local_linear(x, weight: PackedWeight, *, out_dtype=None, bias=None):
+    from .ops.w4a16 import w4a16_linear
+
+    meta = weight.metadata
+    return w4a16_linear(x, weight.qweight, weight.scales, weight.zero_points, bias, group_size=int(meta.group_size),
+                        nibble_signed=bool(meta.nibble_signed), k=meta.logical_shape[1], out_dtype=out_dtype)
+
+
+class ColumnParallelLinear:
+    """``y = x W^T`` with W split over N.  ``gather_output=False`` leaves ``[M, N/g]`` on each rank."""
+
+    def __init__(self, shard: PackedWeight, *, group=None, gather_output: bool = True, bias: torch.Tensor | None = None,
+                 local_linear: LocalLinear | None = None) -> None:
+        if shard.metadata.shard_axis != 0:
+            raise XQTBackendError("ColumnParallelLinear needs a shard over N (shard_axis=0)")
+        self.shard, self.group, self.gather_output, self.bias = shard, group, gather_output, bias
+        self.local_linear = local_linear or _default_local_linear
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        local = self.local_linear(x, self.shard, bias=self.bias)
+        if not self.gather_output or self.world == 1:
+            return local
+        m, n_local = local.shape
+        # all_gather_into_tensor concatenates the ranks' [m, n_local] blocks along dim 0
+        gathered = torch.empty((self.world * m, n_local), device=local.device, dtype=local.dtype)
+        dist.all_gather_into_tensor(gathered, local.contiguous(), group=self.group)
+        return gathered.reshape(self.world, m, n_local).permute(1, 0, 2).reshape(m, self.world * n_local)
+
+
+class RowParallelLinear:
+    """``y = x W^T`` with W split over K; ``x`` is the rank's slice ``[M, K/g]``.  Partials are fp32,
+    summed with an all-reduce, bias added once, result rounded once to the activation dtype."""
+
+    def __init__(self, shard: PackedWeight, *, group=None, bias: torch.Tensor | None = None,
+                 local_linear: LocalLinear | None = None) -> None:
+        if shard.metadata.shard_axis != 1:
+            raise XQTBackendError("RowParallelLinear needs a shard over K (shard_axis=1)")
+        self.shard, self.group, self.bias = shard, group, bias
+        self.local_linear = local_linear or _default_local_linear
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return self.local_linear(x, self.shard, bias=self.bias)
+        partial = self.local_linear(x, self.shard, out_dtype=torch.float32)
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+        if self.bias is not None:
+            partial = partial + self.bias.to(partial.dtype)
+        return partial.to(x.dtype)
+
+
+class TensorParallelSwiGLUMLP:
+    """``down(silu(gate x) * up x)`` with gate/up column-parallel (no gather: the gating is
+    element-wise on the local slice) and down row-parallel (one all-reduce per call).
+
+    ``gate``, ``up`` are shards over N of ``[inter, hidden]``; ``down`` is a shard over K of
+    ``[hidden, inter]``.  ``swiglu(g, u)`` defaults to the CUDA kernel.
+    """
+
+    def __init__(self, gate: PackedWeight, up: PackedWeight, down: PackedWeight, *, group=None,
+                 local_linear: LocalLinear | None = None, swiglu: Callable | None = None) -> None:
+        self.gate = ColumnParallelLinear(gate, group=group, gather_output=False, local_linear=local_linear)
+        self.up = ColumnParallelLinear(up, group=group, gather_output=False, local_linear=local_linear)
+        self.down = RowParallelLinear(down, group=group, local_linear=local_linear)
+        self.swiglu = swiglu or _default_swiglu
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down(self.swiglu(self.gate(x), self.up(x)))
+
+
+def _default_swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    from .ops.mlp import swiglu
+
+    return swiglu(torch.cat((gate, up), dim=1))
+
+
+__all__ = ["ColumnParallelLinear", "RowParallelLinear", "TensorParallelSwiGLUMLP", "shard_packed_weight"]
