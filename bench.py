@@ -369,6 +369,7 @@ def run_gpu_arm(args) -> None:
                 nb = algorithmic_bytes(k, n // world, m)
                 detail.append({"k": k, "n": n, "m": m, "us": round(us, 3), "gbs": round(nb / us / 1e3, 1),
                                "frac": round(nb / us / 1e3 / peak, 4)})
+    extras = measure_other_configs(device, world, rank, barrier)
     alg_bytes_step = sum(algorithmic_bytes(k, n // world, m) for k, n in SHAPES for m in MS)
     achieved = alg_bytes_step / (ms_per_step * 1e-3) / 1e9
 
@@ -395,6 +396,7 @@ def run_gpu_arm(args) -> None:
                 "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": timed_launches,
         "detail": detail,
+        "other_configs": extras,
     }
     if world == 1:
         torch.set_num_threads(os.cpu_count() or 1)
@@ -409,6 +411,104 @@ def run_gpu_arm(args) -> None:
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _time_us(fn, barrier, reps: int, warm: int = 3) -> float:
+    for _ in range(warm):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def measure_other_configs(device, world, rank, barrier) -> dict:
+    """The other benchmark configurations, timed with CUDA events (kernels only, inputs resident):
+    the SwiGLU MLP block at every world size (gate/up column-parallel, down row-parallel + all-reduce),
+    and on one GPU the W8A8 and W4A4 linears.  Tensor-pipe fractions use the bf16 peak of
+    MEASURED_PEAKS.json and, for int8, a cuBLAS int8 GEMM (torch._int_mm 8192^3) timed in this run."""
+
+    import torch.distributed as dist
+
+    from xqt_b200 import quantize
+    from xqt_b200.ops.mlp import W4A16SwiGLUMLP
+
+    out: dict = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        bf16_peak = float(peaks.get("bf16_tflops_sustained", 1339.5))
+    except Exception:  # noqa: BLE001
+        bf16_peak = 1400.0
+    hidden, inter = 4096, 14336
+    mk = lambda n, k, s: quantize.quantize_w4_asymmetric(  # noqa: E731
+        torch.randn((n, k), generator=torch.Generator().manual_seed(s)) * 0.02, group_size=GROUP)
+    block = W4A16SwiGLUMLP(mk(inter, hidden, 20), mk(inter, hidden, 21), mk(hidden, inter, 22), device=device,
+                           rank=rank, world=world)
+    mlp = []
+    for m in (1, 16, 512, 4096):
+        x = torch.randn((m, hidden), device=device, dtype=torch.bfloat16)
+        us = _time_us(lambda: block(x), barrier, reps=20 if m <= 512 else 5)
+        if world > 1:
+            t = torch.tensor([us], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+        row = {"m": m, "us": round(us, 2)}
+        if m <= 16:
+            row["weight_gbs"] = round(3 * weight_aux_bytes(hidden, inter) / us / 1e3, 1)
+        else:
+            tf = 2.0 * m * 3 * inter * hidden / us / 1e6
+            row["tflops"] = round(tf, 1)
+            row["frac_of_bf16_sustained_peak_per_gpu"] = round(tf / world / bf16_peak, 4)
+        mlp.append(row)
+    out["w4a16_swiglu_mlp_4096x14336"] = {"world": world, "rows": mlp,
+                                          "note": "L2-resident weights (93.6 MB per copy, one copy)"}
+    del block
+    if world > 1:
+        return out
+    # int8 library peak measured here
+    a = torch.randint(-128, 127, (8192, 8192), device=device, dtype=torch.int8)
+    i8_peak = None
+    try:
+        us = _time_us(lambda: torch._int_mm(a, a.t()), barrier, reps=10)
+        i8_peak = 2.0 * 8192 ** 3 / us / 1e6
+    except Exception:  # noqa: BLE001
+        pass
+    del a
+    out["i8_library_gemm_tops"] = None if i8_peak is None else round(i8_peak, 1)
+    from xqt_b200.ops.w8a8 import convrot_w8a8_linear, pack_convrot_w8a8_linear, w8a8_gemm
+    from xqt_b200.ops.activation import rotate_quantize
+
+    m, n, k = 2048, 4096, 4096
+    rot = quantize.regular_rotation(256)
+    w = torch.randn((n, k), generator=torch.Generator().manual_seed(6)) * 0.02
+    q, sc = quantize.quantize_w8_per_channel(rot.apply(w))
+    packed = pack_convrot_w8a8_linear(q.t().contiguous().to(device), sc.to(device), None, dtype=torch.bfloat16)
+    x = torch.randn((m, k), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(device)
+    codes, scales = rotate_quantize(x, rot, bits=8)
+    y = torch.empty((m, n), device=device, dtype=torch.bfloat16)
+    t_gemm = _time_us(lambda: w8a8_gemm(codes, scales, packed, y), barrier, reps=30)
+    t_full = _time_us(lambda: convrot_w8a8_linear(x, packed, rot_size=256), barrier, reps=30)
+    tops = 2.0 * m * n * k / t_gemm / 1e6
+    out["w8a8_convrot_2048x4096x4096"] = {
+        "gemm_us": round(t_gemm, 2), "gemm_tops": round(tops, 1), "full_forward_us": round(t_full, 2),
+        "gemm_frac_of_i8_library_peak": None if i8_peak is None else round(tops / i8_peak, 4)}
+    from xqt_b200.ops.w4a4 import pack_svdq_w4a4_linear, svdq_w4a4_linear
+
+    m, n, k, r = 4096, 12288, 3072, 32
+    rot4 = quantize.randomized_rotation(128, seed=3)
+    layer = pack_svdq_w4a4_linear(torch.randn((n, k), device=device) * 0.02, torch.randn((r, k), device=device) * 0.05,
+                                  torch.randn((n, r), device=device) * 0.05, None, rotation=rot4)
+    x4 = torch.randn((m, k), device=device, dtype=torch.bfloat16)
+    t4 = _time_us(lambda: svdq_w4a4_linear(x4, layer), barrier, reps=5)
+    tops4 = 2.0 * m * n * k / t4 / 1e6
+    out["w4a4_svdquant_4096x12288x3072_r32"] = {
+        "full_forward_us": round(t4, 2), "tops": round(tops4, 1),
+        "frac_of_i8_library_peak": None if i8_peak is None else round(tops4 / i8_peak, 4)}
+    return out
 
 
 def run_single_problem(args) -> None:

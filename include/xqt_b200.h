@@ -76,7 +76,8 @@ int xqt_b200_device_supported(int device);
  *   (xqt/kernels/ops/gemm/reference.py:263-271,362-390,527).
  *   workspace   scratch of at least xqt_b200_w4a16_workspace_bytes(m, n, k) bytes; must be zero
  *               before its first use (the kernels leave it zeroed where it matters); one
- *               workspace must not be shared by launches that can overlap on the GPU.
+ *               workspace must not be shared by launches that can overlap on the GPU, nor with
+ *               the decode / GEMM entry points below, whose scratch layouts differ.
  * group_size in {32, 64, 128}; M >= 0 (M == 0 is a no-op).
  */
 size_t xqt_b200_w4a16_workspace_bytes(int m, int n, int k);

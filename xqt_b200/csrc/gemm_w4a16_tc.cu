@@ -321,7 +321,10 @@ __global__ void __launch_bounds__(256) bf16_to_f16_kernel(const __nv_bfloat16* _
   reinterpret_cast<uint4*>(dst)[i] = o;
 }
 
-size_t w4a16_gemm_tc_workspace_bytes(int m, int k) { return 256 + (size_t)m * k * 2; }
+// [0,256) status, [256, 256+16 KiB) reserved for the ticket area of the M <= 16 kernel that shares this
+// workspace, then the fp16 copy of bf16 activations
+constexpr size_t kScratchOffset = 256 + 16384;
+size_t w4a16_gemm_tc_workspace_bytes(int m, int k) { return kScratchOffset + (size_t)m * k * 2; }
 
 bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size) {
   return m >= 1 && n % 8 == 0 && k == padded_k && k % 64 == 0 && (group_size == 64 || group_size == 128);
@@ -363,7 +366,7 @@ int w4a16_gemm_tc_launch(const void* x, const void* qw, const void* scales, cons
   unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
   if (act_dtype == XQT_B200_BF16) {
     XQT_REQUIRE(workspace_bytes >= w4a16_gemm_tc_workspace_bytes(m, k));
-    __half* x16 = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + 256);
+    __half* x16 = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + kScratchOffset);
     const size_t n8 = (size_t)m * k / 8;
     bf16_to_f16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, x16, n8);
     XQT_CUDA(cudaGetLastError());

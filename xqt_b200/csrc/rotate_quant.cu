@@ -105,6 +105,147 @@ rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_sc
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Register-resident variant for K % 16 == 0, K <= 16384: thread t owns elements [16t, 16t+16) of the
+// token (two 16-byte loads), the butterflies with stride < 16 stay in its registers and the wider
+// ones go through warp shuffles (a rotation block of <= 256 elements spans <= 16 lanes).  Every
+// output element is produced by exactly the additions and subtractions of the definition above, so
+// the result is bit-identical to the shared-memory kernel and to the CPU oracle.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ column_scale, int8_t* __restrict__ codes,
+                         float* __restrict__ scales, T* __restrict__ x_rot, int k, int rot_kind, int rot_block, int mode,
+                         int group) {
+  __shared__ float s_red[32];
+  __shared__ float s_scale;
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+  const bool active = tid * 16 < k;
+  float v[16];
+  if (active) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)row * k + tid * 16);
+    const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+    const T* a = reinterpret_cast<const T*>(&lo);
+    const T* b = reinterpret_cast<const T*>(&hi);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i] = to_float<T>(a[i]);
+      v[8 + i] = to_float<T>(b[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+  }
+  if (rot_kind == 1) {
+    // regular family: radix-4 stages, strides 1 and 4 in registers, 16 and 64 across lanes
+#pragma unroll
+    for (int st = 1; st <= 4; st *= 4) {
+      if (st < rot_block) {
+#pragma unroll
+        for (int bfly = 0; bfly < 4; ++bfly) {
+          const int base = (bfly / st) * 4 * st + (bfly % st);
+          const float a = v[base], b = v[base + st], c = v[base + 2 * st], d = v[base + 3 * st];
+          const float p = __fadd_rn(a, b), q = __fsub_rn(a, b), r = __fadd_rn(c, d), t = __fsub_rn(c, d);
+          v[base] = __fadd_rn(p, t);
+          v[base + st] = __fsub_rn(p, t);
+          v[base + 2 * st] = __fadd_rn(q, r);
+          v[base + 3 * st] = __fsub_rn(r, q);
+        }
+      }
+    }
+#pragma unroll
+    for (int L = 1; L <= 4; L *= 4) {          // lane distance 1 <-> stride 16, 4 <-> stride 64
+      if (16 * L < rot_block) {
+        // The four inputs (a,b,c,d) of a butterfly sit in the lanes whose 2-bit digit is 0..3.
+        // Exchange with the lane at distance L: digits {0,1} form p=a+b and q=a-b, digits {2,3} form
+        // r=c+d and t=c-d (the odd digit computes the difference the other way round and negates
+        // it, which is exact).  Exchange the difference at distance 2L: outputs p+t, p-t, q+r, r-q
+        // are then sum +- received difference, minus on odd digits.  Same operations as the definition.
+        const uint32_t flip = (lane & L) ? 0x80000000u : 0u;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float own = v[i];
+          const float other = __shfl_xor_sync(0xffffffffu, own, L);
+          const float sum = __fadd_rn(own, other);
+          const float diff = __uint_as_float(__float_as_uint(__fsub_rn(own, other)) ^ flip);
+          const float got = __shfl_xor_sync(0xffffffffu, diff, 2 * L);
+          v[i] = __fadd_rn(sum, __uint_as_float(__float_as_uint(got) ^ flip));
+        }
+      }
+    }
+  } else if (rot_kind == 2) {
+#pragma unroll
+    for (int st = 1; st <= 8; st *= 2) {
+      if (st < rot_block) {
+#pragma unroll
+        for (int bfly = 0; bfly < 8; ++bfly) {
+          const int base = (bfly / st) * 2 * st + (bfly % st);
+          const float a = v[base], b = v[base + st];
+          v[base] = __fadd_rn(a, b);
+          v[base + st] = __fsub_rn(a, b);
+        }
+      }
+    }
+#pragma unroll
+    for (int L = 1; L <= 8; L *= 2) {          // lane distance L <-> stride 16 L
+      if (16 * L < rot_block) {
+        const bool upper = (lane & L) != 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[i], L);
+          v[i] = upper ? __fsub_rn(other, v[i]) : __fadd_rn(v[i], other);
+        }
+      }
+    }
+  }
+  float amax = 0.f;
+  {
+    T rounded[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float r = v[i];
+      if (rot_kind != 0 && active) r = __fmul_rn(r, __ldg(column_scale + ((tid * 16 + i) % rot_block)));
+      rounded[i] = from_float<T>(r);
+      v[i] = to_float<T>(rounded[i]);
+      amax = fmaxf(amax, fabsf(v[i]));
+    }
+    if (x_rot != nullptr && active) {
+      uint4* dst = reinterpret_cast<uint4*>(x_rot + (size_t)row * k + tid * 16);
+      dst[0] = *reinterpret_cast<const uint4*>(&rounded[0]);
+      dst[1] = *reinterpret_cast<const uint4*>(&rounded[8]);
+    }
+  }
+  float sc;
+  float lo_clamp, hi_clamp;
+  if (mode == 8) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (lane == 0) s_red[tid >> 5] = amax;
+    __syncthreads();
+    if (tid == 0) {
+      float mx = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, s_red[w]);
+      const float s0 = __fdiv_rn(fmaxf(mx, 1e-8f), 127.0f);
+      s_scale = s0;
+      scales[row] = s0;
+    }
+    __syncthreads();
+    sc = fmaxf(s_scale, 1e-8f);
+    lo_clamp = -128.f; hi_clamp = 127.f;
+  } else {
+    // group of `group` elements = group/16 adjacent lanes (group is 16, 32, 64, ... <= 512)
+    for (int off = 1; off < group / 16; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    sc = fmaxf(__fdiv_rn(amax, 7.0f), 1e-6f);
+    if (active && (tid % (group / 16)) == 0) scales[(size_t)row * (k / group) + (tid * 16) / group] = sc;
+    lo_clamp = -8.f; hi_clamp = 7.f;
+  }
+  if (active) {
+    int8_t q[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = (int8_t)(int)fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), lo_clamp), hi_clamp);
+    *reinterpret_cast<uint4*>(codes + (size_t)row * k + tid * 16) = *reinterpret_cast<const uint4*>(q);
+  }
+}
+
 int rotate_quant_launch(const void* x, const float* column_scale, void* codes, float* scales, void* x_rot, int m, int k,
                         int rot_kind, int rot_block, int mode, int group, int act_dtype, cudaStream_t stream) {
   XQT_REQUIRE(m > 0 && k > 0 && (mode == 8 || mode == 4));
@@ -118,6 +259,18 @@ int rotate_quant_launch(const void* x, const float* column_scale, void* codes, f
   }
   if (mode == 4) XQT_REQUIRE(group > 0 && k % group == 0);
   XQT_REQUIRE(act_dtype == XQT_B200_BF16 || act_dtype == XQT_B200_FP16);
+  const bool group_ok = mode == 8 || (group >= 16 && group <= 512 && (group & (group - 1)) == 0);
+  if (k % 16 == 0 && k <= 16384 && group_ok && ((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 15) == 0 &&
+      (x_rot == nullptr || ((uintptr_t)x_rot & 15) == 0)) {
+    const int threads = ceil_div(k / 16, 32) * 32;
+    if (act_dtype == XQT_B200_BF16)
+      rotate_quant_fast_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>(
+          (const __nv_bfloat16*)x, column_scale, (int8_t*)codes, scales, (__nv_bfloat16*)x_rot, k, rot_kind, rot_block, mode, group);
+    else
+      rotate_quant_fast_kernel<__half><<<m, threads, 0, stream>>>(
+          (const __half*)x, column_scale, (int8_t*)codes, scales, (__half*)x_rot, k, rot_kind, rot_block, mode, group);
+    return launch_status();
+  }
   const size_t smem = (size_t)k * sizeof(float);
   XQT_REQUIRE(smem <= 200 * 1024);
 #define XQT_RQ(TT)                                                                                               \

@@ -295,7 +295,7 @@ size_t w4a16_gemv_workspace_bytes(int n, int k) {
   // tickets, then one [16, 64] fp32 partial per (split, tile).  Sized for the split a device
   // with up to 256 SMs would choose, which bounds what any B200 launch needs.
   const GemvPlan p = gemv_plan(n, k, 256);
-  return (size_t)kGemvMaxCounters * sizeof(unsigned int) +
+  return 256 + (size_t)kGemvMaxCounters * sizeof(unsigned int) +
          (size_t)p.splits * p.tiles * 16 * kGemvRows * sizeof(float);
 }
 
@@ -335,11 +335,13 @@ int w4a16_gemv_launch(const void* x, const void* qw, const void* scales, const v
                       const void* residual, void* out, int m, int n, int k, int nibble_signed, int act_dtype,
                       int param_dtype, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   const GemvPlan p = gemv_plan(n, k, cached_sm_count());
-  const size_t need = (size_t)kGemvMaxCounters * sizeof(unsigned int) +
+  // workspace: [0,256) status block, [256, 256+16 KiB) tickets (must stay zero between launches),
+  // then partial sums (need not be zero; the tensor-core GEMM uses the same area as its scratch)
+  const size_t need = 256 + (size_t)kGemvMaxCounters * sizeof(unsigned int) +
                       (p.splits > 1 ? (size_t)p.splits * p.tiles * 16 * kGemvRows * sizeof(float) : 0);
   if (p.splits > 1) XQT_REQUIRE(workspace != nullptr && workspace_bytes >= need);
-  unsigned int* tickets = reinterpret_cast<unsigned int*>(workspace);
-  float* partials = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + kGemvMaxCounters * sizeof(unsigned int));
+  unsigned int* tickets = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(workspace) + 256);
+  float* partials = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 256 + kGemvMaxCounters * sizeof(unsigned int));
   const bool zp = zeros != nullptr;
 #define XQT_GEMV_T(TT)                                                                                             \
   do {                                                                                                             \

@@ -121,14 +121,18 @@ def stream_handle(device: torch.device) -> int:
 
 # One scratch buffer per (device, stream): launches on one stream are ordered, so they may share
 # it; launches on different streams may overlap and must not.
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_workspaces: dict[tuple[int, int, str], torch.Tensor] = {}
 
 
-def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Zero-initialised scratch of at least ``nbytes`` for the current stream of ``device``."""
+def workspace(device: torch.device, nbytes: int, tag: str = "run") -> torch.Tensor:
+    """Zero-initialised scratch of at least ``nbytes`` for the current stream of ``device``.
+
+    ``tag`` separates kernel families whose scratch layouts differ: the decode kernels keep tickets
+    that must stay zero between launches where the GEMM keeps a converted copy of the activations,
+    so they never share a buffer."""
 
     index = device.index if device.index is not None else torch.cuda.current_device()
-    key = (index, stream_handle(device))
+    key = (index, stream_handle(device), tag)
     buffer = _workspaces.get(key)
     if buffer is None or buffer.numel() < nbytes:
         size = max(int(nbytes), 1 << 20)
@@ -141,13 +145,15 @@ def workspace_status(device: torch.device) -> int:
     """Status word of the current stream's scratch buffer (0 = every bounded wait completed)."""
 
     index = device.index if device.index is not None else torch.cuda.current_device()
-    buffer = _workspaces.get((index, stream_handle(device)))
-    if buffer is None:
-        return 0
-    value = ctypes.c_uint(0)
-    check(library().xqt_b200_workspace_status(buffer.data_ptr(), ctypes.byref(value), stream_handle(device)),
-          "xqt_b200_workspace_status")
-    return int(value.value)
+    worst = 0
+    for (dev_index, stream, _tag), buffer in list(_workspaces.items()):
+        if dev_index != index or stream != stream_handle(device):
+            continue
+        value = ctypes.c_uint(0)
+        check(library().xqt_b200_workspace_status(buffer.data_ptr(), ctypes.byref(value), stream_handle(device)),
+              "xqt_b200_workspace_status")
+        worst = max(worst, int(value.value))
+    return worst
 
 
 __all__ = [

@@ -248,7 +248,7 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
         if residual is not None and (residual.dtype != dtype or tuple(residual.shape) != (rows, n)
                                      or not residual.is_contiguous()):
             raise XQTBackendError("bound B200 W4A16 decode: residual must be contiguous [M,N] in the activation dtype")
-        scratch = native.workspace(device, nbytes)
+        scratch = native.workspace(device, nbytes, "decode")
         code = fn(x.data_ptr(), *head, native.ptr(residual), out.data_ptr(), *tail, scratch.data_ptr(),
                   scratch.numel(), torch.cuda.current_stream(device).cuda_stream)
         if code != 0:

@@ -129,7 +129,7 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
                                                    native.DTYPE_CODE[packed.dtype], stream), "xqt_b200_lowrank_down")
             if lora_scale != 1.0:
                 la.mul_(float(lora_scale))
-        scratch = native.workspace(device, 256)
+        scratch = native.workspace(device, 256, "gemm")
         native.check(lib.xqt_b200_w4a4_gemm(
             codes.data_ptr(), scales.data_ptr(), packed.qweight.data_ptr(), packed.aux.data_ptr(), la.data_ptr(),
             native.ptr(packed.bias), out.data_ptr(), m, n, k, native.DTYPE_CODE[packed.dtype], scratch.data_ptr(),

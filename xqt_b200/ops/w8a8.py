@@ -69,7 +69,7 @@ def w8a8_gemm(codes: torch.Tensor, act_scale: torch.Tensor, packed: PackedConvRo
         out = torch.empty((m, n), device=device, dtype=packed.dtype)
     if m == 0:
         return out
-    scratch = native.workspace(device, 256)
+    scratch = native.workspace(device, 256, "gemm")
     with torch.cuda.device(device):
         code = native.library().xqt_b200_w8a8_gemm(
             codes.data_ptr(), packed.qweight.data_ptr(), act_scale.data_ptr(), packed.weight_scales.data_ptr(),
