@@ -203,6 +203,8 @@ def run_gpu_arm(args) -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    # the launcher pins OMP_NUM_THREADS=1; the synthetic layers are quantised on the host
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // max(world, 1)))
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
@@ -303,17 +305,17 @@ def run_gpu_arm(args) -> None:
         barrier()
         ms_total = e0.elapsed_time(e1)
         timed_launches = launches
-        # keep the same load running until the clock sampler has seen at least ~0.5 s of it
-        t_end = time.perf_counter() + max(0.0, 0.5 - ms_total / 1e3)
-        i = 0
-        while time.perf_counter() < t_end:
+        if world > 1:
+            t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_total = float(t.item())
+        # keep the same load running until the clock sampler has seen about 0.5 s of it; the number of
+        # extra steps is derived from the agreed (max over ranks) time, so every rank replays the same
+        # count and the collectives inside the graphs stay matched
+        extra = int(max(0.0, 500.0 - ms_total) / max(ms_total / args.steps, 1e-3)) + 1
+        for i in range(min(extra, 20000)):
             step(i)
-            i += 1
-            torch.cuda.synchronize()
-    if world > 1:
-        t = torch.tensor([ms_total], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+        barrier()
     ms_per_step = ms_total / args.steps
     value = sweep_weight_bytes() / (ms_per_step * 1e-3) / 1e9
 
@@ -445,7 +447,7 @@ def measure_other_configs(device, world, rank, barrier) -> dict:
         bf16_peak = 1400.0
     hidden, inter = 4096, 14336
     mk = lambda n, k, s: quantize.quantize_w4_asymmetric(  # noqa: E731
-        torch.randn((n, k), generator=torch.Generator().manual_seed(s)) * 0.02, group_size=GROUP)
+        (torch.randn((n, k), generator=torch.Generator().manual_seed(s)) * 0.02).to(device), group_size=GROUP)
     block = W4A16SwiGLUMLP(mk(inter, hidden, 20), mk(inter, hidden, 21), mk(hidden, inter, 22), device=device,
                            rank=rank, world=world)
     mlp = []

@@ -14,7 +14,7 @@ module fills and consumes those fields:
 One process per GPU, ``torch.distributed`` for the plumbing; collectives run on the current stream
 after the kernels that feed them.  The local computation is injected (``local_linear``), so the
 partition arithmetic and the collective wiring are tested on CPU ranks with the gloo backend.
-No TMA multicast and no load from a peer's memory is used: peers' data arrive through NCCL only.
+Every kernel reads only its own GPU's memory: peers' data arrive through NCCL into local buffers.
 """
 
 from __future__ import annotations
