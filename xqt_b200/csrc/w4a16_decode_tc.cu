@@ -1,26 +1,39 @@
 // W4A16 decode (M <= 16) with the inner product on tcgen05: the Blackwell-native form of the
 // persistent stream-K decode kernel.
 //
-// Roles inside the one CTA per SM (320 threads):
-//   warps 0-3, 4-7  two dequantisation warpgroups.  Thread (warp % 4, lane) owns output channel
-//                   32*(warp%4)+lane of the 128-channel tile -- the same index as its tensor-memory
-//                   lane.  Per unit (one quantisation group: 128 or 64 K of its channel) it reads
-//                   its packed weights from the shared-memory stage, turns the nibbles into exact
-//                   bf16/fp16 integers (code - zero point, one lop3 + one sub per pair), stores
-//                   them to tensor memory as the A operand (tcgen05.st), and later drains the
-//                   16 fp32 results of the unit and folds them into its 16 running sums with the
-//                   group scale:  y[m] += s * sum_k x[m,k] (q[k] - z).
-//   warp 8          producer: per 256-K stage one bulk copy of the weights (16 KiB), one of the
-//                   scales/zero points, one tiled TMA load of the activations [16 x 256] into the
-//                   128-byte-swizzled layout tcgen05 reads (rows >= M arrive as zeros).
-//   warp 9          MMA issuer: for each unit, M=128 x N=16 x K=16 tcgen05.mma steps with A from
-//                   tensor memory and B (activations) from shared memory, committed to mbarriers.
+// Roles inside the one CTA per SM (19 warps, 608 threads):
+//   warps 0-15   four dequantisation warpgroups.  Thread (warp % 4, lane) owns output channel
+//                32*(warp%4)+lane of the 128-channel tile -- the same index as its tensor-memory
+//                lane.  A unit is 64 K of the 128 channels; warpgroup w takes unit w of every 256-K
+//                stage.  Per unit a thread reads its 32 packed bytes from the shared-memory stage,
+//                turns the nibbles into exact bf16/fp16 integers (code - zero point: shift, lop3 and
+//                one packed subtraction per pair), stores them to tensor memory as the A operand
+//                (one tcgen05.st of 32 columns), and two units later drains the 16 fp32 results of
+//                that unit and folds them into its 16 running sums with the group scale:
+//                y[m] += s * sum_k x[m,k] (q[k] - z).
+//   warp 16      producer: per stage one bulk copy of the weights (16 KiB), one of the scales and
+//                zero points, one tiled TMA load of the activations [16 x 256] into the
+//                128-byte-swizzled layout tcgen05 reads (rows >= M arrive as zeros).
+//   warps 17-18  MMA issuers, one per pair of warpgroups: M=128 x N=16 x K=16 tcgen05.mma steps
+//                with A from tensor memory and B (activations) from shared memory, committed to
+//                mbarriers.
+// Measured on B200, and what the structure follows from: one tcgen05.mma costs its issuing thread
+// about 44 cycles whatever its shape up to N=64 (27 when two threads issue), so a stage of 16 steps
+// needs two issuers; an mbarrier try_wait returns its predicate after about 150 cycles even when
+// the phase is complete, but independent polls pipeline, so every wait is one poll of everything
+// the step needs and only lane 0 of a warp polls; the loop is instruction-bound (about 340
+// warp-instructions per unit), hence four warpgroups and no divisions or generic loads inside it.
+// The kernel is launched with programmatic stream serialization: it lets the next kernel of the
+// stream start its set-up and weight prefetch early, and itself touches data of the previous
+// kernel (activations, scratch, outputs) only after griddepcontrol.wait.
 // The dequantised weight is an exact small integer, the scale is applied in fp32 to the fp32 group
 // sum, so the result equals the contract reference (xqt/kernels/ops/gemm/reference.py:263-271,527)
 // up to fp32 summation order.  Zero points must be integers in [0, 127] (true of every RTN / AWQ
 // checkpoint); other weights are served by the mma.sync decode kernel.
 // Stream-K partition, partial-sum scratch, ticket-elected finisher and bounded waits are those of
 // w4a16_decode.cu.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -38,27 +51,49 @@ using namespace sm100;
       reinterpret_cast<unsigned long long*>(p.status)[(slot)] = t__;                         \
     }                                                                                        \
   } while (0)
+// per-iteration SM cycle stamps of CTA 0: trace[role][iteration < 24][point < 8], kept in the unused
+// tail of the partial-sum scratch (slots of CTAs >= 160)
+#define XQT_TRACE_CLK(role, iter, point)                                                     \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && (iter) < 24u) {                                                   \
+      long long c__;                                                                         \
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(c__)::"memory");                          \
+      reinterpret_cast<long long*>(p.partials + (size_t)160 * 2 * 2048)[((role) * 24 + (iter)) * 8 + (point)] = c__; \
+    }                                                                                        \
+  } while (0)
 #else
 #define XQT_TRACE_AT(slot) do { } while (0)
+#define XQT_TRACE_CLK(role, iter, point) do { } while (0)
 #endif
 
 namespace dtc {
 constexpr int kTileRows = 128;
 constexpr int kStageK = 256;
-constexpr int kDequantThreads = 256;
-constexpr int kThreads = 320;
+constexpr int kUnitK = 64;                                 // K per unit: 32 tensor-memory columns, four MMA steps
+constexpr int kUnitsPerStage = kStageK / kUnitK;           // 4
+constexpr int kWG = 4;                                     // dequantisation warpgroups
+constexpr int kUnitsPerWg = kUnitsPerStage / kWG;          // units of a stage per warpgroup
+constexpr int kDequantThreads = kWG * 128;
+constexpr int kMmaWarps = 2;                               // each issues for kWG / kMmaWarps warpgroups
+constexpr int kProducerWarp = kWG * 4;
+constexpr int kFirstMmaWarp = kProducerWarp + 1;
+constexpr int kThreads = (kWG * 4 + 1 + kMmaWarps) * 32;
 constexpr int kWBytes = 128 * kStageK / 2;   // 16 KiB
 constexpr int kXBytes = 16 * kStageK * 2;    // 8 KiB: four 64-K atoms of [16 rows x 128 B]
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 216 * 1024;
 constexpr int kPartialFloats = 16 * kTileRows;
+constexpr int kRedFloats = (kWG - 1) * kPartialFloats;
 constexpr int kMaxTiles = 8192;
 constexpr int kMaxGrid = 256;
 constexpr uint32_t kTmemCols = 512;
 enum Status : unsigned int { kTimeout = 32 };
-constexpr int kNB = 3;   // tensor-memory buffers (A operand + result) per warpgroup: units in flight
-__host__ __device__ constexpr uint32_t a_col(int wg, int buf) { return wg * 240 + buf * 64; }
-__host__ __device__ constexpr uint32_t d_col(int wg, int buf) { return wg * 240 + 192 + buf * 16; }
+constexpr int kNB = 2;   // tensor-memory buffers (A operand + result) per warpgroup
+constexpr int kColsPerWg = kNB * (kUnitK / 2 + 16);
+static_assert(kWG * kColsPerWg <= (int)kTmemCols, "tensor memory budget");
+static_assert(kWG == 2 * kMmaWarps && kUnitsPerWg == 1, "each MMA issuer serves a pair of warpgroups, one unit each per stage");
+__host__ __device__ constexpr uint32_t a_col(int wg, int buf) { return wg * kColsPerWg + buf * (kUnitK / 2); }
+__host__ __device__ constexpr uint32_t d_col(int wg, int buf) { return wg * kColsPerWg + kNB * (kUnitK / 2) + buf * 16; }
 }  // namespace dtc
 
 struct DecodeTcParams {
@@ -83,7 +118,7 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void dq_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
+__device__ __forceinline__ void dq_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(dtc::kDequantThreads) : "memory"); }
 
 template <typename T>
 struct TcTraits;
@@ -110,63 +145,135 @@ struct TcTraits<__nv_bfloat16> {
   }
 };
 
+// nibbles i (low half) and i (high half) of `word` as the exact 16-bit integers code - zero
 template <typename T>
-__device__ __forceinline__ uint32_t dq_col(uint32_t word, int i, uint32_t off2) {
+__device__ __forceinline__ uint32_t dq_col(uint32_t word, int i, uint32_t off2, uint32_t magic) {
   using Tr = TcTraits<T>;
   uint32_t r;
-  asm("lop3.b32 %0, %1, %2, %3, 0xea;\n" : "=r"(r) : "r"(word >> (4 * i)), "n"(0x000f000f), "r"(Tr::kMagic));
+  asm("lop3.b32 %0, %1, %2, %3, 0xea;\n" : "=r"(r) : "r"(word >> (4 * i)), "n"(0x000f000f), "r"(magic));
   typename Tr::h2 v = __hsub2(*reinterpret_cast<typename Tr::h2*>(&r), *reinterpret_cast<const typename Tr::h2*>(&off2));
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__device__ __forceinline__ int cta_of_stage(long long x, long long total, int grid) {
-  return (int)(((x + 1) * grid - 1) / total);
+// shared-memory loads by 32-bit shared address (the stage pointers are computed, so generic loads
+// would be emitted otherwise)
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+// (scale, zero point) pair of one channel and group
+template <typename P>
+__device__ __forceinline__ void load_scale_zero(uint32_t addr, float& sc, float& zp);
+template <>
+__device__ __forceinline__ void load_scale_zero<__nv_bfloat16>(uint32_t addr, float& sc, float& zp) {
+  const uint32_t v = lds32(addr);
+  sc = __uint_as_float(v << 16);
+  zp = __uint_as_float(v & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void load_scale_zero<__half>(uint32_t addr, float& sc, float& zp) {
+  const uint32_t v = lds32(addr);
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+  sc = f.x;
+  zp = f.y;
+}
+template <>
+__device__ __forceinline__ void load_scale_zero<float>(uint32_t addr, float& sc, float& zp) {
+  sc = __uint_as_float(lds32(addr));
+  zp = __uint_as_float(lds32(addr + 4));
 }
 
-// GK: K per unit = quantisation group size (128 or 64)
+// a / b for non-negative operands; `small` (uniform) says both fit 32 bits, which avoids the long
+// software routine of the 64-bit division
+__device__ __forceinline__ long long div_nn(long long a, long long b, bool small) {
+  return small ? (long long)((uint32_t)a / (uint32_t)b) : a / b;
+}
+__device__ __forceinline__ int cta_of_stage(long long x, long long total, int grid, bool small) {
+  return (int)div_nn((x + 1) * grid - 1, total, small);
+}
+
+// GK: quantisation group size (128 or 64)
 template <typename T, typename P, bool SIGNED, int GK>
 __global__ void __launch_bounds__(dtc::kThreads, 1)
 w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcParams p) {
   using namespace dtc;
   using Tr = TcTraits<T>;
-  constexpr int kUnits = kStageK / GK;        // units per stage: 2 or 4
-  constexpr int kUnitsPerWg = kUnits / 2;
-  constexpr int kColsPerUnit = GK / 2;        // 32-bit tensor-memory columns of A per unit
   constexpr uint32_t kIdesc = umma_idesc(kAccF32, Tr::kFmt, Tr::kFmt, 128, 16);
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[2 * kMaxStages + 4 * kNB];
+  __shared__ __align__(8) unsigned long long bars[2 * kMaxStages + kWG * kNB + kMmaWarps * kNB];
   __shared__ uint32_t s_tmem_base;
   __shared__ unsigned int s_flag;
   __shared__ volatile unsigned int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grid = gridDim.x, cta = blockIdx.x;
-  const long long s_begin = (long long)cta * p.total / grid, s_end = (long long)(cta + 1) * p.total / grid;
+  const bool small = p.total * (long long)(grid + 1) < 0x7fffffffLL;
+  const long long s_begin = div_nn((long long)cta * p.total, grid, small), s_end = div_nn((long long)(cta + 1) * p.total, grid, small);
   const int ns = p.nstages;
   if (tid == 0) XQT_TRACE_AT(1);
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* red = reinterpret_cast<float*>(stages + (size_t)ns * p.stage_bytes);   // [16][128] fp32
+  float* red = reinterpret_cast<float*>(stages + (size_t)ns * p.stage_bytes);   // [kWG-1][16][128] fp32
   auto full_bar = [&](int s) { return smem_addr(&bars[s]); };
   auto empty_bar = [&](int s) { return smem_addr(&bars[kMaxStages + s]); };
   auto aready_bar = [&](int wg, int b) { return smem_addr(&bars[2 * kMaxStages + wg * kNB + b]); };
-  auto dready_bar = [&](int wg, int b) { return smem_addr(&bars[2 * kMaxStages + 2 * kNB + wg * kNB + b]); };
+  // results ready: one barrier per MMA issuer (pair of warpgroups) and buffer
+  auto dready_bar = [&](int wg, int b) { return smem_addr(&bars[2 * kMaxStages + kWG * kNB + (wg >> 1) * kNB + b]); };
 
-  if (tid == 0) {
+  // Producer state (used by one thread): running (tile, stage-in-tile, ring slot, ring phase) so that
+  // the loop has no divisions.
+  const uint32_t tx = kWBytes + kXBytes + p.sz_stage_bytes;
+  const long long units_per_tile = p.k / 128;
+  long long pr_tile = 0;
+  int pr_ks = 0, pr_slot = 0;
+  uint32_t pr_phase = 0;
+  // weights and scales of the next stage (they never depend on an earlier kernel) ...
+  auto issue_weights = [&]() {
+    unsigned char* st = stages + (size_t)pr_slot * p.stage_bytes;
+    const long long unit = pr_tile * units_per_tile + (long long)pr_ks * 2;   // first (tile, 128-K block)
+    mbar_expect_tx(full_bar(pr_slot), tx);
+    bulk_g2s(smem_addr(st + kXBytes), p.wt + unit * 8192, kWBytes, full_bar(pr_slot));
+    bulk_g2s(smem_addr(st + kXBytes + kWBytes), p.sz + unit * (p.sz_stage_bytes / 2), p.sz_stage_bytes, full_bar(pr_slot));
+  };
+  // ... and its activations, which may be the output of the kernel before this one
+  auto issue_acts = [&](int slot, int ks) {
+    tma_load_3d(smem_addr(stages + (size_t)slot * p.stage_bytes), &tm_x, 0, 0, ks * 4, full_bar(slot));
+  };
+  auto advance = [&]() {
+    if (++pr_ks == p.spt) { pr_ks = 0; ++pr_tile; }
+    if (++pr_slot == ns) { pr_slot = 0; pr_phase ^= 1; }
+  };
+  uint32_t pr_it = 0;
+
+  if (tid == kProducerWarp * 32) {
+    // The same thread initialises the barriers and at once requests the first stage, so that the
+    // first weights are on their way while the other warps are still setting up.
     s_abort = 0u;
     for (int i = 0; i < ns; ++i) {
       mbar_init(full_bar(i), 1);
-      mbar_init(empty_bar(i), 1);
+      mbar_init(empty_bar(i), kMmaWarps);   // one tcgen05.commit per MMA issuer
     }
-    for (int wg = 0; wg < 2; ++wg)
+    for (int wg = 0; wg < kWG; ++wg)
       for (int b = 0; b < kNB; ++b) {
-        mbar_init(aready_bar(wg, b), 4);   // one arrival per warp of the warpgroup
-        mbar_init(dready_bar(wg, b), 1);   // tcgen05.commit
+        mbar_init(aready_bar(wg, b), 4);                      // one arrival per warp of the warpgroup
+        if ((wg & 1) == 0) mbar_init(dready_bar(wg, b), 1);   // tcgen05.commit
       }
     fence_barrier_init();
     tma_prefetch_desc(&tm_x);
+    pr_tile = div_nn(s_begin, p.spt, small);
+    pr_ks = (int)(s_begin - pr_tile * p.spt);
+    if (s_begin < s_end) {   // the first weights go out before the CTA-wide barrier, the rest right after it
+      issue_weights();
+      XQT_TRACE_AT(3);
+    }
   }
-  if (warp == 9) {
+  if (warp == kFirstMmaWarp) {
     tmem_alloc(smem_addr(&s_tmem_base), kTmemCols);
     tmem_relinquish();
   }
@@ -175,60 +282,89 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   if (tid == 0) XQT_TRACE_AT(2);
+  // Programmatic dependent launch: the next kernel of the stream may start its own set-up and
+  // weight prefetch as soon as every CTA here has passed this point; everything of this kernel
+  // that reads or writes data of the previous one comes after the dependency wait (the producer
+  // thread waits later, after it has requested its first weights).
+  grid_launch_dependents();
+  if (tid != kProducerWarp * 32) grid_dependency_wait();
 
+  // Waits: the first poll is the fast path; the abort flag is consulted only when a wait has to spin,
+  // so that after one timeout the remaining waits of the CTA fall through quickly.
   auto guarded_wait = [&](uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return;
     if (s_abort == 0u && !mbar_wait(bar, parity)) {
       s_abort = 1u;
       atomicExch(p.status, (unsigned int)kTimeout);
     }
   };
+  auto guarded_wait2 = [&](uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b) {
+    if (mbar_try_wait2(bar_a, parity_a, bar_b, parity_b)) return;
+    if (s_abort == 0u && !mbar_wait2(bar_a, parity_a, bar_b, parity_b)) {
+      s_abort = 1u;
+      atomicExch(p.status, (unsigned int)kTimeout);
+    }
+  };
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ producer
-    if (elect_one()) {
-      const uint32_t tx = kWBytes + kXBytes + p.sz_stage_bytes;
-      uint32_t it = 0;
-      for (long long s = s_begin; s < s_end; ++s, ++it) {
-        const int slot = it % ns;
-        guarded_wait(empty_bar(slot), ((it / ns) & 1) ^ 1);
-        const long long tile = s / p.spt;
-        const int ks = (int)(s % p.spt);
-        unsigned char* st = stages + (size_t)slot * p.stage_bytes;
-        const long long unit = tile * (long long)(p.k / 128) + (long long)ks * 2;   // first (tile, 128-K block)
-        mbar_expect_tx(full_bar(slot), tx);
-        bulk_g2s(smem_addr(st + kXBytes), p.wt + unit * 8192, kWBytes, full_bar(slot));
-        bulk_g2s(smem_addr(st + kXBytes + kWBytes), p.sz + unit * (p.sz_stage_bytes / 2), p.sz_stage_bytes, full_bar(slot));
-        tma_load_3d(smem_addr(st), &tm_x, 0, 0, ks * 4, full_bar(slot));
-        if (it == 0) XQT_TRACE_AT(3);
+    if (lane == 0) {
+      // Fill the ring with weights first: under programmatic dependent launch this kernel may have
+      // started while the one before it (which may produce the activations) is still running.
+      const int ks0 = pr_ks;
+      long long s = s_begin;
+      for (; s < s_end && pr_it < (uint32_t)ns; ++s, ++pr_it) {
+        if (pr_it != 0) issue_weights();   // stage 0 went out before the barrier
+        advance();
+      }
+      grid_dependency_wait();
+      for (int j = 0, ks = ks0; j < (int)pr_it; ++j) {
+        issue_acts(j, ks);
+        if (++ks == p.spt) ks = 0;
+      }
+      for (; s < s_end; ++s, ++pr_it) {
+        guarded_wait(empty_bar(pr_slot), pr_phase ^ 1);
+        XQT_TRACE_CLK(3, pr_it, 0);
+        issue_weights();
+        issue_acts(pr_slot, pr_ks);
+        advance();
       }
       XQT_TRACE_AT(4);
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp >= kFirstMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuers
     if (elect_one()) {
+      const int wg0 = (warp - kFirstMmaWarp) * 2;   // the pair of warpgroups served
       uint32_t it = 0;
+      int slot = 0;
+      // No wait on the stage's own barrier: a warpgroup signals its unit only after it has seen the
+      // stage complete, and the activations arrive under the same barrier as the weights.
       for (long long s = s_begin; s < s_end; ++s, ++it) {
-        const int slot = it % ns;
-        guarded_wait(full_bar(slot), (it / ns) & 1);
-        if (it == 0) XQT_TRACE_AT(5);
         const uint32_t xbase = smem_addr(stages + (size_t)slot * p.stage_bytes);
+        const int buf = it & (kNB - 1);
+        const uint32_t bphase = (it / kNB) & 1;
+        guarded_wait2(aready_bar(wg0, buf), bphase, aready_bar(wg0 + 1, buf), bphase);
+        if (warp == kFirstMmaWarp) XQT_TRACE_CLK(2, it, 0);
+        if (it == 0) XQT_TRACE_AT(5);
+        tc_fence_after();
+        // The instruction rate, not the arithmetic, bounds these M=128 x N=16 x K=16 steps (each
+        // moves 4 KiB of A operand); the two units are interleaved only to keep the order fixed.
 #pragma unroll
-        for (int u = 0; u < kUnits; ++u) {
-          const int wg = u & 1;
-          const uint32_t iw = it * kUnitsPerWg + (u >> 1);   // this warpgroup's unit counter
-          const int buf = iw % kNB;
-          guarded_wait(aready_bar(wg, buf), (iw / kNB) & 1);
-          tc_fence_after();
+        for (int kk = 0; kk < kUnitK / 16; ++kk) {
 #pragma unroll
-          for (int kk = 0; kk < GK / 16; ++kk) {
-            const int koff = u * GK + kk * 16;               // K offset inside the stage
-            const uint64_t bdesc = umma_desc_sw128(xbase + (koff >> 6) * 2048 + (koff & 63) * 2);
+          for (int j = 0; j < 2; ++j) {
+            const int wg = wg0 + j;                     // 64-K unit of the stage == its swizzle atom
+            const uint64_t bdesc = umma_desc_sw128(xbase + wg * 2048 + kk * 32);
             umma_ts_f16(tmem_base + d_col(wg, buf), tmem_base + a_col(wg, buf) + kk * 8, bdesc, kIdesc, kk != 0 ? 1u : 0u);
           }
-          umma_commit(dready_bar(wg, buf));
-          if (it == 0 && u == 0) XQT_TRACE_AT(6);
         }
-        umma_commit(empty_bar(slot));   // all reads of this stage (weights by threads, activations by MMA) are done
+        if (warp == kFirstMmaWarp) XQT_TRACE_CLK(2, it, 1);
+        umma_commit(dready_bar(wg0, buf));
+        umma_commit(empty_bar(slot));   // this issuer's reads of the stage (activations) are done; the weights
+                                        // were consumed by the threads before they signalled the units ready
+        if (warp == kFirstMmaWarp) XQT_TRACE_CLK(2, it, 2);
+        if (it == 0) XQT_TRACE_AT(6);
+        if (++slot == ns) slot = 0;
       }
     }
   } else {
@@ -239,144 +375,181 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-    uint32_t iw = 0;        // units issued by this warpgroup
-    uint32_t drained = 0;   // units already folded into acc; units [drained, iw) are in tensor memory
-    float s_ring[kNB];      // their scales
-#pragma unroll
-    for (int i = 0; i < kNB; ++i) s_ring[i] = 0.f;
+    // Units of this warpgroup alternate between two tensor-memory buffers.  Up to two units are
+    // outstanding (stored, their MMAs possibly still running); the older one is folded into acc at
+    // the start of the next unit, a whole unit after it was handed to the MMA issuer.
+    uint32_t iw = 0;             // units issued
+    uint32_t drained = 0;        // units folded into acc
+    float s_even = 0.f, s_odd = 0.f;   // scales of the outstanding units, by buffer
 
-    auto drain = [&]() {
-      // fold the oldest outstanding unit of this warpgroup into the running sums
+    // fold unit `drained` into acc; `waited` says its barrier has already been observed
+    auto drain = [&](bool waited) {
       const uint32_t j = drained;
-      const int buf = j % kNB;
-      guarded_wait(dready_bar(wg, buf), (j / kNB) & 1);
+      const int b = j & (kNB - 1);
+      if (!waited) guarded_wait(dready_bar(wg, b), (j / kNB) & 1);
       tc_fence_after();
       uint32_t r[16];
-      tmem_ld_32x16(tmem_base + lane_addr + d_col(wg, buf), r);
-      tmem_wait_ld();
-      const float sc = buf == 0 ? s_ring[0] : (buf == 1 ? s_ring[1] : s_ring[2]);
+      tmem_ld_32x16(tmem_base + lane_addr + d_col(wg, b), r);
+      tmem_wait_ld_dep(r);
+      const float sc = b == 0 ? s_even : s_odd;
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = fmaf(sc, __uint_as_float(r[i]), acc[i]);
       ++drained;
     };
 
-    uint32_t it = 0;
+    const uint32_t stages_s = smem_addr(stages);
+    // the magic exponent pattern lives in a register the compiler cannot re-create per use
+    uint32_t magic;
+    asm volatile("mov.b32 %0, %1;\n" : "=r"(magic) : "n"(Tr::kMagic));
+    long long tile = div_nn(s_begin, p.spt, small);
+    int ks = (int)(s_begin - tile * p.spt);
+    int slot = 0;
+    uint32_t phase = 0, it = 0;
+    // the (at most two) tiles this CTA shares with other CTAs: who contributes, and in which of its
+    // two partial-sum slots the first contributor keeps this tile
+    struct Edge { long long tile; int c_first, c_last, first_seg; };
+    auto make_edge = [&](long long t) {
+      Edge e;
+      e.tile = t;
+      const long long t_first = t * p.spt;
+      e.c_first = cta_of_stage(t_first, p.total, grid, small);
+      e.c_last = cta_of_stage(t_first + p.spt - 1, p.total, grid, small);
+      e.first_seg = (div_nn((long long)e.c_first * p.total, grid, small) == t_first) ? 0 : 1;
+      return e;
+    };
+    const Edge edge_a = make_edge(tile), edge_b = make_edge(div_nn(s_end - 1, p.spt, small));
     for (long long s = s_begin; s < s_end; ++s, ++it) {
-      const int slot = it % ns;
-      const long long tile = s / p.spt;
-      const int ks = (int)(s % p.spt);
-      const unsigned char* st = stages + (size_t)slot * p.stage_bytes;
-      guarded_wait(full_bar(slot), (it / ns) & 1);
+      const uint32_t st_s = stages_s + (uint32_t)slot * (uint32_t)p.stage_bytes;
+      // one poll for both things this unit needs: the stage, and (two units later) the results of
+      // the unit whose tensor-memory buffers it will reuse
+      // Lane 0 polls for its warp (512 threads polling the same barriers queue up behind one another),
+      // the warp barrier hands the observation to the other lanes.
+      const bool due = iw - drained >= (uint32_t)kNB;
+      if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 5);
+      if (lane == 0) {
+        if (due) guarded_wait2(full_bar(slot), phase, dready_bar(wg, drained & (kNB - 1)), (drained / kNB) & 1);
+        else guarded_wait(full_bar(slot), phase);
+      }
+      if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 6);
+      __syncwarp();
+      if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 0);
+      if (++slot == ns) { slot = 0; phase ^= 1; }
 #pragma unroll
       for (int uu = 0; uu < kUnitsPerWg; ++uu) {
-        const int u = uu * 2 + wg;                       // unit of the stage handled by this warpgroup
-        const int kb = (u * GK) >> 7;                    // 128-K block of the stage
-        const int sub = ((u * GK) & 127) / GK;           // group inside the block
+        if (due) drain(true);                            // frees the buffers the new unit will use
+        const int u = uu * kWG + wg;                     // 64-K unit of the stage handled by this warpgroup
+        const int kb = u >> 1;                           // its 128-K block
+        const int sub = GK == 64 ? (u & 1) : 0;          // its group inside the block
         // scale and zero point of (channel, group)
-        const P* q = reinterpret_cast<const P*>(st + kXBytes + kWBytes) + ((size_t)(kb * (128 / GK) + sub) * kTileRows + ch) * 2;
-        const float sc = to_float<P>(q[0]);
-        const float zp = to_float<P>(q[1]);
+        float sc, zp;
+        load_scale_zero<P>(st_s + kXBytes + kWBytes + (uint32_t)(((kb * (128 / GK) + sub) * kTileRows + ch) * 2 * sizeof(P)), sc, zp);
         const uint32_t off2 = Tr::pair(Tr::kBase + zp + (SIGNED ? 8.f : 0.f));
-        // packed weights: [kblock][chunk][channel][16 B]; a chunk is 32 K
-        uint32_t cols[kColsPerUnit];
+        // packed weights: [kblock][chunk][channel][16 B]; a chunk is 32 K, a unit two chunks
+        const uint32_t wsrc = st_s + kXBytes + (uint32_t)(((kb * 4 + (u & 1) * 2) * kTileRows + ch) * 16);
+        const uint4 v0 = lds128(wsrc);
+        const uint4 v1 = lds128(wsrc + kTileRows * 16);
+        const uint32_t words[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const int buf = iw & (kNB - 1);
+        uint32_t cols[32];
 #pragma unroll
-        for (int c = 0; c < GK / 32; ++c) {
-          const int chunk = ((u * GK) & 127) / 32 + c;
-          const uint4 v = *reinterpret_cast<const uint4*>(st + kXBytes + ((size_t)(kb * 4 + chunk) * kTileRows + ch) * 16);
-          const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+        for (int w = 0; w < 8; ++w) {
+          const uint32_t word = SIGNED ? (words[w] ^ 0x88888888u) : words[w];
 #pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const uint32_t word = SIGNED ? (words[w] ^ 0x88888888u) : words[w];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) cols[c * 16 + w * 4 + i] = dq_col<T>(word, i, off2);
-          }
+          for (int i = 0; i < 4; ++i) cols[w * 4 + i] = dq_col<T>(word, i, off2, magic);
         }
-        // buffer iw % kNB was last used by unit iw - kNB: make sure that one has been drained
-        if (iw - drained >= (uint32_t)kNB) drain();
-        const int buf = iw % kNB;
-        const uint32_t a_addr = tmem_base + lane_addr + a_col(wg, buf);
-#pragma unroll
-        for (int c = 0; c < kColsPerUnit / 32; ++c) {
-          uint32_t chunk32[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) chunk32[i] = cols[c * 32 + i];
-          tmem_st_32x32(a_addr + c * 32, chunk32);
-        }
+        tmem_st_32x32(tmem_base + lane_addr + a_col(wg, buf), cols);
+        if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 1);
         tmem_wait_st();
+        if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 3);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(aready_bar(wg, buf));
-        if (buf == 0) s_ring[0] = sc; else if (buf == 1) s_ring[1] = sc; else s_ring[2] = sc;
+        if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 4);
+        if (buf == 0) s_even = sc; else s_odd = sc;
         ++iw;
       }
       if (tid == 0 && it == 0) XQT_TRACE_AT(7);
       if (tid == 0 && s == s_end - 1) XQT_TRACE_AT(8);
-      if (ks != p.spt - 1 && s != s_end - 1) continue;
+      const bool tile_end = (ks == p.spt - 1);
+      const long long cur_tile = tile;
+      if (++ks == p.spt) { ks = 0; ++tile; }
+      if (!tile_end && s != s_end - 1) continue;
 
       // ---------------------------------------------------------------- end of this CTA's run in `tile`
-      while (drained < iw) drain();
+      while (drained < iw) drain(false);
       if (tid == 0 && s == s_end - 1) XQT_TRACE_AT(9);
-      if (wg == 1) {
+      // combine the warpgroups' sums (fixed order)
+      if (wg != 0) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) red[i * kTileRows + ch] = acc[i];
+        for (int i = 0; i < 16; ++i) red[((wg - 1) * 16 + i) * kTileRows + ch] = acc[i];
       }
       dq_sync();
       if (wg == 0) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] += red[i * kTileRows + ch];
+        for (int g = 0; g < kWG - 1; ++g) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] += red[(g * 16 + i) * kTileRows + ch];
+        }
       }
-      const long long t_first = tile * p.spt, t_last = t_first + p.spt - 1;
-      const int c_first = cta_of_stage(t_first, p.total, grid), c_last = cta_of_stage(t_last, p.total, grid);
+      const bool at_a = cur_tile == edge_a.tile, at_b = cur_tile == edge_b.tile;
+      const int c_first = at_a ? edge_a.c_first : (at_b ? edge_b.c_first : cta);
+      const int c_last = at_a ? edge_a.c_last : (at_b ? edge_b.c_last : cta);
+      const int first_seg = at_a ? edge_a.first_seg : edge_b.first_seg;
       bool finish = true;
       if (c_first != c_last) {
-        const int seg = (s_begin / p.spt == tile) ? 0 : 1;
+        const int seg = at_a ? 0 : 1;
         float* mine = p.partials + ((size_t)cta * 2 + seg) * kPartialFloats;
         if (wg == 0) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             if (i < p.m) mine[i * kTileRows + ch] = acc[i];
-          __threadfence();
         }
         dq_sync();
-        if (tid == 0) s_flag = atomicAdd(&p.tickets[tile], 1u);
+        if (tid == 0) {
+          __threadfence();   // cumulative: publishes the partial sums the barrier has ordered before it
+          s_flag = atomicAdd(&p.tickets[cur_tile], 1u);
+        }
         dq_sync();
         finish = (s_flag == (unsigned int)(c_last - c_first));
         if (finish) {
           __threadfence();
-          // the two warpgroups add alternate contributors (always in the same order), then combine
+          // the warpgroups add interleaved contributors (always in the same order), then combine
 #pragma unroll
           for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-          // four contributors per batch: all their loads are in flight before the first add
-          for (int c0 = c_first + wg; c0 <= c_last; c0 += 8) {
-            float v[4][16];
+          // two contributors per batch: all their loads are in flight before the first add
+          for (int c0 = c_first + wg; c0 <= c_last; c0 += 2 * kWG) {
+            float v[2][16];
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const int c = c0 + 2 * b;
-              const int cseg = (((long long)c * p.total / grid) / p.spt == tile) ? 0 : 1;
+            for (int b = 0; b < 2; ++b) {
+              const int c = c0 + kWG * b;
+              const int cseg = c == c_first ? first_seg : 0;   // later contributors begin inside the tile
               const float* src = p.partials + ((size_t)c * 2 + cseg) * kPartialFloats;
 #pragma unroll
               for (int i = 0; i < 16; ++i) v[b][i] = (c <= c_last && i < p.m) ? __ldcg(src + i * kTileRows + ch) : 0.f;
             }
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
+            for (int b = 0; b < 2; ++b) {
 #pragma unroll
               for (int i = 0; i < 16; ++i) acc[i] += v[b][i];
             }
           }
-          if (wg == 1) {
+          if (wg != 0) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) red[i * kTileRows + ch] = acc[i];
+            for (int i = 0; i < 16; ++i) red[((wg - 1) * 16 + i) * kTileRows + ch] = acc[i];
           }
           dq_sync();
           if (wg == 0) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] += red[i * kTileRows + ch];
+            for (int g = 0; g < kWG - 1; ++g) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) acc[i] += red[(g * 16 + i) * kTileRows + ch];
+            }
           }
-          if (tid == 0) p.tickets[tile] = 0u;
+          if (tid == 0) p.tickets[cur_tile] = 0u;
         }
       }
       if (finish && wg == 0) {
-        const long long chn = tile * kTileRows + ch;
+        const long long chn = cur_tile * kTileRows + ch;
         if (chn < p.n) {
           T* out = reinterpret_cast<T*>(p.out);
           const T* res = reinterpret_cast<const T*>(p.residual);
@@ -393,6 +566,8 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
           }
         }
       }
+      // `red` is reused at the next tile end: nobody may overwrite it before warpgroup 0 has read it
+      dq_sync();
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
     }
@@ -400,7 +575,7 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
   if (tid == 0) XQT_TRACE_AT(10);
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kFirstMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
   if (tid == 0) XQT_TRACE_AT(11);
 }
 
@@ -451,18 +626,41 @@ bool w4a16_decode_tc_supported(int m, int n, int k, int group_size) {
          ceil_div(n, kTileRows) <= kMaxTiles;
 }
 
+// XQT_B200_PDL=0 in the environment launches the kernel without the programmatic-dependency
+// attribute (the in-kernel dependency instructions are then no-ops).
+static bool dependent_launch_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* v = getenv("XQT_B200_PDL");
+    state = (v != nullptr && v[0] == '0') ? 0 : 1;
+  }
+  return state == 1;
+}
+
 template <typename T, typename P>
 static int dtc_launch(const CUtensorMap& tm, const DecodeTcParams& p, int group_size, bool is_signed, int grid,
                       size_t smem_bytes, cudaStream_t stream) {
 #define XQT_DTC(SG, GKV)                                                                                     \
   do {                                                                                                       \
     auto kern = w4a16_decode_tc_kernel<T, P, SG, GKV>;                                                       \
-    static bool configured = false;                                                                          \
-    if (!configured) {                                                                                       \
+    static bool configured[64] = {};                                                                         \
+    int dev = 0;                                                                                             \
+    XQT_CUDA(cudaGetDevice(&dev));                                                                           \
+    if (dev < 0 || dev >= 64 || !configured[dev]) {                                                          \
       XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dtc::kSmemBudget));   \
-      configured = true;                                                                                     \
+      if (dev >= 0 && dev < 64) configured[dev] = true;                                                      \
     }                                                                                                        \
-    kern<<<grid, dtc::kThreads, smem_bytes, stream>>>(tm, p);                                                \
+    cudaLaunchConfig_t cfg = {};                                                                             \
+    cfg.gridDim = dim3((unsigned)grid);                                                                      \
+    cfg.blockDim = dim3(dtc::kThreads);                                                                      \
+    cfg.dynamicSmemBytes = smem_bytes;                                                                       \
+    cfg.stream = stream;                                                                                     \
+    cudaLaunchAttribute attr[1];                                                                             \
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                         \
+    attr[0].val.programmaticStreamSerializationAllowed = 1;                                                  \
+    cfg.attrs = attr;                                                                                        \
+    cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;                                                       \
+    XQT_CUDA(cudaLaunchKernelEx(&cfg, kern, tm, p));                                                         \
   } while (0)
   if (group_size == 128) {
     if (is_signed) XQT_DTC(true, 128); else XQT_DTC(false, 128);
@@ -495,7 +693,7 @@ int w4a16_decode_tc_launch(const void* x, const void* wt, const void* sz, const 
   p.total = (long long)p.tiles * p.spt;
   p.sz_stage_bytes = 2 * (128 / group_size) * kTileRows * 2 * psize;
   p.stage_bytes = (kXBytes + kWBytes + p.sz_stage_bytes + 1023) / 1024 * 1024;
-  int ns = (kSmemBudget - 1024 - kPartialFloats * 4) / p.stage_bytes;
+  int ns = (kSmemBudget - 1024 - kRedFloats * 4) / p.stage_bytes;
   p.nstages = ns > kMaxStages ? kMaxStages : ns;
   XQT_REQUIRE(p.nstages >= 2);
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
@@ -505,7 +703,7 @@ int w4a16_decode_tc_launch(const void* x, const void* wt, const void* sz, const 
   long long grid = dtc_sm_count();
   if (grid > kMaxGrid) grid = kMaxGrid;
   if (grid > p.total) grid = p.total;
-  const size_t smem_bytes = (size_t)p.nstages * p.stage_bytes + kPartialFloats * 4 + 1024;
+  const size_t smem_bytes = (size_t)p.nstages * p.stage_bytes + kRedFloats * 4 + 1024;
   const bool sg = nibble_signed != 0;
   if (act_dtype == XQT_B200_BF16) {
     if (param_dtype == XQT_B200_BF16) return dtc_launch<__nv_bfloat16, __nv_bfloat16>(tm, p, group_size, sg, (int)grid, smem_bytes, stream);
