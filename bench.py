@@ -29,6 +29,7 @@ import threading
 import time
 
 ROOT = pathlib.Path(__file__).resolve().parent
+_T0 = time.perf_counter()
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
@@ -43,6 +44,12 @@ L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_tc_kernel launch from the committed
 # ncu capture (profiles/), or None while no capture backs it
 NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def _log(msg: str) -> None:
+    """Progress marker on stderr (rank-tagged), so that a stalled multi-rank run shows where it stopped."""
+
+    print(f"[bench rank {os.environ.get('RANK', '0')} +{time.perf_counter() - _T0:.1f}s] {msg}", file=sys.stderr, flush=True)
 
 
 def weight_aux_bytes(k: int, n: int) -> int:
@@ -207,6 +214,7 @@ def run_gpu_arm(args) -> None:
     torch.set_num_threads(max(1, (os.cpu_count() or 1) // max(world, 1)))
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    _log(f"process group ready (world {world})")
 
     # --- synthetic layers: POOL device copies of every (sharded) layer, rotated to defeat L2
     cpu_layers = {(k, n): make_layer(k, n, 10 + i) for i, (k, n) in enumerate(SHAPES)}
@@ -241,48 +249,55 @@ def run_gpu_arm(args) -> None:
         for (k, n) in SHAPES:
             for m in MS:
                 bound[(copy, k, n, m)] = bind_w4a16_decode(dev_layers[copy][(k, n)], rows=m, dtype=torch.bfloat16)
-    outputs = {(n, m): torch.empty((m, n // world), device=device, dtype=torch.bfloat16) for _, n in SHAPES for m in MS}
-    gathered = {(n, m): torch.empty((world * m, n // world), device=device, dtype=torch.bfloat16)
-                for _, n in SHAPES for m in MS} if world > 1 else {}
+    # Every problem's local output [m, n/world] is a slice of one packed buffer; with more than one
+    # rank the packed buffer of a step is gathered with one NCCL all-gather (column-parallel layers).
+    sizes = {(n, m): m * (n // world) for _, n in SHAPES for m in MS}
+    packed = torch.empty(sum(sizes.values()), device=device, dtype=torch.bfloat16)
+    outputs, off = {}, 0
+    for key, count in sizes.items():
+        outputs[key] = packed[off:off + count].view(key[1], key[0] // world)
+        off += count
+    packed_all = torch.empty((world, packed.numel()), device=device, dtype=torch.bfloat16) if world > 1 else None
     launches = 0
+
+    def gather_step():
+        if world > 1:
+            dist.all_gather_into_tensor(packed_all.view(-1), packed)
 
     def one_problem(copy, k, n, m, x):
         nonlocal launches
         y = bound[(copy, k, n, m)](x, outputs[(n, m)])
         launches += 1
-        if world > 1:
-            buf = gathered[(n, m)]
-            dist.all_gather_into_tensor(buf, y)
-            return buf.reshape(world, m, n // world).permute(1, 0, 2).reshape(m, n)
         return y
 
-    def eager_step(i):
+    def local_step(i):
         copy = i % pool
-        out = None
         for (k, n) in SHAPES:
             for m in MS:
-                out = one_problem(copy, k, n, m, dev_inputs[(k, m)])
-        return out
+                one_problem(copy, k, n, m, dev_inputs[(k, m)])
 
-    # the launch-bound step (16 kernels of a few microseconds) is captured in CUDA graphs, one per
-    # pool copy; the timed region replays them
+    # the launch-bound local part of a step (16 kernels of a few microseconds) is captured in CUDA
+    # graphs, one per pool copy; the timed region replays them.  Collectives stay outside the graphs.
+    _log(f"layers ready: pool={pool}, warm-up launches")
     side = torch.cuda.Stream(device)
     graphs = []
     with torch.cuda.stream(side):
         for i in range(pool):
-            eager_step(i)
+            local_step(i)
         side.synchronize()
         for i in range(pool):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                eager_step(i)
+                local_step(i)
             graphs.append(graph)
     torch.cuda.synchronize()
+    _log("graphs captured")
     launches_per_step = len(SHAPES) * len(MS)
 
     def step(i):
         nonlocal launches
         graphs[i % pool].replay()
+        gather_step()
         launches += launches_per_step
 
     def barrier():
@@ -320,19 +335,22 @@ def run_gpu_arm(args) -> None:
     value = sweep_weight_bytes() / (ms_per_step * 1e-3) / 1e9
 
     # --- end to end through the public API with host buffers
-    host_out = {(n, m): torch.empty((m, n), dtype=torch.bfloat16).pin_memory() for _, n in SHAPES for m in MS}
+    result = packed_all if world > 1 else packed          # what the caller reads back: all ranks' columns
+    host_out = torch.empty(result.shape, dtype=torch.bfloat16).pin_memory()
     h2d = sum(inputs[(k, m)].numel() * 2 for k, _ in SHAPES for m in MS)
-    d2h = sum(m * n * 2 for _, n in SHAPES for m in MS)
+    d2h = result.numel() * 2
 
     def e2e_step(i):
         copy = i % pool
         for (k, n) in SHAPES:
             for m in MS:
                 x = host_inputs[(k, m)].to(device, non_blocking=True)
-                y = one_problem(copy, k, n, m, x)
-                host_out[(n, m)].copy_(y, non_blocking=True)
+                one_problem(copy, k, n, m, x)
+        gather_step()
+        host_out.copy_(result, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
+    _log("timed region done; end-to-end arm")
     for i in range(3):
         e2e_step(i)
     barrier()
@@ -348,7 +366,8 @@ def run_gpu_arm(args) -> None:
         e2e_ms = float(t.item())
     e2e_value = sweep_weight_bytes() / (e2e_ms / args.steps * 1e-3) / 1e9
 
-    # --- per-problem detail: each kernel timed alone, weights rotated through the pool
+    _log("end-to-end done; per-problem detail")
+    # --- per-problem detail: each (local) kernel timed alone, weights rotated through the pool
     peak, peak_kind = measured_peak()
     detail = []
     reps = 10
@@ -371,7 +390,9 @@ def run_gpu_arm(args) -> None:
                 nb = algorithmic_bytes(k, n // world, m)
                 detail.append({"k": k, "n": n, "m": m, "us": round(us, 3), "gbs": round(nb / us / 1e3, 1),
                                "frac": round(nb / us / 1e3 / peak, 4)})
+    _log("detail done; other configurations")
     extras = measure_other_configs(device, world, rank, barrier)
+    _log("other configurations done")
     alg_bytes_step = sum(algorithmic_bytes(k, n // world, m) for k, n in SHAPES for m in MS)
     achieved = alg_bytes_step / (ms_per_step * 1e-3) / 1e9
 
@@ -385,7 +406,7 @@ def run_gpu_arm(args) -> None:
         "dtype": "bf16", "data": "synthetic",
         "config": {
             "workload": "w4a16_decode_gemv_sweep", "shapes_kn": SHAPES, "m": MS, "group_size": GROUP,
-            "weight_scheme": "uint4 RTN, bf16 scale+zero", "parallelism": "single" if world == 1 else f"column-parallel x{world} + all-gather",
+            "weight_scheme": "uint4 RTN, bf16 scale+zero", "parallelism": "single" if world == 1 else f"column-parallel x{world}, one NCCL all-gather of the step's outputs per step",
             "l2": f"weights rotated through a pool of {pool} copies ({pool * bytes_per_copy / 1e6:.0f} MB > 126 MB L2)",
         },
         "roofline": {
@@ -454,6 +475,7 @@ def measure_other_configs(device, world, rank, barrier) -> dict:
     for m in (1, 16, 512, 4096):
         x = torch.randn((m, hidden), device=device, dtype=torch.bfloat16)
         us = _time_us(lambda: block(x), barrier, reps=20 if m <= 512 else 5)
+        _log(f"mlp m={m}: {us:.1f} us")
         if world > 1:
             t = torch.tensor([us], device=device, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
