@@ -43,7 +43,10 @@ UNIT = "GB/s"
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_tc_kernel launch from the committed
 # ncu capture (profiles/), or None while no capture backs it
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_tc_kernel launch (K=4096, N=14336, M=16:
+# 31,410,688 bytes, see profiles/) over that launch's algorithmic bytes; traffic grows with the weight bytes, so
+# the step's average launch is scaled by this ratio
+NCU_TRAFFIC_RATIO = 31410688 / 31784960
 
 
 def _log(msg: str) -> None:
@@ -411,8 +414,8 @@ def run_gpu_arm(args) -> None:
         },
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peak_kind}",
-            "kernel": "w4a16_decode_tc_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank)",
+            "traffic": round(NCU_TRAFFIC_RATIO * alg_bytes_step / (len(SHAPES) * len(MS))), "peak_source": f"of {peak_kind}",
+            "kernel": "w4a16_decode_tc_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank); traffic = bytes of the average launch, scaled from one ncu capture",
         },
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -535,6 +538,53 @@ def measure_other_configs(device, world, rank, barrier) -> dict:
     return out
 
 
+def run_single_case(args) -> None:
+    """One of the other configurations alone, a few eager calls: the small command used for ncu
+    captures of the GEMM-shaped kernels (`--case mlp:M`, `--case w8a8`, `--case w4a4`)."""
+
+    from xqt_b200 import quantize
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    name, _, arg = args.case.partition(":")
+    if name == "mlp":
+        from xqt_b200.ops.mlp import W4A16SwiGLUMLP
+
+        m, hidden, inter = int(arg or 4096), 4096, 14336
+        mk = lambda n, k, s: quantize.quantize_w4_asymmetric(  # noqa: E731
+            (torch.randn((n, k), generator=torch.Generator().manual_seed(s)) * 0.02).to(device), group_size=GROUP)
+        block = W4A16SwiGLUMLP(mk(inter, hidden, 20), mk(inter, hidden, 21), mk(hidden, inter, 22), device=device)
+        x = torch.randn((m, hidden), device=device, dtype=torch.bfloat16)
+        fn = lambda: block(x)  # noqa: E731
+        work = 2.0 * m * 3 * inter * hidden
+    elif name == "w8a8":
+        from xqt_b200.ops.activation import rotate_quantize
+        from xqt_b200.ops.w8a8 import convrot_w8a8_linear, pack_convrot_w8a8_linear
+
+        m, n, k = 2048, 4096, 4096
+        rot = quantize.regular_rotation(256)
+        w = torch.randn((n, k), generator=torch.Generator().manual_seed(6)) * 0.02
+        q, sc = quantize.quantize_w8_per_channel(rot.apply(w))
+        packed = pack_convrot_w8a8_linear(q.t().contiguous().to(device), sc.to(device), None, dtype=torch.bfloat16)
+        x = torch.randn((m, k), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(device)
+        fn = lambda: convrot_w8a8_linear(x, packed, rot_size=256)  # noqa: E731
+        work = 2.0 * m * n * k
+    elif name == "w4a4":
+        from xqt_b200.ops.w4a4 import pack_svdq_w4a4_linear, svdq_w4a4_linear
+
+        m, n, k, r = 4096, 12288, 3072, 32
+        rot4 = quantize.randomized_rotation(128, seed=3)
+        layer = pack_svdq_w4a4_linear(torch.randn((n, k), device=device) * 0.02, torch.randn((r, k), device=device) * 0.05,
+                                      torch.randn((n, r), device=device) * 0.05, None, rotation=rot4)
+        x4 = torch.randn((m, k), device=device, dtype=torch.bfloat16)
+        fn = lambda: svdq_w4a4_linear(x4, layer)  # noqa: E731
+        work = 2.0 * m * n * k
+    else:
+        raise SystemExit(f"unknown --case {args.case!r}")
+    us = _time_us(fn, torch.cuda.synchronize, reps=max(1, args.steps), warm=max(1, args.warmup))
+    print(json.dumps({"case": args.case, "us_per_call": us, "tera_ops_per_s": work / us / 1e6}), flush=True)
+
+
 def run_single_problem(args) -> None:
     """One decode problem, `steps` eager launches over a weight pool larger than L2."""
 
@@ -572,9 +622,13 @@ def main() -> None:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--problem", default=None,
                         help="K,N,M: run only this decode problem, eagerly (the small case used for ncu captures)")
+    parser.add_argument("--case", default=None,
+                        help="mlp:M, w8a8 or w4a4: run only that configuration, eagerly (small command for ncu captures)")
     args = parser.parse_args()
     if args.problem is not None:
         run_single_problem(args)
+    elif args.case is not None:
+        run_single_case(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:
