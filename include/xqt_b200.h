@@ -93,6 +93,13 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
 int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_size,
                                   int epilogue_activation, int has_residual);
 
+/* 1 when XQT_B200_VARIANT_TCGEN05 serves this M in two passes (weights dequantised once per call
+ * into an fp16 scratch in fp32 arithmetic, then a dense tcgen05 GEMM): in that form any zero
+ * point is accepted, integer or not, and xqt_b200_w4a16_workspace_bytes includes N*K*2 bytes for
+ * the scratch.  The single-pass form (smaller M) needs integer zero points.  No counterpart in
+ * xqt: its sm_89 GEMM has one form (xqt/kernels/ops/_impl/cute/awq_w4a16_sm89.py:225-262). */
+int xqt_b200_w4a16_two_pass(int m);
+
 /* ------------------------------------------------------------------------------------------
  * W4A16 decode (M <= 16) on the tile-ordered execution layout b200_w4_tile128_v1.
  *

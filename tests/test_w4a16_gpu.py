@@ -243,6 +243,35 @@ def test_gemm_tcgen05_groups_signed_epilogue(group, symmetric):
     assert oracle.rel_l2(out, ref) <= TOL
 
 
+@pytest.mark.parametrize("group,symmetric", [(64, False), (128, True), (128, False)])
+def test_gemm_two_pass_groups_signed_epilogue(group, symmetric):
+    """M >= 256: weights dequantised once into an fp16 scratch, then the dense tcgen05 GEMM."""
+
+    from xqt_b200 import native
+
+    m, n, k = 300, 264, 768
+    assert native.library().xqt_b200_w4a16_two_pass(m) == 1 and native.library().xqt_b200_w4a16_two_pass(255) == 0
+    x, pw = _synthetic(n, k, m, seed=35, symmetric=symmetric, group=group, param_dtype=torch.float32)
+    bias = torch.randn((n,), generator=seeded(8))
+    residual = torch.randn((m, n), generator=seeded(9)).to(torch.bfloat16)
+    out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=group, signed=symmetric, bias=bias,
+               residual=residual, variant="tcgen05")
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=group, signed=symmetric, bias=bias,
+                      residual=residual)
+    assert oracle.rel_l2(out, ref) <= TOL
+
+
+def test_gemm_two_pass_serves_non_integer_zero_points():
+    m, n, k = 320, 128, 256
+    x, pw = _synthetic(n, k, m, seed=45, param_dtype=torch.float32)
+    zeros = pw.zero_points + 0.25
+    out = _run(x, pw.qweight, pw.scales, zeros, group=128, signed=False, variant="tcgen05")
+    ref = oracle.gemm(x, pw.qweight, pw.scales, zeros, group_size=128, signed=False)
+    assert oracle.rel_l2(out, ref) <= TOL
+    auto = _run(x, pw.qweight, pw.scales, zeros, group=128, signed=False)
+    assert torch.equal(auto, out)          # auto takes the same two-pass kernel at this M
+
+
 def test_gemm_non_integer_zero_points_take_the_exact_path():
     m, n, k = 64, 128, 256
     x, pw = _synthetic(n, k, m, seed=44, param_dtype=torch.float32)

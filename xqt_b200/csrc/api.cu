@@ -23,7 +23,8 @@ bool w4a16_decode_tc_supported(int m, int n, int k, int group_size);
 int w4a16_gemm_tc_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int,
                          int, int, int, int, int, int, void*, size_t, cudaStream_t);
 int swiglu_launch(const void*, void*, int, int, int, cudaStream_t);
-size_t w4a16_gemm_tc_workspace_bytes(int m, int k);
+size_t w4a16_gemm_tc_workspace_bytes(int m, int n, int k);
+bool w4a16_gemm_tc_any_zero_point(int m);
 bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size);
 int lowrank_down_launch(const void*, const void*, float*, int, int, int, cudaStream_t);
 int w4a4_gemm_launch(const void*, const float*, const void*, const void*, const float*, const float*, void*, int, int, int,
@@ -53,7 +54,7 @@ int xqt_b200_device_supported(int device) {
 size_t xqt_b200_w4a16_workspace_bytes(int m, int n, int k) {
   if (n <= 0 || k <= 0) return 0;
   const size_t a = w4a16_gemv_workspace_bytes(n, k);
-  const size_t b = m > 16 ? w4a16_gemm_tc_workspace_bytes(m, k) : 0;   // fp16 copy of bf16 activations
+  const size_t b = m > 16 ? w4a16_gemm_tc_workspace_bytes(m, n, k) : 0;   // fp16 activations (+ fp16 weights at large M)
   return a > b ? a : b;
 }
 
@@ -66,6 +67,8 @@ int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_s
     return XQT_B200_VARIANT_TCGEN05;
   return XQT_B200_VARIANT_SIMT;
 }
+
+int xqt_b200_w4a16_two_pass(int m) { return w4a16_gemm_tc_any_zero_point(m) ? 1 : 0; }
 
 int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* scales, const void* zero_points,
                        const float* bias, const void* residual, void* output, int m, int n, int k, int padded_k,
@@ -91,7 +94,9 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
     variant = xqt_b200_w4a16_select_variant(m, n, k, padded_k, group_size, epilogue_activation, residual != nullptr);
     // the tensor-core GEMM folds the zero point into an exact integer subtraction: only a caller who
     // knows its zero points are integers may ask for it; AUTO takes it for symmetric weights only
-    if (variant == XQT_B200_VARIANT_TCGEN05 && zero_points != nullptr) variant = XQT_B200_VARIANT_SIMT;
+    // (at large M the weights are dequantised in fp32 first, which serves any zero point)
+    if (variant == XQT_B200_VARIANT_TCGEN05 && zero_points != nullptr && !w4a16_gemm_tc_any_zero_point(m))
+      variant = XQT_B200_VARIANT_SIMT;
   }
   cudaStream_t s = (cudaStream_t)stream;
   switch (variant) {

@@ -33,6 +33,8 @@ struct GemmTcParams {
   const float* row_scale;   // [M]  activation scale per token
   const float* col_scale;   // [N]  weight scale per output channel
   const float* bias;        // [N] or null
+  const void* residual;     // [M, N] in the output dtype or null (fp16 kind only)
+  int out_f32;              // fp16 kind only: 1 = the output is fp32 (partial sums of a K-sharded layer)
   void* out;                // [M, N]
   unsigned int* status;
 };
@@ -58,9 +60,10 @@ __device__ __forceinline__ void store8<__half>(__half* dst, const float (&v)[8])
   *reinterpret_cast<uint4*>(dst) = o;
 }
 
-template <int BN, typename OutT>
-__global__ void __launch_bounds__(gemm::kThreads, 1)
-gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmTcParams p) {
+// I8: int8 operands, int32 accumulators, scaled epilogue.  Otherwise fp16 operands, fp32
+// accumulators, epilogue acc (+ bias) (+ residual).
+template <int BN, typename OutT, bool I8>
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmTcParams& p) {
   using namespace gemm;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStages + 4];
@@ -69,7 +72,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   constexpr int kABytes = kBM * kRowBytes, kBBytes = BN * kRowBytes, kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = 2 * BN;
-  constexpr uint32_t kIdesc = umma_idesc(kAccS32, kFmtS8, kFmtS8, kBM, BN);
+  constexpr uint32_t kIdesc = I8 ? umma_idesc(kAccS32, kFmtS8, kFmtS8, kBM, BN) : umma_idesc(kAccF32, kFmtF16, kFmtF16, kBM, BN);
+  constexpr int kElemsPerRow = I8 ? kRowBytes : kRowBytes / 2;   // K elements per 128-byte swizzle row
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ns = p.stages;
@@ -122,30 +126,38 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           guarded_wait(empty_bar(s), ((it / ns) & 1) ^ 1);
           unsigned char* st = tiles + (size_t)s * kStageBytes;
           mbar_expect_tx(full_bar(s), kStageBytes);
-          tma_load_2d(smem_addr(st), &tm_a, kb * kRowBytes, m0, full_bar(s));
-          tma_load_2d(smem_addr(st + kABytes), &tm_b, kb * kRowBytes, n0, full_bar(s));
+          tma_load_2d(smem_addr(st), &tm_a, kb * kElemsPerRow, m0, full_bar(s));
+          tma_load_2d(smem_addr(st + kABytes), &tm_b, kb * kElemsPerRow, n0, full_bar(s));
         }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      uint32_t it = 0, local = 0;
+      uint32_t local = 0, phase = 0;
+      int s = 0;
+      bool ready = false;   // the current stage's barrier has already been seen complete
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
         const int buf = local & 1;
         guarded_wait(tempty_bar(buf), ((local >> 1) & 1) ^ 1);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = it % ns;
-          guarded_wait(full_bar(s), (it / ns) & 1);
+        const bool last_tile = tile + (int)gridDim.x >= total_tiles;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!ready) guarded_wait(full_bar(s), phase);
           tc_fence_after();
           const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
           const uint64_t adesc = umma_desc_sw128(a_addr), bdesc = umma_desc_sw128(a_addr + kABytes);
-#pragma unroll
-          for (int k = 0; k < kRowBytes / 32; ++k)  // 32 bytes of K per MMA: the descriptor start advances by 2 units
-            umma_ss<true>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
-          umma_commit(empty_bar(s));     // the stage is free once these MMAs have read it
+          // the next stage in ring order (the first of the next tile after the last K block)
+          int sn = s + 1;
+          uint32_t pn = phase;
+          if (sn == ns) { sn = 0; pn ^= 1; }
+          // four 32-byte K steps, the commit that frees the stage, and the poll of the next stage's
+          // barrier in one go: the poll's round trip is hidden behind the MMA issue
+          ready = umma_ss_x4_commit_poll<I8>(d_tmem, adesc, bdesc, kIdesc, kb != 0 ? 1u : 0u, empty_bar(s), full_bar(sn), pn);
+          if (last_tile && kb == p.kblocks - 1) ready = false;
+          s = sn;
+          phase = pn;
         }
         umma_commit(tfull_bar(buf));      // accumulator complete
       }
@@ -161,7 +173,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       guarded_wait(tfull_bar(buf), (local >> 1) & 1);
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      const float rs = row < p.m ? __ldg(p.row_scale + row) : 0.f;
+      float rs = 0.f;
+      if (I8) rs = row < p.m ? __ldg(p.row_scale + row) : 0.f;
+      const OutT* res = reinterpret_cast<const OutT*>(p.residual);
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -174,12 +188,34 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int col = n0 + c * 32 + j * 8;
             if (col < p.n) {   // N is a multiple of 8
               float v[8];
+              if (I8) {
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                v[e] = (float)(int)r[j * 8 + e] * (rs * __ldg(p.col_scale + col + e));
-                if (p.bias != nullptr) v[e] += __ldg(p.bias + col + e);
+                for (int e = 0; e < 8; ++e) {
+                  v[e] = (float)(int)r[j * 8 + e] * (rs * __ldg(p.col_scale + col + e));
+                  if (p.bias != nullptr) v[e] += __ldg(p.bias + col + e);
+                }
+                store8<OutT>(out + (size_t)row * p.n + col, v);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j * 8 + e]);
+                if (p.bias != nullptr) {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[e] += __ldg(p.bias + col + e);
+                }
+                if (res != nullptr) {
+                  const uint4 raw = *reinterpret_cast<const uint4*>(res + (size_t)row * p.n + col);
+                  const OutT* re = reinterpret_cast<const OutT*>(&raw);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[e] += to_float<OutT>(re[e]);
+                }
+                if (p.out_f32) {
+                  float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)row * p.n + col);
+                  dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+                  dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+                } else {
+                  store8<OutT>(out + (size_t)row * p.n + col, v);
+                }
               }
-              store8<OutT>(out + (size_t)row * p.n + col, v);
             }
           }
         }
@@ -192,6 +228,20 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(gemm::kThreads, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmTcParams p) {
+  gemm_tc_body<BN, OutT, true>(tm_a, tm_b, p);
+}
+
+// fp16 x fp16 -> fp32: the second pass of the W4A16 linear at large M (weights dequantised once per
+// call into an fp16 scratch by dequant_w4_f16_kernel)
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(gemm::kThreads, 1)
+gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmTcParams p) {
+  gemm_tc_body<BN, OutT, false>(tm_a, tm_b, p);
 }
 
 // ----------------------------------------------------------------------------------------- host
@@ -235,25 +285,24 @@ static int sm_count_now() {
   return v;
 }
 
-template <int BN, typename OutT>
-static int launch_i8(const void* a, const void* b, GemmTcParams p, cudaStream_t stream) {
+template <int BN, typename OutT, bool I8>
+static int launch_tc(const void* a, const void* b, GemmTcParams p, cudaStream_t stream) {
   using namespace gemm;
   CUtensorMap tm_a, tm_b;
-  XQT_CUDA((cudaError_t)make_tile_map(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.m, p.k, kBM));
-  XQT_CUDA((cudaError_t)make_tile_map(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.n, p.k, BN));
+  const int esize = I8 ? 1 : 2;
+  const CUtensorMapDataType dt = I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  XQT_CUDA((cudaError_t)make_tile_map(&tm_a, a, dt, esize, p.m, p.k, kBM));
+  XQT_CUDA((cudaError_t)make_tile_map(&tm_b, b, dt, esize, p.n, p.k, BN));
   constexpr int stage_bytes = kBM * kRowBytes + BN * kRowBytes;
   int stages = (kSmemBudget - 1024) / stage_bytes;
   p.stages = stages > kMaxStages ? kMaxStages : stages;
   p.mtiles = ceil_div(p.m, kBM);
   p.ntiles = ceil_div(p.n, BN);
-  p.kblocks = ceil_div(p.k, kRowBytes);
+  p.kblocks = ceil_div(p.k * esize, kRowBytes);
   const size_t smem_bytes = (size_t)p.stages * stage_bytes + 1024;
-  auto kern = gemm_i8_kernel<BN, OutT>;
-  static bool configured = false;
-  if (!configured) {
-    XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
-    configured = true;
-  }
+  void (*kern)(const CUtensorMap, const CUtensorMap, const GemmTcParams) =
+      I8 ? gemm_i8_kernel<BN, OutT> : gemm_f16_kernel<BN, OutT>;
+  XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
   int grid = sm_count_now();
   if (grid > p.mtiles * p.ntiles) grid = p.mtiles * p.ntiles;
   kern<<<grid, kThreads, smem_bytes, stream>>>(tm_a, tm_b, p);
@@ -272,8 +321,26 @@ int gemm_i8_launch(const void* a, const void* b, const float* row_scale, const f
   p.row_scale = row_scale; p.col_scale = col_scale; p.bias = bias; p.out = out; p.status = status;
   const bool wide = (n % 256 == 0);
   if (out_dtype == XQT_B200_BF16)
-    return wide ? launch_i8<256, __nv_bfloat16>(a, b, p, stream) : launch_i8<128, __nv_bfloat16>(a, b, p, stream);
-  return wide ? launch_i8<256, __half>(a, b, p, stream) : launch_i8<128, __half>(a, b, p, stream);
+    return wide ? launch_tc<256, __nv_bfloat16, true>(a, b, p, stream) : launch_tc<128, __nv_bfloat16, true>(a, b, p, stream);
+  return wide ? launch_tc<256, __half, true>(a, b, p, stream) : launch_tc<128, __half, true>(a, b, p, stream);
+}
+
+
+// fp16 A [M,K] x fp16 B [N,K]^T with fp32 accumulation; out = acc (+ bias[n]) (+ residual[m,n]) in
+// bf16 / fp16 (out_dtype) or fp32 (out_f32)
+int gemm_f16_launch(const void* a, const void* b, const float* bias, const void* residual, void* out, int m, int n,
+                    int k, int out_dtype, int out_f32, unsigned int* status, cudaStream_t stream) {
+  XQT_REQUIRE(m > 0 && n > 0 && k > 0 && k % 8 == 0 && n % 8 == 0);
+  XQT_REQUIRE(out_dtype == XQT_B200_BF16 || out_dtype == XQT_B200_FP16);
+  XQT_REQUIRE(a != nullptr && b != nullptr && out != nullptr && status != nullptr && ((uintptr_t)out & 15) == 0);
+  XQT_REQUIRE(!out_f32 || residual == nullptr);
+  GemmTcParams p{};
+  p.m = m; p.n = n; p.k = k;
+  p.bias = bias; p.residual = residual; p.out_f32 = out_f32; p.out = out; p.status = status;
+  const bool wide = (n % 256 == 0);
+  if (out_dtype == XQT_B200_BF16)
+    return wide ? launch_tc<256, __nv_bfloat16, false>(a, b, p, stream) : launch_tc<128, __nv_bfloat16, false>(a, b, p, stream);
+  return wide ? launch_tc<256, __half, false>(a, b, p, stream) : launch_tc<128, __half, false>(a, b, p, stream);
 }
 
 }  // namespace xqt_b200

@@ -321,10 +321,55 @@ __global__ void __launch_bounds__(256) bf16_to_f16_kernel(const __nv_bfloat16* _
   reinterpret_cast<uint4*>(dst)[i] = o;
 }
 
+// Canonical int4 weights -> fp16 [N, K] row-major, value = fp16((code - zero) * scale) computed in
+// fp32 and rounded once.  One thread converts 32 weights (16 packed bytes -> 64 bytes).
+template <typename P>
+__global__ void __launch_bounds__(256) dequant_w4_f16_kernel(const uint8_t* __restrict__ qweight, const P* __restrict__ scales,
+                                                            const P* __restrict__ zeros, __half* __restrict__ dst, int n,
+                                                            int k, int group_size, int nibble_signed) {
+  const int chunks = k / 32;                                   // 16-byte chunks per row
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n * chunks) return;
+  const int row = (int)(i / chunks), c = (int)(i % chunks);
+  const int g = (c * 32) / group_size;
+  const size_t pi = (size_t)row * (k / group_size) + g;
+  const float sc = to_float<P>(scales[pi]);
+  const float zp = (zeros != nullptr ? to_float<P>(zeros[pi]) : 0.f) + (nibble_signed ? 8.f : 0.f);
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(qweight + (size_t)row * (k / 2)) + c);
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint4* out = reinterpret_cast<uint4*>(dst + (size_t)row * k + (size_t)c * 32);
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const uint32_t word = nibble_signed ? (words[w] ^ 0x88888888u) : words[w];   // two's complement -> code + 8
+    uint4 o;
+    __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = ((float)((word >> (8 * j)) & 15u) - zp) * sc;
+      const float b = ((float)((word >> (8 * j + 4)) & 15u) - zp) * sc;
+      h[j] = __floats2half2_rn(a, b);
+    }
+    out[w] = o;
+  }
+}
+
+// Above this M the weights are dequantised once per call into an fp16 scratch and multiplied by the
+// dense tcgen05 GEMM: the fused kernel converts the whole weight matrix again for every 128-row tile
+// of M, which costs more than one pass over N*K as soon as M spans a few tiles.
+constexpr int kDenseMinM = 256;
+
 // [0,256) status, [256, 256+16 KiB) reserved for the ticket area of the M <= 16 kernel that shares this
 // workspace, then the fp16 copy of bf16 activations
 constexpr size_t kScratchOffset = 256 + 16384;
-size_t w4a16_gemm_tc_workspace_bytes(int m, int k) { return kScratchOffset + (size_t)m * k * 2; }
+size_t w4a16_gemm_tc_workspace_bytes(int m, int n, int k) {
+  size_t bytes = kScratchOffset + (((size_t)m * k * 2 + 255) & ~(size_t)255);
+  if (m >= kDenseMinM) bytes += (size_t)n * k * 2;   // fp16 weights of the two-pass form
+  return bytes;
+}
+bool w4a16_gemm_tc_any_zero_point(int m) { return m >= kDenseMinM; }
+
+int gemm_f16_launch(const void* a, const void* b, const float* bias, const void* residual, void* out, int m, int n,
+                    int k, int out_dtype, int out_f32, unsigned int* status, cudaStream_t stream);
 
 bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size) {
   return m >= 1 && n % 8 == 0 && k == padded_k && k % 64 == 0 && (group_size == 64 || group_size == 128);
@@ -364,13 +409,28 @@ int w4a16_gemm_tc_launch(const void* x, const void* qw, const void* scales, cons
   XQT_REQUIRE(w4a16_gemm_tc_supported(m, n, k, k, group_size));
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256 && ((uintptr_t)out & 15) == 0);
   unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
+  unsigned char* scratch = reinterpret_cast<unsigned char*>(workspace) + kScratchOffset;
+  if (act_dtype == XQT_B200_BF16 || m >= kDenseMinM) XQT_REQUIRE(workspace_bytes >= w4a16_gemm_tc_workspace_bytes(m, n, k));
   if (act_dtype == XQT_B200_BF16) {
-    XQT_REQUIRE(workspace_bytes >= w4a16_gemm_tc_workspace_bytes(m, k));
-    __half* x16 = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + kScratchOffset);
+    __half* x16 = reinterpret_cast<__half*>(scratch);
     const size_t n8 = (size_t)m * k / 8;
     bf16_to_f16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, x16, n8);
     XQT_CUDA(cudaGetLastError());
     x = x16;
+  }
+  if (m >= kDenseMinM) {
+    // two passes: weights -> fp16 scratch (any zero point, fp32 arithmetic), then the dense GEMM
+    __half* w16 = reinterpret_cast<__half*>(scratch + (((size_t)m * k * 2 + 255) & ~(size_t)255));
+    const size_t threads = (size_t)n * (k / 32);
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (param_dtype == XQT_B200_BF16)
+      dequant_w4_f16_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const uint8_t*)qw, (const __nv_bfloat16*)scales, (const __nv_bfloat16*)zeros, w16, n, k, group_size, nibble_signed);
+    else if (param_dtype == XQT_B200_FP16)
+      dequant_w4_f16_kernel<__half><<<blocks, 256, 0, stream>>>((const uint8_t*)qw, (const __half*)scales, (const __half*)zeros, w16, n, k, group_size, nibble_signed);
+    else
+      dequant_w4_f16_kernel<float><<<blocks, 256, 0, stream>>>((const uint8_t*)qw, (const float*)scales, (const float*)zeros, w16, n, k, group_size, nibble_signed);
+    XQT_CUDA(cudaGetLastError());
+    return gemm_f16_launch(x, w16, bias, residual, out, m, n, k, act_dtype, out_f32, status, stream);
   }
   W4GemmParams p{};
   p.m = m; p.n = n; p.k = k; p.group_size = group_size; p.groups = k / group_size;

@@ -202,6 +202,54 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_
         : "memory");
   }
 }
+// One K block of four SS MMA steps (descriptors a0..a3 / b0..b3), its commit to `done_bar`, and --
+// issued first, consumed last -- one poll of `next_bar`: the 150-cycle round trip of the poll runs
+// while the MMAs are being issued.  Returns whether `next_bar` had completed `next_parity`.
+// `first_accumulate` is the accumulate flag of the first step; the other three always accumulate.
+template <bool I8>
+__device__ __forceinline__ bool umma_ss_x4_commit_poll(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t idesc,
+                                                        uint32_t first_accumulate, uint32_t done_bar, uint32_t next_bar,
+                                                        uint32_t next_parity) {
+  uint32_t ok;
+  if (I8) {
+    asm volatile(
+        "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a, b;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%6], %7;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%1], %2, %3, %8, p;\n\t"
+        "add.u64 a, %2, 2;\n\tadd.u64 b, %3, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%1], a, b, %8, t;\n\t"
+        "add.u64 a, %2, 4;\n\tadd.u64 b, %3, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%1], a, b, %8, t;\n\t"
+        "add.u64 a, %2, 6;\n\tadd.u64 b, %3, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%1], a, b, %8, t;\n\t"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}\n"
+        : "=r"(ok)
+        : "r"(d_tmem), "l"(a0), "l"(b0), "r"(first_accumulate), "r"(done_bar), "r"(next_bar), "r"(next_parity), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a, b;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%6], %7;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %8, p;\n\t"
+        "add.u64 a, %2, 2;\n\tadd.u64 b, %3, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %8, t;\n\t"
+        "add.u64 a, %2, 4;\n\tadd.u64 b, %3, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %8, t;\n\t"
+        "add.u64 a, %2, 6;\n\tadd.u64 b, %3, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %8, t;\n\t"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}\n"
+        : "=r"(ok)
+        : "r"(d_tmem), "l"(a0), "l"(b0), "r"(first_accumulate), "r"(done_bar), "r"(next_bar), "r"(next_parity), "r"(idesc)
+        : "memory");
+  }
+  return ok != 0;
+}
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(

@@ -110,13 +110,14 @@ def w4a16_linear(
     if m == 0:
         return out
     lib = native.library()
+    two_pass = bool(lib.xqt_b200_w4a16_two_pass(m))   # large M: fp32 dequantisation pass, any zero point
     if odt == torch.float32:
-        if not _integer_zero_points(zero_points):
+        if not two_pass and not _integer_zero_points(zero_points):
             raise XQTBackendError("fp32 partial sums need the tensor-core GEMM, i.e. integer zero points")
         variant = "tcgen05"
     if variant == "auto":
         variant = select_variant(m, n, k, padded_k, int(group_size), activation, residual is not None)
-        if variant == "tcgen05" and not _integer_zero_points(zero_points):
+        if variant == "tcgen05" and not two_pass and not _integer_zero_points(zero_points):
             variant = "simt"
     scratch = native.workspace(device, lib.xqt_b200_w4a16_workspace_bytes(m, n, k))
     stream = native.stream_handle(device)
