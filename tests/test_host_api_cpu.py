@@ -175,3 +175,32 @@ def test_kernel_namespace_selection_and_conflicts(monkeypatch):
     with pytest.raises(KeyError):
         ks.select_kernel("quantization.nothing", table=table)
     assert "quantization.svdq_w4a4_linear" in ks.registry.ops() and ks.ENGINE["min_capability"] == 100
+
+
+def _w8a8_spec(m=4, n=8, k=64, out="bf16"):
+    from xqt_b200.contracts import EpilogueSpec, GemmSpec
+
+    return GemmSpec(
+        problem=GemmProblem(m=m, n=n, k=k, sm=100),
+        quant=QuantSpec(weight_dtype="int8", activation_dtype="int8", output_dtype=out, weight_granularity="per_channel",
+                        activation_granularity="per_token", weight_scale_source="weight_offline",
+                        activation_scale_source="activation_dynamic"),
+        epilogue=EpilogueSpec(output_dtype=out))
+
+
+def test_w8a8_executor_validates_before_touching_the_gpu():
+    from xqt_b200.executors import b200_w8a8_executor
+
+    w = torch.zeros((8, 64), dtype=torch.int8)
+    ws = torch.ones(8)
+    x = torch.zeros((4, 64), dtype=torch.bfloat16)
+    with pytest.raises(XQTBackendError, match="CUDA"):
+        b200_w8a8_executor(x, w, spec=_w8a8_spec(), weight_scales=ws)
+    with pytest.raises(XQTBackendError, match="int8 \\[N, K\\]"):
+        b200_w8a8_executor(x, w.to(torch.float32), spec=_w8a8_spec(), weight_scales=ws)
+    with pytest.raises(XQTBackendError, match="weight_scales"):
+        b200_w8a8_executor(x, w, spec=_w8a8_spec())
+    with pytest.raises(XQTBackendError, match="zero points"):
+        b200_w8a8_executor(x, w, spec=_w8a8_spec(), weight_scales=ws, weight_zero_points=torch.zeros(8))
+    with pytest.raises(XQTBackendError, match="bias only"):
+        b200_w8a8_executor(x, w, spec=_w8a8_spec(), weight_scales=ws, residual=torch.zeros((4, 8)))

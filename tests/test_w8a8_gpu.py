@@ -85,3 +85,40 @@ def test_batched_input_and_fp16():
     assert tuple(out.shape) == (3, 5, 72)
     ref = oracle.linear(x.reshape(15, 256), q, s, rot_block=64, rot_kind="regular")
     assert o16.rel_l2(out.cpu().reshape(15, 72), ref) <= 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prequantized", [True, False])
+def test_registry_executor_through_dispatch(prequantized):
+    """The GEMM-registry row `sm100_w8a8_int8_b200`: int8 codes + per-token scales, or a floating
+    activation quantised per token by the prologue kernel."""
+
+    from xqt_b200.contracts import EpilogueSpec, GemmProblem, GemmSpec, QuantSpec
+    from xqt_b200.dispatch import dispatch_gemm
+    from xqt_b200.executors import install_b200_executors
+    from xqt_b200.registry import B200_W8A8, GemmKernelRegistry, b200_rows
+
+    m, n, k = 96, 264, 512
+    dev = torch.device("cuda", 0)
+    w = torch.randn((n, k), generator=seeded(21)) * 0.02
+    q_w, s_w = quantize.quantize_w8_per_channel(w)
+    x = torch.randn((m, k), generator=seeded(22)).to(torch.bfloat16)
+    bias = torch.randn((n,), generator=seeded(23))
+    q_a, s_a = oracle.quantize_act_per_token(x)
+    ref = oracle.gemm_integer(q_a, s_a, q_w, s_w, bias=bias, out_dtype=torch.bfloat16)
+    reg = GemmKernelRegistry(b200_rows())
+    assert B200_W8A8 in install_b200_executors(reg)
+    spec = GemmSpec(
+        problem=GemmProblem(m=m, n=n, k=k, sm=100),
+        quant=QuantSpec(weight_dtype="int8", activation_dtype="int8", output_dtype="bf16", weight_granularity="per_channel",
+                        activation_granularity="per_token", weight_scale_source="weight_offline",
+                        activation_scale_source="activation_dynamic"),
+        epilogue=EpilogueSpec(has_bias=True, output_dtype="bf16"))
+    if prequantized:
+        result = dispatch_gemm(q_a.to(dev), q_w.to(dev), spec=spec, registry=reg, weight_scales=s_w.to(dev),
+                               activation_scales=s_a.to(dev), bias=bias.to(dev))
+    else:
+        result = dispatch_gemm(x.to(dev), q_w.to(dev), spec=spec, registry=reg, weight_scales=s_w.to(dev), bias=bias.to(dev))
+    torch.cuda.synchronize()
+    assert result.report.selected_kernel == B200_W8A8 and result.report.native
+    assert o16.rel_l2(result.output.cpu(), ref) <= 1e-3

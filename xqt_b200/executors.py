@@ -21,7 +21,7 @@ import torch
 from . import native
 from .errors import XQTBackendError
 from .layout import validate_w4a16_packed_weight
-from .registry import B200_W4A16, GemmKernelRegistry, b200_rows
+from .registry import B200_W4A16, B200_W8A8, GemmKernelRegistry, b200_rows
 
 _TORCH = {"fp16": torch.float16, "bf16": torch.bfloat16}
 
@@ -85,7 +85,64 @@ def b200_w4a16_executor(activation, weight, *, spec, weight_scales=None, activat
     )
 
 
-_EXECUTORS = {B200_W4A16: b200_w4a16_executor}
+def b200_w8a8_executor(activation, weight, *, spec, weight_scales=None, activation_scales=None,
+                       weight_zero_points=None, activation_zero_points=None, bias=None, residual=None,
+                       output: torch.Tensor | None = None) -> torch.Tensor:
+    """W8A8 of the GEMM contract (xqt/kernels/ops/gemm/reference.py:278-323, quantize.py:60-131):
+    ``weight`` int8 ``[N, K]`` with per-output-channel ``weight_scales [N]``; ``activation`` either
+    int8 ``[M, K]`` with per-token ``activation_scales`` (``[M]`` or ``[M,1]``) or fp16/bf16, which is
+    quantised per token here (``amax/127``, clamp [-128,127]) by the prologue kernel.  Output in
+    ``QuantSpec.output_dtype`` (fp16 / bf16): ``acc * a_scale[m] * w_scale[n] (+ bias)``."""
+
+    from .ops.activation import rotate_quantize
+    from .ops.w8a8 import PackedConvRotW8A8Linear, w8a8_gemm
+
+    quant, problem = spec.quant, spec.problem
+    if quant.weight_dtype != "int8" or quant.activation_dtype != "int8":
+        raise XQTBackendError("B200 W8A8 executor serves int8 weights with int8 activations")
+    if quant.output_dtype not in _TORCH:
+        raise XQTBackendError("B200 W8A8 output dtype must be fp16 or bf16")
+    if quant.weight_granularity != "per_channel" or quant.activation_granularity != "per_token":
+        raise XQTBackendError("B200 W8A8 supports per-channel weight scales with per-token activation scales")
+    if weight_zero_points is not None or activation_zero_points is not None or quant.activation_zero_point:
+        raise XQTBackendError("B200 W8A8 is symmetric: zero points are not supported")
+    if residual is not None or spec.epilogue.has_residual or spec.epilogue.activation != "none":
+        raise XQTBackendError("B200 W8A8 epilogue supports bias only")
+    qweight = getattr(weight, "qweight", weight)
+    if weight_scales is None:
+        weight_scales = getattr(weight, "scales", None)
+    if not isinstance(qweight, torch.Tensor) or qweight.dtype != torch.int8 or tuple(qweight.shape) != (problem.n, problem.k):
+        raise XQTBackendError("B200 W8A8 weight must be int8 [N, K]")
+    if weight_scales is None or weight_scales.numel() != problem.n:
+        raise XQTBackendError("B200 W8A8 needs per-channel weight_scales with N entries")
+    if not isinstance(activation, torch.Tensor) or activation.ndim != 2 or not activation.is_cuda:
+        raise XQTBackendError("B200 W8A8 activation must be CUDA rank-2")
+    _require_b200(activation.device)
+    if tuple(activation.shape) != (problem.m, problem.k):
+        raise XQTBackendError("B200 W8A8 activation shape does not match GemmProblem")
+    if problem.k % 16 or problem.n % 8:
+        raise XQTBackendError("B200 W8A8 needs K % 16 == 0 and N % 8 == 0")
+    device, dtype = activation.device, _TORCH[quant.output_dtype]
+    if activation.dtype == torch.int8:
+        if activation_scales is None or activation_scales.numel() != problem.m:
+            raise XQTBackendError("int8 activations need per-token activation_scales with M entries")
+        codes = activation.contiguous()
+        a_scale = activation_scales.reshape(-1).to(device=device, dtype=torch.float32).contiguous()
+    elif activation.dtype in (torch.float16, torch.bfloat16):
+        if activation_scales is not None:
+            raise XQTBackendError("floating activations are quantised dynamically: do not pass activation_scales")
+        codes, a_scale = rotate_quantize(activation.contiguous(), None, bits=8)
+    else:
+        raise XQTBackendError("B200 W8A8 activation must be int8, fp16 or bf16")
+    packed = PackedConvRotW8A8Linear(
+        qweight=qweight.to(device).contiguous(),
+        weight_scales=weight_scales.reshape(-1).to(device=device, dtype=torch.float32).contiguous(),
+        bias=None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous(),
+        input_features=problem.k, output_features=problem.n, padded_input_features=problem.k, dtype=dtype)
+    return w8a8_gemm(codes, a_scale, packed, output)
+
+
+_EXECUTORS = {B200_W4A16: b200_w4a16_executor, B200_W8A8: b200_w8a8_executor}
 
 
 def install_b200_executors(registry: GemmKernelRegistry | None = None, *, require_native: bool = True) -> tuple[str, ...]:
@@ -116,4 +173,4 @@ def install_b200_executors(registry: GemmKernelRegistry | None = None, *, requir
     return tuple(promoted)
 
 
-__all__ = ["b200_w4a16_executor", "install_b200_executors"]
+__all__ = ["b200_w4a16_executor", "b200_w8a8_executor", "install_b200_executors"]
