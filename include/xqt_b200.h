@@ -219,6 +219,26 @@ int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const voi
                        int k, int out_dtype, void* workspace, size_t workspace_bytes,
                        xqt_b200_stream_t stream);
 
+/* The same linear in its operand-dequantised form, for M >= 256 (xqt_b200_w4a4_dense_preferred):
+ * both operands are expanded once per call to fp16 -- code * scale, an exact fp32 product rounded
+ * once -- the low-rank pair (la, up) is appended along K, and one dense tcgen05 fp16 GEMM with fp32
+ * accumulation gives the output.  Same codes and scales as the integer form; it avoids that form's
+ * per-group int32 drain and fp32 scaling, which bound it on the CUDA cores.  No counterpart in xqt
+ * (its sm_89 kernel has int4 tensor-core instructions, Blackwell has none).
+ *   weight_scales fp32 [N, K/64] (the artifact's residual_scale);  up fp32 [N, 32] or NULL with la
+ *   K a multiple of 64, N a multiple of 8; workspace >= xqt_b200_w4a4_dense_workspace_bytes(m, n, k),
+ *   256-byte aligned.
+ * xqt_b200_lowrank_down_tc is xqt_b200_lowrank_down on the dense tcgen05 GEMM (la rows >= M are not
+ * written); workspace >= 256 bytes (status word). */
+size_t xqt_b200_w4a4_dense_workspace_bytes(int m, int n, int k);
+int xqt_b200_w4a4_dense_preferred(int m, int n, int k);
+int xqt_b200_w4a4_dense(const void* act_codes, const float* act_scales, const void* qweight,
+                        const float* weight_scales, const float* la, const float* up, const float* bias,
+                        void* output, int m, int n, int k, int out_dtype, void* workspace,
+                        size_t workspace_bytes, xqt_b200_stream_t stream);
+int xqt_b200_lowrank_down_tc(const void* rotated, const void* down, float* la, int m, int k, int act_dtype,
+                             void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream);
+
 /* SwiGLU gating between the projections of an MLP: output[m, i] = silu(gate_up[m, i]) * gate_up[m, inter + i],
  * evaluated in fp32 and rounded once.  gate_up is [M, 2*inter] (the gate and up projections fused
  * horizontally into one linear), output [M, inter].  Replaces xqt_convrot_w8a8_sm89_fused_swiglu

@@ -52,16 +52,17 @@ def test_group_int4_codes_bit_exact(kind, block):
     assert torch.equal(codes.cpu(), q_ref)
 
 
+@pytest.mark.parametrize("form", ["integer", "dense"])
 @pytest.mark.parametrize("m,n,k,rank", [(128, 128, 128, 32), (200, 264, 512, 16), (33, 136, 256, 4), (512, 1024, 3072, 32),
                                         (1, 128, 128, 32)])
-def test_svdq_forward(m, n, k, rank):
+def test_svdq_forward(m, n, k, rank, form):
     rot = quantize.randomized_rotation(128, seed=7)
     x = _outliers(torch.randn((m, k), generator=seeded(m)), 9).to(torch.bfloat16)
     packed_w, scale, down, up = _layer(n, k, rank, 100 + n, rot)
     bias = torch.randn((n,), generator=seeded(2))
     layer = pack_svdq_w4a4_linear(None, down.to(DEV), up.to(DEV), bias.to(DEV), packed_residual=packed_w.to(DEV),
                                   residual_scale=scale.to(DEV), rotation=rot)
-    out, parts = svdq_w4a4_linear(x.to(DEV), layer, return_parts=True)
+    out, parts = svdq_w4a4_linear(x.to(DEV), layer, return_parts=True, form=form)
     torch.cuda.synchronize()
     assert native.workspace_status(DEV) == 0
     ref, rparts = oracle.w4a4_forward(x, packed_w, scale, down, up, group_size=64, rot_kind=rot.kind, rot_block=128,
@@ -84,6 +85,24 @@ def test_convrot_w4a4_without_low_rank_and_fp16():
     zeros_d, zeros_u = torch.zeros((1, k)), torch.zeros((n, 1))
     ref = oracle.w4a4_forward(x, packed_w, scale, zeros_d, zeros_u, group_size=64, rot_kind="regular", rot_block=256)
     assert o16.rel_l2(out.cpu(), ref) <= 1e-3
+
+
+def test_dense_form_is_the_default_from_m_256_and_matches_the_integer_form():
+    m, n, k, rank = 300, 264, 512, 8
+    assert native.library().xqt_b200_w4a4_dense_preferred(m, n, k) == 1
+    assert native.library().xqt_b200_w4a4_dense_preferred(255, n, k) == 0
+    rot = quantize.randomized_rotation(128, seed=5)
+    x = _outliers(torch.randn((m, k), generator=seeded(12)), 4).to(torch.bfloat16)
+    packed_w, scale, down, up = _layer(n, k, rank, 77, rot)
+    layer = pack_svdq_w4a4_linear(None, down.to(DEV), up.to(DEV), None, packed_residual=packed_w.to(DEV),
+                                  residual_scale=scale.to(DEV), rotation=rot)
+    auto = svdq_w4a4_linear(x.to(DEV), layer)
+    dense = svdq_w4a4_linear(x.to(DEV), layer, form="dense")
+    integer = svdq_w4a4_linear(x.to(DEV), layer, form="integer")
+    torch.cuda.synchronize()
+    assert native.workspace_status(DEV) == 0
+    assert torch.equal(auto, dense)
+    assert o16.rel_l2(dense.cpu(), integer.cpu()) <= 1e-3
 
 
 def test_config3_full_size():

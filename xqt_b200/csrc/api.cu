@@ -34,6 +34,11 @@ bool w4a4_gemm_supported(int m, int n, int k);
 int rotate_quant_launch(const void*, const float*, void*, float*, void*, int, int, int, int, int, int, int, cudaStream_t);
 int gemm_i8_launch(const void*, const void*, const float*, const float*, const float*, void*, int, int, int, int,
                    unsigned int*, cudaStream_t);
+size_t w4a4_dense_workspace_bytes(int m, int n, int k);
+bool w4a4_dense_supported(int m, int n, int k);
+int w4a4_dense_launch(const void*, const float*, const void*, const float*, const float*, const float*, const float*, void*,
+                      int, int, int, int, void*, size_t, cudaStream_t);
+int lowrank_down_tc_launch(const void*, const void*, float*, int, int, int, unsigned int*, cudaStream_t);
 }  // namespace xqt_b200
 
 using namespace xqt_b200;
@@ -218,6 +223,30 @@ int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const voi
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
   return w4a4_gemm_launch(act_codes, act_scales, qweight, aux, la, bias, output, m, n, k, out_dtype,
                           reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
+}
+
+size_t xqt_b200_w4a4_dense_workspace_bytes(int m, int n, int k) {
+  return w4a4_dense_supported(m, n, k) ? w4a4_dense_workspace_bytes(m, n, k) : 0;
+}
+
+int xqt_b200_w4a4_dense_preferred(int m, int n, int k) { return (m >= 256 && w4a4_dense_supported(m, n, k)) ? 1 : 0; }
+
+int xqt_b200_w4a4_dense(const void* act_codes, const float* act_scales, const void* qweight, const float* weight_scales,
+                        const float* la, const float* up, const float* bias, void* output, int m, int n, int k,
+                        int out_dtype, void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(out_dtype == XQT_B200_FP16 || out_dtype == XQT_B200_BF16);
+  return w4a4_dense_launch(act_codes, act_scales, qweight, weight_scales, la, up, bias, output, m, n, k, out_dtype,
+                           workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int xqt_b200_lowrank_down_tc(const void* rotated, const void* down, float* la, int m, int k, int act_dtype,
+                             void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
+  XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
+  return lowrank_down_tc_launch(rotated, down, la, m, k, act_dtype, reinterpret_cast<unsigned int*>(workspace),
+                                (cudaStream_t)stream);
 }
 
 int xqt_b200_swiglu(const void* gate_up, void* output, int m, int inter, int dtype, xqt_b200_stream_t stream) {

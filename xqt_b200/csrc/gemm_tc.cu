@@ -60,11 +60,12 @@ __device__ __forceinline__ void store8<__half>(__half* dst, const float (&v)[8])
   *reinterpret_cast<uint4*>(dst) = o;
 }
 
-// I8: int8 operands, int32 accumulators, scaled epilogue.  Otherwise fp16 operands, fp32
-// accumulators, epilogue acc (+ bias) (+ residual).
-template <int BN, typename OutT, bool I8>
+// KIND 0: int8 operands, int32 accumulators, scaled epilogue.  KIND 1 / 2: fp16 / bf16 operands (both
+// sides the same format), fp32 accumulators, epilogue acc (+ bias) (+ residual).
+template <int BN, typename OutT, int KIND>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmTcParams& p) {
   using namespace gemm;
+  constexpr bool I8 = KIND == 0;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) unsigned long long bars[2 * kMaxStages + 4];
   __shared__ uint32_t s_tmem_base;
@@ -72,7 +73,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
 
   constexpr int kABytes = kBM * kRowBytes, kBBytes = BN * kRowBytes, kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = 2 * BN;
-  constexpr uint32_t kIdesc = I8 ? umma_idesc(kAccS32, kFmtS8, kFmtS8, kBM, BN) : umma_idesc(kAccF32, kFmtF16, kFmtF16, kBM, BN);
+  constexpr uint32_t kIdesc = I8 ? umma_idesc(kAccS32, kFmtS8, kFmtS8, kBM, BN)
+                                 : (KIND == 1 ? umma_idesc(kAccF32, kFmtF16, kFmtF16, kBM, BN) : umma_idesc(kAccF32, kFmtBF16, kFmtBF16, kBM, BN));
   constexpr int kElemsPerRow = I8 ? kRowBytes : kRowBytes / 2;   // K elements per 128-byte swizzle row
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -233,7 +235,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(gemm::kThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmTcParams p) {
-  gemm_tc_body<BN, OutT, true>(tm_a, tm_b, p);
+  gemm_tc_body<BN, OutT, 0>(tm_a, tm_b, p);
 }
 
 // fp16 x fp16 -> fp32: the second pass of the W4A16 linear at large M (weights dequantised once per
@@ -241,7 +243,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(gemm::kThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmTcParams p) {
-  gemm_tc_body<BN, OutT, false>(tm_a, tm_b, p);
+  gemm_tc_body<BN, OutT, 1>(tm_a, tm_b, p);
+}
+
+// bf16 x bf16 -> fp32 (the rank-32 down projection of the rotated activations)
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(gemm::kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmTcParams p) {
+  gemm_tc_body<BN, OutT, 2>(tm_a, tm_b, p);
 }
 
 // ----------------------------------------------------------------------------------------- host
@@ -264,18 +273,23 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // row-major [rows, cols] matrix of `esize`-byte elements; box = 128 bytes of a row x box_rows rows,
 // written to shared memory with the 128-byte swizzle; out-of-range elements read as zero
-int make_tile_map(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int esize, long long rows,
-                  long long cols, int box_rows) {
+int make_tile_map_ld(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int esize, long long rows,
+                     long long cols, long long ld, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return (int)cudaErrorNotSupported;
-  if (((uintptr_t)base & 15) != 0 || (cols * esize) % 16 != 0) return (int)cudaErrorInvalidValue;
+  if (((uintptr_t)base & 15) != 0 || (ld * esize) % 16 != 0 || ld < cols) return (int)cudaErrorInvalidValue;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * esize};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
   cuuint32_t box[2] = {(cuuint32_t)(128 / esize), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+int make_tile_map(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int esize, long long rows,
+                  long long cols, int box_rows) {
+  return make_tile_map_ld(map, base, dtype, esize, rows, cols, cols, box_rows);
 }
 
 static int sm_count_now() {
@@ -285,14 +299,16 @@ static int sm_count_now() {
   return v;
 }
 
-template <int BN, typename OutT, bool I8>
-static int launch_tc(const void* a, const void* b, GemmTcParams p, cudaStream_t stream) {
+template <int BN, typename OutT, int KIND>
+static int launch_tc(const void* a, long long lda, const void* b, long long ldb, GemmTcParams p, cudaStream_t stream) {
   using namespace gemm;
   CUtensorMap tm_a, tm_b;
+  constexpr bool I8 = KIND == 0;
   const int esize = I8 ? 1 : 2;
-  const CUtensorMapDataType dt = I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  XQT_CUDA((cudaError_t)make_tile_map(&tm_a, a, dt, esize, p.m, p.k, kBM));
-  XQT_CUDA((cudaError_t)make_tile_map(&tm_b, b, dt, esize, p.n, p.k, BN));
+  const CUtensorMapDataType dt = I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                    : (KIND == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  XQT_CUDA((cudaError_t)make_tile_map_ld(&tm_a, a, dt, esize, p.m, p.k, lda, kBM));
+  XQT_CUDA((cudaError_t)make_tile_map_ld(&tm_b, b, dt, esize, p.n, p.k, ldb, BN));
   constexpr int stage_bytes = kBM * kRowBytes + BN * kRowBytes;
   int stages = (kSmemBudget - 1024) / stage_bytes;
   p.stages = stages > kMaxStages ? kMaxStages : stages;
@@ -301,7 +317,7 @@ static int launch_tc(const void* a, const void* b, GemmTcParams p, cudaStream_t 
   p.kblocks = ceil_div(p.k * esize, kRowBytes);
   const size_t smem_bytes = (size_t)p.stages * stage_bytes + 1024;
   void (*kern)(const CUtensorMap, const CUtensorMap, const GemmTcParams) =
-      I8 ? gemm_i8_kernel<BN, OutT> : gemm_f16_kernel<BN, OutT>;
+      I8 ? gemm_i8_kernel<BN, OutT> : (KIND == 1 ? gemm_f16_kernel<BN, OutT> : gemm_bf16_kernel<BN, OutT>);
   XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
   int grid = sm_count_now();
   if (grid > p.mtiles * p.ntiles) grid = p.mtiles * p.ntiles;
@@ -321,16 +337,27 @@ int gemm_i8_launch(const void* a, const void* b, const float* row_scale, const f
   p.row_scale = row_scale; p.col_scale = col_scale; p.bias = bias; p.out = out; p.status = status;
   const bool wide = (n % 256 == 0);
   if (out_dtype == XQT_B200_BF16)
-    return wide ? launch_tc<256, __nv_bfloat16, true>(a, b, p, stream) : launch_tc<128, __nv_bfloat16, true>(a, b, p, stream);
-  return wide ? launch_tc<256, __half, true>(a, b, p, stream) : launch_tc<128, __half, true>(a, b, p, stream);
+    return wide ? launch_tc<256, __nv_bfloat16, 0>(a, k, b, k, p, stream) : launch_tc<128, __nv_bfloat16, 0>(a, k, b, k, p, stream);
+  return wide ? launch_tc<256, __half, 0>(a, k, b, k, p, stream) : launch_tc<128, __half, 0>(a, k, b, k, p, stream);
 }
 
 
-// fp16 A [M,K] x fp16 B [N,K]^T with fp32 accumulation; out = acc (+ bias[n]) (+ residual[m,n]) in
-// bf16 / fp16 (out_dtype) or fp32 (out_f32)
+// 16-bit A [M,K] x 16-bit B [N,K]^T (both fp16, or both bf16 with operand_bf16) with fp32
+// accumulation; out = acc (+ bias[n]) (+ residual[m,n]) in bf16 / fp16 (out_dtype) or fp32 (out_f32).
+// `lda` / `ldb` are the row strides in elements (>= k, multiples of 8).
+int gemm_f16_launch_strided(const void* a, long long lda, const void* b, long long ldb, const float* bias,
+                            const void* residual, void* out, int m, int n, int k, int out_dtype, int out_f32,
+                            int operand_bf16, unsigned int* status, cudaStream_t stream);
+
 int gemm_f16_launch(const void* a, const void* b, const float* bias, const void* residual, void* out, int m, int n,
                     int k, int out_dtype, int out_f32, unsigned int* status, cudaStream_t stream) {
-  XQT_REQUIRE(m > 0 && n > 0 && k > 0 && k % 8 == 0 && n % 8 == 0);
+  return gemm_f16_launch_strided(a, k, b, k, bias, residual, out, m, n, k, out_dtype, out_f32, 0, status, stream);
+}
+
+int gemm_f16_launch_strided(const void* a, long long lda, const void* b, long long ldb, const float* bias,
+                            const void* residual, void* out, int m, int n, int k, int out_dtype, int out_f32,
+                            int operand_bf16, unsigned int* status, cudaStream_t stream) {
+  XQT_REQUIRE(m > 0 && n > 0 && k > 0 && n % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && lda >= k && ldb >= k);
   XQT_REQUIRE(out_dtype == XQT_B200_BF16 || out_dtype == XQT_B200_FP16);
   XQT_REQUIRE(a != nullptr && b != nullptr && out != nullptr && status != nullptr && ((uintptr_t)out & 15) == 0);
   XQT_REQUIRE(!out_f32 || residual == nullptr);
@@ -338,9 +365,10 @@ int gemm_f16_launch(const void* a, const void* b, const float* bias, const void*
   p.m = m; p.n = n; p.k = k;
   p.bias = bias; p.residual = residual; p.out_f32 = out_f32; p.out = out; p.status = status;
   const bool wide = (n % 256 == 0);
-  if (out_dtype == XQT_B200_BF16)
-    return wide ? launch_tc<256, __nv_bfloat16, false>(a, b, p, stream) : launch_tc<128, __nv_bfloat16, false>(a, b, p, stream);
-  return wide ? launch_tc<256, __half, false>(a, b, p, stream) : launch_tc<128, __half, false>(a, b, p, stream);
+#define XQT_F16_GO(OUT, KIND) (wide ? launch_tc<256, OUT, KIND>(a, lda, b, ldb, p, stream) : launch_tc<128, OUT, KIND>(a, lda, b, ldb, p, stream))
+  if (out_dtype == XQT_B200_BF16) return operand_bf16 ? XQT_F16_GO(__nv_bfloat16, 2) : XQT_F16_GO(__nv_bfloat16, 1);
+  return operand_bf16 ? XQT_F16_GO(__half, 2) : XQT_F16_GO(__half, 1);
+#undef XQT_F16_GO
 }
 
 }  // namespace xqt_b200

@@ -168,22 +168,29 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_a, const W4GemmParams p
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      uint32_t it = 0, local = 0;
+      uint32_t local = 0, phase = 0;
+      int s = 0;
+      bool ready = false;   // the current stage's barrier has already been seen complete
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
         const int buf = local & 1;
         guarded_wait(tempty_bar(buf), ((local >> 1) & 1) ^ 1);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const int s = it % ns;
-          guarded_wait(bready_bar(s), (it / ns) & 1);   // weights dequantised (and the activation tile landed)
+        const bool last_tile = tile + (int)gridDim.x >= total_tiles;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!ready) guarded_wait(bready_bar(s), phase);   // weights dequantised (and the activation tile landed)
           tc_fence_after();
           const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
           const uint64_t adesc = umma_desc_sw128(a_addr), bdesc = umma_desc_sw128(a_addr + kABytes);
-#pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            umma_ss<false>(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
-          umma_commit(empty_bar(s));
+          int sn = s + 1;
+          uint32_t pn = phase;
+          if (sn == ns) { sn = 0; pn ^= 1; }
+          // four K steps, the commit that frees the stage, and the poll of the next stage's barrier
+          // (its 150-cycle round trip runs while the MMAs are issued)
+          ready = umma_ss_x4_commit_poll<false>(d_tmem, adesc, bdesc, kIdesc, kb != 0 ? 1u : 0u, empty_bar(s), bready_bar(sn), pn);
+          if (last_tile && kb == p.kblocks - 1) ready = false;
+          s = sn;
+          phase = pn;
         }
         umma_commit(tfull_bar(buf));
       }

@@ -10,8 +10,11 @@ sm_89 path does (xqt/runtime/modules/composite_add_w4a4.py:198-216) -- plus a sm
 transposed scales and up factors.
 
 Per call: rotate + round + group-64 int4 quantisation (one kernel), rank-R down projection (one
-kernel), tcgen05 ``kind::i8`` GEMM with per-slab fp32 scaling, rank-R up projection and bias in the
-epilogue (one kernel).
+kernel), then one of two forms of the product.  Integer form (M < 256): tcgen05 ``kind::i8`` GEMM with
+per-slab fp32 scaling, rank-R up projection and bias in the epilogue.  Operand-dequantised form
+(M >= 256): both operands expanded once to fp16 (code x scale), the low-rank pair appended along K,
+one dense tcgen05 fp16 GEMM -- the per-group scaling of the integer form runs on the CUDA cores and
+bounds it at a few per cent of the tensor peak.  Codes and scales are identical in both forms.
 """
 
 from __future__ import annotations
@@ -34,7 +37,8 @@ TILE = 128
 class PackedSVDQW4A4Linear:
     qweight: torch.Tensor          # uint8 [N, K/2] canonical signed nibbles
     aux: torch.Tensor              # fp32 [ceil(N/128), K/64*128 + 128*32]
-    weight_scales: torch.Tensor    # fp32 [N, K/64] (kept for inspection / export)
+    weight_scales: torch.Tensor    # fp32 [N, K/64]: the artifact's residual_scale (read by the dense form)
+    up: torch.Tensor | None        # fp32 [N, 32] up factors, rank padded with zeros (None without low-rank branch)
     down: torch.Tensor             # dtype [32, K], rows past the rank are zero
     bias: torch.Tensor | None      # fp32 [N]
     input_features: int
@@ -100,15 +104,18 @@ def pack_svdq_w4a4_linear(
     aux = torch.cat((sw.reshape(tiles, TILE, groups).transpose(1, 2).reshape(tiles, -1),
                      up.reshape(tiles, -1)), dim=1).contiguous()
     return PackedSVDQW4A4Linear(
-        qweight=packed_residual.to(device).contiguous(), aux=aux, weight_scales=scale.contiguous(), down=down,
+        qweight=packed_residual.to(device).contiguous(), aux=aux, weight_scales=scale.contiguous(),
+        up=up[:n].contiguous() if rank else None, down=down,
         bias=None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous(),
         input_features=k, output_features=n, padded_input_features=k, rank=rank, dtype=dtype, rotation=rotation)
 
 
 def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, workspace=None, lora_scale: float = 1.0,
-                     return_parts: bool = False):
+                     return_parts: bool = False, form: str = "auto"):
     """Full forward: rotation (``packed.rotation``; None = input already rotated), int4 activations
-    per (token, 64-K), integer GEMM with per-group scales, low-rank branch, bias."""
+    per (token, 64-K), GEMM with per-group scales, low-rank branch, bias.  ``form``: ``integer``
+    (tcgen05 int8 MMA, per-group int32 sums scaled in fp32), ``dense`` (operands expanded to fp16 once,
+    dense fp16 MMA) or ``auto`` (dense from M = 256)."""
 
     del workspace
     if inputs.shape[-1] != packed.input_features or inputs.dtype != packed.dtype:
@@ -123,17 +130,31 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
     codes, scales, rotated = rotate_quantize(x, packed.rotation, bits=4, group_size=GROUP, return_rotated=True)
     la = torch.zeros((-(-m // TILE) * TILE, RANK_PAD), device=device, dtype=torch.float32)
     stream = native.stream_handle(device)
+    dense = (form == "dense") or (form == "auto" and bool(lib.xqt_b200_w4a4_dense_preferred(m, n, k)))
+    if form not in ("auto", "dense", "integer"):
+        raise XQTBackendError("form must be auto, dense or integer")
     with torch.cuda.device(device):
+        scratch = native.workspace(device, lib.xqt_b200_w4a4_dense_workspace_bytes(m, n, k) if dense else 256, "gemm")
         if packed.rank:
-            native.check(lib.xqt_b200_lowrank_down(rotated.data_ptr(), packed.down.data_ptr(), la.data_ptr(), m, k,
-                                                   native.DTYPE_CODE[packed.dtype], stream), "xqt_b200_lowrank_down")
+            if dense:
+                native.check(lib.xqt_b200_lowrank_down_tc(
+                    rotated.data_ptr(), packed.down.data_ptr(), la.data_ptr(), m, k, native.DTYPE_CODE[packed.dtype],
+                    scratch.data_ptr(), scratch.numel(), stream), "xqt_b200_lowrank_down_tc")
+            else:
+                native.check(lib.xqt_b200_lowrank_down(rotated.data_ptr(), packed.down.data_ptr(), la.data_ptr(), m, k,
+                                                       native.DTYPE_CODE[packed.dtype], stream), "xqt_b200_lowrank_down")
             if lora_scale != 1.0:
                 la.mul_(float(lora_scale))
-        scratch = native.workspace(device, 256, "gemm")
-        native.check(lib.xqt_b200_w4a4_gemm(
-            codes.data_ptr(), scales.data_ptr(), packed.qweight.data_ptr(), packed.aux.data_ptr(), la.data_ptr(),
-            native.ptr(packed.bias), out.data_ptr(), m, n, k, native.DTYPE_CODE[packed.dtype], scratch.data_ptr(),
-            scratch.numel(), stream), "xqt_b200_w4a4_gemm")
+        if dense:
+            native.check(lib.xqt_b200_w4a4_dense(
+                codes.data_ptr(), scales.data_ptr(), packed.qweight.data_ptr(), packed.weight_scales.data_ptr(),
+                la.data_ptr() if packed.rank else 0, native.ptr(packed.up), native.ptr(packed.bias), out.data_ptr(), m, n, k,
+                native.DTYPE_CODE[packed.dtype], scratch.data_ptr(), scratch.numel(), stream), "xqt_b200_w4a4_dense")
+        else:
+            native.check(lib.xqt_b200_w4a4_gemm(
+                codes.data_ptr(), scales.data_ptr(), packed.qweight.data_ptr(), packed.aux.data_ptr(), la.data_ptr(),
+                native.ptr(packed.bias), out.data_ptr(), m, n, k, native.DTYPE_CODE[packed.dtype], scratch.data_ptr(),
+                scratch.numel(), stream), "xqt_b200_w4a4_gemm")
     out = out.reshape(*inputs.shape[:-1], n)
     if return_parts:
         return out, {"codes": codes, "scales": scales, "rotated": rotated, "la": la[:m]}
