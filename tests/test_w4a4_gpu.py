@@ -102,7 +102,8 @@ def test_dense_form_is_the_default_from_m_256_and_matches_the_integer_form():
     torch.cuda.synchronize()
     assert native.workspace_status(DEV) == 0
     assert torch.equal(auto, dense)
-    assert o16.rel_l2(dense.cpu(), integer.cpu()) <= 1e-3
+    # each form is within 1e-3 of the reference (test_svdq_forward); against each other two bf16 roundings add up
+    assert o16.rel_l2(dense.cpu(), integer.cpu()) <= 2e-3
 
 
 def test_config3_full_size():
