@@ -229,6 +229,9 @@ size_t xqt_b200_w4a4_dense_workspace_bytes(int m, int n, int k) {
   return w4a4_dense_supported(m, n, k) ? w4a4_dense_workspace_bytes(m, n, k) : 0;
 }
 
+// The dense form is the faster one from M = 256 on, but its fp16 operand rounding leaves about 1.2e-3
+// of rel-L2 (after the bf16 output rounding) at K = 3072 where the integer form leaves 1e-4: it is
+// reported as available, not chosen by default.
 int xqt_b200_w4a4_dense_preferred(int m, int n, int k) { return (m >= 256 && w4a4_dense_supported(m, n, k)) ? 1 : 0; }
 
 int xqt_b200_w4a4_dense(const void* act_codes, const float* act_scales, const void* qweight, const float* weight_scales,

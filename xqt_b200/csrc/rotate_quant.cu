@@ -201,9 +201,23 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
   {
     T rounded[16];
 #pragma unroll
+    // the 16 column factors of this thread are contiguous (a rotation block is a multiple of 16 here,
+    // or the kernel is not chosen): four vector loads instead of sixteen indexed ones
+    float cs[16];
+    if (rot_kind != 0 && active) {
+      const float4* c4 = reinterpret_cast<const float4*>(column_scale + ((tid * 16) % rot_block));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 c = __ldg(c4 + j);
+        cs[4 * j] = c.x; cs[4 * j + 1] = c.y; cs[4 * j + 2] = c.z; cs[4 * j + 3] = c.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) cs[j] = 1.f;
+    }
     for (int i = 0; i < 16; ++i) {
       float r = v[i];
-      if (rot_kind != 0 && active) r = __fmul_rn(r, __ldg(column_scale + ((tid * 16 + i) % rot_block)));
+      if (rot_kind != 0 && active) r = __fmul_rn(r, cs[i]);
       rounded[i] = from_float<T>(r);
       v[i] = to_float<T>(rounded[i]);
       amax = fmaxf(amax, fabsf(v[i]));
@@ -241,7 +255,18 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
   if (active) {
     int8_t q[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = (int8_t)(int)fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), lo_clamp), hi_clamp);
+    // round(v / sc) with the IEEE quotient: a multiplication by the reciprocal gives the same integer
+    // unless it lands within 2^-10 of a rounding boundary; only those elements pay for the division
+    const float rcp = __frcp_rn(sc);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float quot = __fmul_rn(v[i], rcp);
+      const float nearest = rintf(quot);
+      const float dist = fabsf(fabsf(__fsub_rn(quot, nearest)) - 0.5f);   // distance from a half-integer
+      float code = nearest;
+      if (dist < 0x1p-10f && fabsf(quot) < 512.f) code = rintf(__fdiv_rn(v[i], sc));
+      q[i] = (int8_t)(int)fminf(fmaxf(code, lo_clamp), hi_clamp);
+    }
     *reinterpret_cast<uint4*>(codes + (size_t)row * k + tid * 16) = *reinterpret_cast<const uint4*>(q);
   }
 }
@@ -260,7 +285,8 @@ int rotate_quant_launch(const void* x, const float* column_scale, void* codes, f
   if (mode == 4) XQT_REQUIRE(group > 0 && k % group == 0);
   XQT_REQUIRE(act_dtype == XQT_B200_BF16 || act_dtype == XQT_B200_FP16);
   const bool group_ok = mode == 8 || (group >= 16 && group <= 512 && (group & (group - 1)) == 0);
-  if (k % 16 == 0 && k <= 16384 && group_ok && ((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 15) == 0 &&
+  const bool block_ok = rot_kind == 0 || (rot_block >= 16 && ((uintptr_t)column_scale & 15) == 0);   // vector loads of the column factors
+  if (k % 16 == 0 && k <= 16384 && group_ok && block_ok && ((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 15) == 0 &&
       (x_rot == nullptr || ((uintptr_t)x_rot & 15) == 0)) {
     const int threads = ceil_div(k / 16, 32) * 32;
     if (act_dtype == XQT_B200_BF16)
