@@ -55,6 +55,29 @@ def _log(msg: str) -> None:
     print(f"[bench rank {os.environ.get('RANK', '0')} +{time.perf_counter() - _T0:.1f}s] {msg}", file=sys.stderr, flush=True)
 
 
+_JSON_FD = None
+
+
+def _claim_stdout() -> None:
+    """Keep file descriptor 1 for the result line alone: libraries that print to stdout (NCCL's version
+    banner, for one) are sent to stderr for the rest of the run."""
+
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def _emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
+
+
 def weight_aux_bytes(k: int, n: int) -> int:
     return n * k // 2 + 2 * (n * (k // GROUP)) * 2
 
@@ -194,7 +217,7 @@ def run_reference_arm(args) -> None:
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    _emit(line)
 
 
 # ------------------------------------------------------------------------------------ GPU arm
@@ -434,7 +457,7 @@ def run_gpu_arm(args) -> None:
             "cores": torch.get_num_threads(), "kind": "port",
             "sample": "3 passes of the full sweep (16 problems) after 1 warm-up pass",
         }
-    print(json.dumps(line), flush=True)
+    _emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -587,7 +610,7 @@ def run_single_case(args) -> None:
     else:
         raise SystemExit(f"unknown --case {args.case!r}")
     us = _time_us(fn, torch.cuda.synchronize, reps=max(1, args.steps), warm=max(1, args.warmup))
-    print(json.dumps({"case": args.case, "us_per_call": us, "tera_ops_per_s": work / us / 1e6}), flush=True)
+    _emit({"case": args.case, "us_per_call": us, "tera_ops_per_s": work / us / 1e6})
 
 
 def run_single_problem(args) -> None:
@@ -615,8 +638,7 @@ def run_single_problem(args) -> None:
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / args.steps
-    print(json.dumps({"problem": [k, n, m], "us_per_launch_eager": us, "pool": pool,
-                      "gbs": algorithmic_bytes(k, n, m) / us / 1e3}), flush=True)
+    _emit({"problem": [k, n, m], "us_per_launch_eager": us, "pool": pool, "gbs": algorithmic_bytes(k, n, m) / us / 1e3})
 
 
 def main() -> None:
@@ -630,6 +652,7 @@ def main() -> None:
     parser.add_argument("--case", default=None,
                         help="mlp:M, w8a8 or w4a4: run only that configuration, eagerly (small command for ncu captures)")
     args = parser.parse_args()
+    _claim_stdout()
     if args.problem is not None:
         run_single_problem(args)
     elif args.case is not None:
