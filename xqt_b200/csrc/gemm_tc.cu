@@ -6,7 +6,8 @@
 // Warp roles (192 threads, one CTA per SM):
 //   warp 0      TMA producer: one elected thread arms the stage barrier and issues two tiled loads
 //   warp 1      allocates tensor memory; one elected thread issues the MMAs and commits
-//   warps 2..5  epilogue: each owns one 32-lane quarter of tensor memory (quarter = warp % 4)
+//   warps 2..9  epilogue: each owns one 32-lane quarter of tensor memory (quarter = warp % 4) and one
+//               half of the tile's columns (warps 2-5 the left half, 6-9 the right half)
 //
 // This file holds the int8 instantiation (W8A8: kind::i8, int32 accumulators over the whole K,
 // epilogue acc * a_scale[m] * w_scale[n] in fp32, the arithmetic of xqt's per-token int8 contract,
@@ -21,7 +22,7 @@ using namespace sm100;
 namespace gemm {
 constexpr int kBM = 128;
 constexpr int kRowBytes = 128;           // one swizzle row: 128 int8 or 64 16-bit elements of K
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;            // producer, MMA issuer, 8 epilogue warps
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 208 * 1024;
 enum Status : unsigned int { kOk = 0, kTimeout = 16 };
@@ -94,7 +95,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);
+      mbar_init(tempty_bar(b), 8);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tm_a);
@@ -166,7 +167,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
     }
   } else {
     // ---------------------------------------------------------------- epilogue warps
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     OutT* out = reinterpret_cast<OutT*>(p.out);
     uint32_t local = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
@@ -180,7 +181,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
       const OutT* res = reinterpret_cast<const OutT*>(p.residual);
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_wait_ld();
