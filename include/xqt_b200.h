@@ -41,8 +41,12 @@ typedef struct CUstream_st* xqt_b200_stream_t; /* == cudaStream_t */
 #define XQT_B200_VARIANT_SIMT 1     /* generic CUDA-core kernel: any shape, any group size        */
 #define XQT_B200_VARIANT_GEMV 2     /* M <= 16: split-K tensor-core GEMV, HBM-bound                */
 #define XQT_B200_VARIANT_TCGEN05 3  /* M > 16: TMA + tcgen05.mma with TMEM accumulators; needs group  */
-                                    /* size 64/128, K % 64 == 0, N % 8 == 0 and INTEGER zero points   */
-                                    /* (AUTO picks it only when zero_points is NULL)                  */
+                                    /* size 64/128, K % 64 == 0, N % 8 == 0.  Where                   */
+                                    /* xqt_b200_w4a16_two_pass(m) is 1 (every M > 16 by default) the  */
+                                    /* weights are first dequantised to an fp16 scratch, any zero     */
+                                    /* point; otherwise the single-pass kernel below                  */
+#define XQT_B200_VARIANT_TCGEN05_FUSED 4  /* single-pass form of 3: dequantisation inside the GEMM, no */
+                                    /* N*K*2 scratch, INTEGER zero points only                        */
 
 /* Replaces xqt_w4a16_sm89_version / xqt_awq_w4a16_sm89_version
  * (w4a16_sm89.cu:519-521, awq_w4a16_sm89_kernel.cu:909-911). */
@@ -96,7 +100,7 @@ int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_s
 /* 1 when XQT_B200_VARIANT_TCGEN05 serves this M in two passes (weights dequantised once per call
  * into an fp16 scratch in fp32 arithmetic, then a dense tcgen05 GEMM): in that form any zero
  * point is accepted, integer or not, and xqt_b200_w4a16_workspace_bytes includes N*K*2 bytes for
- * the scratch.  The single-pass form (smaller M) needs integer zero points.  No counterpart in
+ * the scratch.  The single-pass form (XQT_B200_VARIANT_TCGEN05_FUSED) needs integer zero points.  No counterpart in
  * xqt: its sm_89 GEMM has one form (xqt/kernels/ops/_impl/cute/awq_w4a16_sm89.py:225-262). */
 int xqt_b200_w4a16_two_pass(int m);
 

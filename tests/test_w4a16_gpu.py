@@ -237,9 +237,19 @@ def test_gemm_tcgen05_groups_signed_epilogue(group, symmetric):
     bias = torch.randn((n,), generator=seeded(8))
     residual = torch.randn((m, n), generator=seeded(9)).to(torch.bfloat16)
     out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=group, signed=symmetric, bias=bias,
-               residual=residual, variant="tcgen05")
+               residual=residual, variant="tcgen05_fused")
     ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=group, signed=symmetric, bias=bias,
                       residual=residual)
+    assert oracle.rel_l2(out, ref) <= TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(17, 128, 128), (128, 256, 256), (300, 392, 1280), (512, 4096, 4096)])
+def test_gemm_single_pass_variant_shapes(m, n, k):
+    """The single-pass kernel (dequantisation inside the GEMM, no weight scratch) on its own variant code."""
+
+    x, pw = _synthetic(n, k, m, seed=900 + m)
+    out = _run(x, pw.qweight, pw.scales, pw.zero_points, group=128, signed=False, variant="tcgen05_fused")
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=False)
     assert oracle.rel_l2(out, ref) <= TOL
 
 
@@ -250,7 +260,7 @@ def test_gemm_two_pass_groups_signed_epilogue(group, symmetric):
     from xqt_b200 import native
 
     m, n, k = 300, 264, 768
-    assert native.library().xqt_b200_w4a16_two_pass(m) == 1 and native.library().xqt_b200_w4a16_two_pass(255) == 0
+    assert native.library().xqt_b200_w4a16_two_pass(m) == 1 and native.library().xqt_b200_w4a16_two_pass(16) == 0
     x, pw = _synthetic(n, k, m, seed=35, symmetric=symmetric, group=group, param_dtype=torch.float32)
     bias = torch.randn((n,), generator=seeded(8))
     residual = torch.randn((m, n), generator=seeded(9)).to(torch.bfloat16)
@@ -276,6 +286,9 @@ def test_gemm_non_integer_zero_points_take_the_exact_path():
     m, n, k = 64, 128, 256
     x, pw = _synthetic(n, k, m, seed=44, param_dtype=torch.float32)
     zeros = pw.zero_points + 0.25
-    out = _run(x, pw.qweight, pw.scales, zeros, group=128, signed=False)     # auto must not pick tcgen05
+    out = _run(x, pw.qweight, pw.scales, zeros, group=128, signed=False)     # auto: two-pass GEMM (fp32 dequantisation)
     ref = oracle.gemm(x, pw.qweight, pw.scales, zeros, group_size=128, signed=False)
     assert oracle.rel_l2(out, ref) <= TOL
+    from xqt_b200.errors import XQTBackendError
+    with pytest.raises(XQTBackendError):     # the single-pass kernel folds the zero point into an integer subtraction
+        _run(x, pw.qweight, pw.scales, zeros, group=128, signed=False, variant="tcgen05_fused")

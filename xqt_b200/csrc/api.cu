@@ -21,7 +21,7 @@ int w4a16_decode_tc_launch(const void*, const void*, const void*, const float*, 
 size_t w4a16_decode_tc_workspace_bytes();
 bool w4a16_decode_tc_supported(int m, int n, int k, int group_size);
 int w4a16_gemm_tc_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int,
-                         int, int, int, int, int, int, void*, size_t, cudaStream_t);
+                         int, int, int, int, int, int, int, void*, size_t, cudaStream_t);
 int swiglu_launch(const void*, void*, int, int, int, cudaStream_t);
 size_t w4a16_gemm_tc_workspace_bytes(int m, int n, int k);
 bool w4a16_gemm_tc_any_zero_point(int m);
@@ -92,8 +92,9 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
   XQT_REQUIRE(activation != nullptr && qweight != nullptr && scales != nullptr && output != nullptr);
   if (out_f32) {
     // fp32 partial sums (K-sharded layers) are produced by the tensor-core GEMM only
-    XQT_REQUIRE(variant == XQT_B200_VARIANT_AUTO || variant == XQT_B200_VARIANT_TCGEN05);
-    variant = XQT_B200_VARIANT_TCGEN05;
+    XQT_REQUIRE(variant == XQT_B200_VARIANT_AUTO || variant == XQT_B200_VARIANT_TCGEN05 ||
+                variant == XQT_B200_VARIANT_TCGEN05_FUSED);
+    if (variant == XQT_B200_VARIANT_AUTO) variant = XQT_B200_VARIANT_TCGEN05;
   }
   if (variant == XQT_B200_VARIANT_AUTO) {
     variant = xqt_b200_w4a16_select_variant(m, n, k, padded_k, group_size, epilogue_activation, residual != nullptr);
@@ -115,13 +116,14 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
       return w4a16_gemv_launch(activation, qweight, scales, zero_points, bias, residual, output, m, n, k,
                                nibble_signed, act_dtype, param_dtype, workspace, workspace_bytes, s);
     case XQT_B200_VARIANT_TCGEN05:
+    case XQT_B200_VARIANT_TCGEN05_FUSED:
       XQT_REQUIRE(epilogue_activation == XQT_B200_ACT_NONE);
       XQT_REQUIRE(w4a16_gemm_tc_supported(m, n, k, padded_k, group_size));
       XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
       XQT_REQUIRE(((uintptr_t)activation & 15) == 0 && ((uintptr_t)qweight & 15) == 0);
       return w4a16_gemm_tc_launch(activation, qweight, scales, zero_points, bias, residual, output, m, n, k,
-                                  group_size, nibble_signed, act_dtype, param_dtype, out_f32, workspace,
-                                  workspace_bytes, s);
+                                  group_size, nibble_signed, act_dtype, param_dtype, out_f32,
+                                  variant == XQT_B200_VARIANT_TCGEN05_FUSED ? 1 : 0, workspace, workspace_bytes, s);
     default:
       return (int)cudaErrorInvalidValue;
   }

@@ -16,6 +16,8 @@
 // +-65504 outside it), once per call rather than once per weight tile.
 // Envelope: group size 64 or 128, K a multiple of 64, integer zero points; anything else is served
 // by the generic CUDA-core kernel.  Reference arithmetic: xqt/kernels/ops/gemm/reference.py:263-271,527.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100.cuh"
 #include <type_traits>
@@ -360,20 +362,31 @@ __global__ void __launch_bounds__(256) dequant_w4_f16_kernel(const uint8_t* __re
   }
 }
 
-// Above this M the weights are dequantised once per call into an fp16 scratch and multiplied by the
-// dense tcgen05 GEMM: the fused kernel converts the whole weight matrix again for every 128-row tile
-// of M, which costs more than one pass over N*K as soon as M spans a few tiles.
-constexpr int kDenseMinM = 256;
+// From this M on the weights are dequantised once per call into an fp16 scratch and multiplied by the
+// dense tcgen05 GEMM.  Measured on the 4096 x 14336 MLP block the two passes beat the fused
+// single-pass kernel at every M above the decode range (261 vs 328 us at M = 64, 342 vs 474 us at
+// M = 512, 1250 vs 2560 us at M = 4096), so the default threshold is the first M the decode kernels do
+// not serve; the single-pass kernel stays reachable as its own variant (no N*K*2 scratch).
+// XQT_B200_TWO_PASS_MIN_M in the environment moves the threshold (read once; tuning and tests).
+static int dense_min_m() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("XQT_B200_TWO_PASS_MIN_M");
+    const int parsed = e != nullptr ? atoi(e) : 0;
+    v = parsed >= 17 ? parsed : 17;
+  }
+  return v;
+}
 
 // [0,256) status, [256, 256+16 KiB) reserved for the ticket area of the M <= 16 kernel that shares this
 // workspace, then the fp16 copy of bf16 activations
 constexpr size_t kScratchOffset = 256 + 16384;
 size_t w4a16_gemm_tc_workspace_bytes(int m, int n, int k) {
   size_t bytes = kScratchOffset + (((size_t)m * k * 2 + 255) & ~(size_t)255);
-  if (m >= kDenseMinM) bytes += (size_t)n * k * 2;   // fp16 weights of the two-pass form
+  if (m >= dense_min_m()) bytes += (size_t)n * k * 2;   // fp16 weights of the two-pass form
   return bytes;
 }
-bool w4a16_gemm_tc_any_zero_point(int m) { return m >= kDenseMinM; }
+bool w4a16_gemm_tc_any_zero_point(int m) { return m >= dense_min_m(); }
 
 int gemm_f16_launch(const void* a, const void* b, const float* bias, const void* residual, void* out, int m, int n,
                     int k, int out_dtype, int out_f32, unsigned int* status, cudaStream_t stream);
@@ -411,13 +424,15 @@ static int launch_w4gemm(const void* x, const void* qw, W4GemmParams p, cudaStre
 
 int w4a16_gemm_tc_launch(const void* x, const void* qw, const void* scales, const void* zeros, const float* bias,
                          const void* residual, void* out, int m, int n, int k, int group_size, int nibble_signed,
-                         int act_dtype, int param_dtype, int out_f32, void* workspace, size_t workspace_bytes,
-                         cudaStream_t stream) {
+                         int act_dtype, int param_dtype, int out_f32, int single_pass, void* workspace,
+                         size_t workspace_bytes, cudaStream_t stream) {
   XQT_REQUIRE(w4a16_gemm_tc_supported(m, n, k, k, group_size));
+  const bool two_pass = !single_pass && m >= dense_min_m();
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256 && ((uintptr_t)out & 15) == 0);
   unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
   unsigned char* scratch = reinterpret_cast<unsigned char*>(workspace) + kScratchOffset;
-  if (act_dtype == XQT_B200_BF16 || m >= kDenseMinM) XQT_REQUIRE(workspace_bytes >= w4a16_gemm_tc_workspace_bytes(m, n, k));
+  if (two_pass) XQT_REQUIRE(workspace_bytes >= w4a16_gemm_tc_workspace_bytes(m, n, k));
+  else if (act_dtype == XQT_B200_BF16) XQT_REQUIRE(workspace_bytes >= kScratchOffset + (size_t)m * k * 2);
   if (act_dtype == XQT_B200_BF16) {
     __half* x16 = reinterpret_cast<__half*>(scratch);
     const size_t n8 = (size_t)m * k / 8;
@@ -425,7 +440,7 @@ int w4a16_gemm_tc_launch(const void* x, const void* qw, const void* scales, cons
     XQT_CUDA(cudaGetLastError());
     x = x16;
   }
-  if (m >= kDenseMinM) {
+  if (two_pass) {
     // two passes: weights -> fp16 scratch (any zero point, fp32 arithmetic), then the dense GEMM
     __half* w16 = reinterpret_cast<__half*>(scratch + (((size_t)m * k * 2 + 255) & ~(size_t)255));
     const size_t threads = (size_t)n * (k / 32);

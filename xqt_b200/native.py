@@ -26,7 +26,7 @@ LIBRARY_PATH = pathlib.Path(os.environ.get("XQT_B200_LIBRARY") or pathlib.Path(_
 
 FP16, BF16, FP32 = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
-VARIANT = {"auto": 0, "simt": 1, "gemv": 2, "tcgen05": 3}
+VARIANT = {"auto": 0, "simt": 1, "gemv": 2, "tcgen05": 3, "tcgen05_fused": 4}
 VARIANT_NAMES = {value: key for key, value in VARIANT.items()}
 DTYPE_CODE = {torch.float16: FP16, torch.bfloat16: BF16, torch.float32: FP32}
 

@@ -119,6 +119,8 @@ def w4a16_linear(
         variant = select_variant(m, n, k, padded_k, int(group_size), activation, residual is not None)
         if variant == "tcgen05" and not two_pass and not _integer_zero_points(zero_points):
             variant = "simt"
+    if variant == "tcgen05_fused" and not _integer_zero_points(zero_points):
+        raise XQTBackendError("the single-pass tcgen05 GEMM needs integer zero points")
     scratch = native.workspace(device, lib.xqt_b200_w4a16_workspace_bytes(m, n, k))
     stream = native.stream_handle(device)
     act_code, param_code = native.DTYPE_CODE[x.dtype], native.DTYPE_CODE[scales.dtype]
