@@ -246,6 +246,21 @@ int xqt_b200_w4a4_dense(const void* act_codes, const float* act_scales, const vo
 int xqt_b200_lowrank_down_tc(const void* rotated, const void* down, float* la, int m, int k, int act_dtype,
                              void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream);
 
+/* Reduction step of a row-parallel (K-sharded) linear over NVLink peer memory, with the epilogue
+ * fused in.  No counterpart in xqt (it has no multi-device execution; its metadata only records
+ * where a shard would go, xqt/kernels/ops/gemm/contracts.py:379-402).
+ *   partials[r]  device pointer, valid on THIS GPU, to rank r's fp32 partial [count] for this call
+ *                (rank r's own GEMV wrote it; peers' buffers are mapped symmetric / IPC memory)
+ *   flags[r]     device pointer to rank r's flag array, 8 x uint32, zero before the first call
+ *   call         1, 2, 3, ... the same on every rank; a rank must alternate between two partial
+ *                buffers from call to call (the hand-shake has no exit barrier)
+ *   output[count] = round(sum over ranks in rank order + bias[i mod n]); count, n multiples of 4
+ * Every rank launches it on its own GPU after its GEMV on the same stream.  The wait for the peers
+ * is bounded; a timeout is reported through the status word at workspace[0] (>= 256 bytes). */
+int xqt_b200_peer_allreduce(const void* const* partials, void* const* flags, int rank, int world,
+                            unsigned int call, long long count, int n, const float* bias, void* output,
+                            int out_dtype, void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream);
+
 /* SwiGLU gating between the projections of an MLP: output[m, i] = silu(gate_up[m, i]) * gate_up[m, inter + i],
  * evaluated in fp32 and rounded once.  gate_up is [M, 2*inter] (the gate and up projections fused
  * horizontally into one linear), output [M, inter].  Replaces xqt_convrot_w8a8_sm89_fused_swiglu

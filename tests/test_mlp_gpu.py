@@ -59,13 +59,27 @@ dev = torch.device("cuda", rank); torch.cuda.set_device(dev)
 dist.init_process_group("nccl", device_id=dev)
 mk = lambda n, k, s: quantize.quantize_w4_asymmetric(torch.randn((n, k), generator=seeded(s)) * 0.02, group_size=128)
 gate, up, down = mk(2048, 1024, 20), mk(2048, 1024, 21), mk(1024, 2048, 22)
-block = W4A16SwiGLUMLP(gate, up, down, device=dev, rank=rank, world=world)
+block = W4A16SwiGLUMLP(gate, up, down, device=dev, rank=rank, world=world)            # peer-memory reduction at M <= 16
+nccl_block = W4A16SwiGLUMLP(gate, up, down, device=dev, rank=rank, world=world, peer_reduce=False)
+assert block.execution_metadata()["reduction"].startswith("peer_allreduce_kernel")
+from xqt_b200 import native
 for m in (4, 64):
     x = torch.randn((m, 1024), generator=seeded(m)).to(torch.bfloat16).to(dev)
     y = block(x)
     torch.cuda.synchronize()
     if rank == 0:
         torch.save(y.cpu(), os.path.join(os.environ["XQT_OUT"], f"y{m}.pt"))
+# the peer-memory reduction over several calls (alternating slots), against NCCL on the same partials
+for step in range(5):
+    x = torch.randn((1 + 3 * step, 1024), generator=seeded(100 + step)).to(torch.bfloat16).to(dev)
+    a, b = block(x), nccl_block(x)
+    torch.cuda.synchronize()
+    assert native.workspace_status(dev) == 0
+    err = ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert err <= 4e-3, (step, err)      # two bf16 roundings of sums added in different orders
+    gathered = [torch.empty_like(a) for _ in range(world)]
+    dist.all_gather(gathered, a)
+    assert all(torch.equal(g, gathered[0]) for g in gathered)      # every rank holds the same bits
 dist.destroy_process_group()
 '''
 

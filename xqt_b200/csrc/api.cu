@@ -39,6 +39,8 @@ bool w4a4_dense_supported(int m, int n, int k);
 int w4a4_dense_launch(const void*, const float*, const void*, const float*, const float*, const float*, const float*, void*,
                       int, int, int, int, void*, size_t, cudaStream_t);
 int lowrank_down_tc_launch(const void*, const void*, float*, int, int, int, unsigned int*, cudaStream_t);
+int peer_allreduce_launch(const void* const*, void* const*, int, int, unsigned int, long long, int, const float*, void*, int,
+                          unsigned int*, cudaStream_t);
 }  // namespace xqt_b200
 
 using namespace xqt_b200;
@@ -252,6 +254,14 @@ int xqt_b200_lowrank_down_tc(const void* rotated, const void* down, float* la, i
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
   return lowrank_down_tc_launch(rotated, down, la, m, k, act_dtype, reinterpret_cast<unsigned int*>(workspace),
                                 (cudaStream_t)stream);
+}
+
+int xqt_b200_peer_allreduce(const void* const* partials, void* const* flags, int rank, int world, unsigned int call,
+                            long long count, int n, const float* bias, void* output, int out_dtype, void* workspace,
+                            size_t workspace_bytes, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
+  return peer_allreduce_launch(partials, flags, rank, world, call, count, n, bias, output, out_dtype,
+                               reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
 }
 
 int xqt_b200_swiglu(const void* gate_up, void* output, int m, int inter, int dtype, xqt_b200_stream_t stream) {

@@ -1,0 +1,116 @@
+// One-shot all-reduce over NVLink peer memory with the linear's epilogue fused in: the reduction step
+// of a row-parallel (K-sharded) quantized linear at decode sizes.
+//
+// Every rank's GEMV writes its fp32 partial [count] into its own slot of a buffer that all ranks of
+// the node have mapped (symmetric memory: plain peer pointers).  This kernel, launched
+// by every rank on its own GPU, (1) tells every peer that this rank's partial is complete and waits
+// until every peer has said the same, (2) reads the `world` partials straight from their owners'
+// memory, adds them in rank order -- the same order on every rank, so all ranks produce identical
+// bits -- adds the bias, rounds once and writes the rank's own full output.  For a few hundred KiB
+// this is one NVLink round trip instead of the launch and protocol latency of a library all-reduce.
+//
+// Hand-shake: flags[r] on rank q holds the last call number in which rank r signalled q.  Call
+// numbers only grow; partial buffers are used alternately (call e uses slot e & 1), so a rank can
+// only overwrite a slot two calls later, after every peer has signalled the call in between, which
+// a peer does only after its own kernel of the earlier call has finished reading.  No exit barrier
+// is needed.  The wait is bounded: after kSpin polls the kernel records a status word, skips the
+// wait and finishes (the output is then not the sum; the host reads the status).
+#include "common.cuh"
+
+namespace xqt_b200 {
+
+namespace par {
+constexpr int kMaxWorld = 8;
+constexpr unsigned int kSpin = 1u << 22;
+enum Status : unsigned int { kTimeout = 128 };
+}  // namespace par
+
+struct PeerReduceParams {
+  const float* partial[par::kMaxWorld];   // rank r's partial for this call (peer pointers)
+  unsigned int* flags[par::kMaxWorld];    // rank r's flag array [kMaxWorld] (peer pointers)
+  int rank, world;
+  unsigned int call;                      // this call's number (> 0, same on every rank)
+  long long count;                        // elements, a multiple of 4
+  int n;                                  // row length (bias period)
+  const float* bias;                      // [n] or null
+  void* out;                              // [count] in T
+  unsigned int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReduceParams p) {
+  using namespace par;
+  // (1) signal and wait.  Block 0 signals (the partial was written by the kernel before this one on
+  // the same stream, so it is complete); every block waits on this rank's own flag array.
+  if (blockIdx.x == 0 && threadIdx.x < p.world && (int)threadIdx.x != p.rank)
+    st_release_sys(p.flags[threadIdx.x] + p.rank, p.call);
+  if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
+    const unsigned int* f = p.flags[p.rank] + threadIdx.x;
+    unsigned int spins = 0;
+    // call numbers only grow: "signalled this call or a later one"
+    while ((int)(ld_acquire_sys(f) - p.call) < 0) {
+      if (++spins >= kSpin) {
+        atomicExch(p.status, (unsigned int)kTimeout);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  // (2) reduce in rank order, epilogue, store
+  const long long vecs = p.count / 4;
+  T* out = reinterpret_cast<T*>(p.out);
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 part[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      if (r < p.world) part[r] = __ldcg(reinterpret_cast<const float4*>(p.partial[r]) + v);   // all loads in flight
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      if (r < p.world) {
+        acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w;
+      }
+    if (p.bias != nullptr) {
+      const int col = (int)((v * 4) % p.n);   // n is a multiple of 4: the four elements share a row
+      const float4 b = *reinterpret_cast<const float4*>(p.bias + col);
+      acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+    }
+    T o[4] = {from_float<T>(acc.x), from_float<T>(acc.y), from_float<T>(acc.z), from_float<T>(acc.w)};
+    *reinterpret_cast<uint2*>(out + v * 4) = *reinterpret_cast<const uint2*>(o);
+  }
+}
+
+int peer_allreduce_launch(const void* const* partials, void* const* flags, int rank, int world, unsigned int call,
+                          long long count, int n, const float* bias, void* out, int out_dtype, unsigned int* status,
+                          cudaStream_t stream) {
+  using namespace par;
+  XQT_REQUIRE(world >= 2 && world <= kMaxWorld && rank >= 0 && rank < world && call > 0);
+  XQT_REQUIRE(count > 0 && count % 4 == 0 && n > 0 && n % 4 == 0 && count % n == 0);
+  XQT_REQUIRE(partials != nullptr && flags != nullptr && out != nullptr && status != nullptr);
+  XQT_REQUIRE(out_dtype == XQT_B200_BF16 || out_dtype == XQT_B200_FP16);
+  XQT_REQUIRE(((uintptr_t)out & 7) == 0 && (bias == nullptr || ((uintptr_t)bias & 15) == 0));
+  PeerReduceParams p{};
+  for (int r = 0; r < world; ++r) {
+    XQT_REQUIRE(partials[r] != nullptr && flags[r] != nullptr && ((uintptr_t)partials[r] & 15) == 0);
+    p.partial[r] = reinterpret_cast<const float*>(partials[r]);
+    p.flags[r] = reinterpret_cast<unsigned int*>(flags[r]);
+  }
+  p.rank = rank; p.world = world; p.call = call; p.count = count; p.n = n; p.bias = bias; p.out = out; p.status = status;
+  const long long vecs = count / 4;
+  long long blocks = (vecs + 255) / 256;
+  if (blocks > 148) blocks = 148;
+  if (out_dtype == XQT_B200_BF16) peer_allreduce_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  else peer_allreduce_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  return launch_status();
+}
+
+}  // namespace xqt_b200

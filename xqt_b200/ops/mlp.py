@@ -13,6 +13,8 @@ sums of down are added with one NCCL all-reduce and rounded once.
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -69,7 +71,7 @@ class _Linear:
         self.tiled = prepare_decode(self.qweight, self.scales, self.zeros, group_size=self.group, nibble_signed=self.signed)
         self._bound: dict[tuple[int, torch.dtype], object] = {}
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         m = int(x.shape[0])
         odt = self.dtype if out_dtype is None else out_dtype
         if m <= 16 and (odt == self.dtype or self.tiled.layout == "rows128"):
@@ -77,9 +79,9 @@ class _Linear:
             if run is None:
                 run = bind_w4a16_decode(self.tiled, rows=m, dtype=self.dtype, out_dtype=odt)
                 self._bound[(m, odt)] = run
-            return run(x)
+            return run(x, out) if out is not None else run(x)
         return w4a16_linear(x, self.qweight, self.scales, self.zeros, group_size=self.group,
-                            nibble_signed=self.signed, k=self.k, out_dtype=odt)
+                            nibble_signed=self.signed, k=self.k, out_dtype=odt, out=out)
 
 
 class W4A16SwiGLUMLP:
@@ -87,7 +89,8 @@ class W4A16SwiGLUMLP:
     ``down`` is ``[hidden, inter]``; they are sharded here for ``rank`` of ``world``."""
 
     def __init__(self, gate: PackedWeight, up: PackedWeight, down: PackedWeight, *, device: torch.device,
-                 dtype: torch.dtype = torch.bfloat16, rank: int = 0, world: int = 1, group=None) -> None:
+                 dtype: torch.dtype = torch.bfloat16, rank: int = 0, world: int = 1, group=None,
+                 peer_reduce: bool | None = None) -> None:
         if world > 1:
             gate = shard_packed_weight(gate, world=world, rank=rank, axis=0)
             up = shard_packed_weight(up, world=world, rank=rank, axis=0)
@@ -96,11 +99,24 @@ class W4A16SwiGLUMLP:
         self.gate_up = _Linear(_concat_rows(gate, up), device, dtype)
         self.down = _Linear(down, device, dtype)
         self.hidden, self.inter_local = self.down.n, self.down.k
+        # decode sizes (M <= 16): the partial sums of down are added by our own kernel over NVLink peer
+        # memory instead of an NCCL all-reduce (XQT_B200_PEER_REDUCE=0 or peer_reduce=False: NCCL)
+        if peer_reduce is None:
+            peer_reduce = os.environ.get("XQT_B200_PEER_REDUCE", "1") not in {"0", ""}
+        self._peer = None
+        if world > 1 and peer_reduce and self.down.tiled.layout == "rows128":
+            from ..parallel import PeerAllReduce
+
+            self._peer = PeerAllReduce(device, 16 * self.hidden, group)
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         h = swiglu(self.gate_up(x))
         if self.world == 1:
             return self.down(h)
+        m = int(h.shape[0])
+        if self._peer is not None and m <= 16:
+            self.down(h, out_dtype=torch.float32, out=self._peer.partial(m, self.hidden))
+            return self._peer.reduce(m, self.hidden, dtype=self.dtype)
         partial = self.down(h, out_dtype=torch.float32)
         dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
         return partial.to(self.dtype)
@@ -111,6 +127,7 @@ class W4A16SwiGLUMLP:
 
         return {
             "implementation": "b200_w4a16_swiglu_mlp", "world": self.world,
+            "reduction": "none" if self.world == 1 else ("peer_allreduce_kernel (M <= 16) / NCCL all-reduce" if self._peer else "NCCL all-reduce"),
             "decode_layout": self.gate_up.tiled.layout, "hidden": self.hidden, "inter_local": self.inter_local,
             "kernels": {"m<=16": "w4a16_decode_tc_kernel" if self.gate_up.tiled.layout == "rows128" else "w4a16_decode_kernel",
                         "m>16": "gemm_w4a16_kernel", "gating": "swiglu_kernel"},

@@ -14,7 +14,8 @@ module fills and consumes those fields:
 One process per GPU, ``torch.distributed`` for the plumbing; collectives run on the current stream
 after the kernels that feed them.  The local computation is injected (``local_linear``), so the
 partition arithmetic and the collective wiring are tested on CPU ranks with the gloo backend.
-Every kernel reads only its own GPU's memory: peers' data arrive through NCCL into local buffers.
+The GEMM / GEMV kernels read only their own GPU's memory; the one kernel that reads peers' memory is the
+decode-size reduction of ``PeerAllReduce`` (plain peer loads over NVLink, no cluster-wide TMA loads).
 """
 
 from __future__ import annotations
@@ -140,10 +141,78 @@ class TensorParallelSwiGLUMLP:
         return self.down(self.swiglu(self.gate(x), self.up(x)))
 
 
+class PeerAllReduce:
+    """Sum of the ranks' fp32 partials over NVLink peer memory, epilogue (bias, rounding) fused in.
+
+    One instance per (process group, device).  ``partial(call_rows, n)`` hands out this rank's slot of
+    the shared buffer for the next call (the row-parallel GEMV writes its fp32 result straight into
+    it), ``reduce(rows, n, bias, dtype)`` launches the kernel that waits for the peers, adds the
+    partials in rank order and returns the rank's own full ``[rows, n]`` output.  Buffers come from
+    torch's symmetric memory (plain peer pointers).  Meant for decode sizes (a few hundred KiB): every
+    rank reads every partial once; larger reductions stay with NCCL.
+    """
+
+    MAX_WORLD = 8
+
+    def __init__(self, device: torch.device, max_elements: int, group=None) -> None:
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import native
+
+        group = dist.group.WORLD if group is None else group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if not 2 <= self.world <= self.MAX_WORLD:
+            raise XQTBackendError(f"PeerAllReduce serves 2..{self.MAX_WORLD} ranks")
+        self.device, self.max_elements = device, int(-(-max_elements // 4) * 4)
+        # two alternating slots of fp32 partials, then the flag words
+        self._buffer = symm_mem.empty(2 * self.max_elements + 64, dtype=torch.float32, device=device)
+        self._buffer.zero_()
+        handle = symm_mem.rendezvous(self._buffer, group)
+        self._handle = handle
+        base = [int(ptr) for ptr in handle.buffer_ptrs]
+        self._slot_ptrs = [[b + slot * self.max_elements * 4 for b in base] for slot in (0, 1)]
+        flag_ptrs = [b + 2 * self.max_elements * 4 for b in base]
+        array = ctypes.c_void_p * self.world
+        self._partials = [array(*ptrs) for ptrs in self._slot_ptrs]
+        self._flags = array(*flag_ptrs)
+        self._call = 0
+        self._native = native
+        torch.cuda.synchronize(device)
+        dist.barrier(group)          # every rank's zeros are in place before anybody signals
+
+    def partial(self, rows: int, n: int) -> torch.Tensor:
+        """This rank's fp32 ``[rows, n]`` slot for the NEXT call of ``reduce``."""
+
+        count = rows * n
+        if count > self.max_elements:
+            raise XQTBackendError("PeerAllReduce: partial larger than the buffer it was built with")
+        slot = (self._call + 1) & 1
+        return self._buffer[slot * self.max_elements: slot * self.max_elements + count].view(rows, n)
+
+    def reduce(self, rows: int, n: int, *, bias: torch.Tensor | None = None, dtype: torch.dtype = torch.bfloat16,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+        native = self._native
+        if n % 4 or dtype not in (torch.float16, torch.bfloat16):
+            raise XQTBackendError("PeerAllReduce: N must be a multiple of 4 and the output fp16 or bf16")
+        self._call += 1
+        if out is None:
+            out = torch.empty((rows, n), device=self.device, dtype=dtype)
+        scratch = native.workspace(self.device, 256, "peer")
+        with torch.cuda.device(self.device):
+            code = native.library().xqt_b200_peer_allreduce(
+                self._partials[self._call & 1], self._flags, self.rank, self.world, self._call & 0xFFFFFFFF or 1, rows * n, n,
+                native.ptr(bias), out.data_ptr(), native.DTYPE_CODE[dtype], scratch.data_ptr(), scratch.numel(),
+                native.stream_handle(self.device))
+        native.check(code, "xqt_b200_peer_allreduce")
+        return out
+
+
 def _default_swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     from .ops.mlp import swiglu
 
     return swiglu(torch.cat((gate, up), dim=1))
 
 
-__all__ = ["ColumnParallelLinear", "RowParallelLinear", "TensorParallelSwiGLUMLP", "shard_packed_weight"]
+__all__ = ["ColumnParallelLinear", "PeerAllReduce", "RowParallelLinear", "TensorParallelSwiGLUMLP", "shard_packed_weight"]
