@@ -142,6 +142,34 @@ int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, co
                              int out_dtype, void* workspace, size_t workspace_bytes,
                              xqt_b200_stream_t stream);
 
+/* W4A16 decode (M <= 16) as a cluster split-K GEMV, execution layout b200_w4_lanes_v1: the default
+ * decode kernel.  Same replaced reference entry points and arithmetic as xqt_b200_w4a16_decode_tiled
+ * (xqt_awq_w4a16_sm89_decode / _pack, awq_w4a16_sm89_kernel.cu:728-784; the execution layout plays the
+ * role of sm89_awq_w4a16_interleaved_v1, awq_w4a16_decode_sm89.py:16-98).
+ *   lane_weights  uint8 [ceil(N/128)][K/128][4 warps][2 row tiles][32 lanes][32]   (prepack.py: lanes_w4)
+ *                 unsigned codes; two's-complement nibbles are stored as code + 8 and announced by
+ *                 nibble_signed = 1
+ *   lane_params   param_dtype [ceil(N/128)][K/128][128/group_size][4 warps][8][4][2] = (scale, zero point)
+ *   group_size in {64, 128}; K a multiple of 128; 1 <= M <= 16; any zero point (integer or not).
+ *   output        [M, N] act_dtype, or fp32 (out_dtype = XQT_B200_FP32: unrounded partial sums of a
+ *                 K-sharded layer, then no residual)
+ *   status        NULL, or a device word the kernel sets to 64 when the bounded wait for its
+ *                 activation copy ran out (the result is then undefined; nothing hangs)
+ * Needs no workspace: the K pieces of a tile are the CTAs of one thread-block cluster and reduce
+ * through distributed shared memory in a fixed order (bit-reproducible). */
+int xqt_b200_w4a16_decode_lanes_supported(int m, int n, int k, int group_size);
+/* How the kernel would cut this problem: *warp_quads K pieces inside a CTA (1, 2 or 4) times *cluster
+ * CTAs per 128-channel tile (1..8).  set_plan forces one split for every later call of the process
+ * (a tuning aid; (0, 0) returns to the automatic choice); a forced split is still shrunk to what the
+ * problem's K allows.  No counterpart in the reference, whose decode kernel has one fixed shape
+ * (awq_w4a16_sm89_kernel.cu:26-60). */
+int xqt_b200_w4a16_decode_lanes_plan(int m, int n, int k, int group_size, int* warp_quads, int* cluster);
+int xqt_b200_w4a16_decode_lanes_set_plan(int warp_quads, int cluster);
+int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights, const void* lane_params,
+                                const float* bias, const void* residual, void* output, int m, int n, int k,
+                                int group_size, int nibble_signed, int act_dtype, int param_dtype,
+                                int out_dtype, unsigned int* status, xqt_b200_stream_t stream);
+
 /* W4A16 decode with the scratch built into the library: same operation, arguments and result as
  * xqt_b200_w4a16_decode_tiled, minus the workspace pair.  It has no counterpart in the reference.
  *

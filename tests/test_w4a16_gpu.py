@@ -213,6 +213,91 @@ def test_decode_tc_groups_dtypes_epilogue(group, dtype, symmetric):
     assert oracle.rel_l2(out, ref) <= TOL
 
 
+# ---------------------------------------------------------------------------- cluster split-K decode kernel
+
+
+def _lanes_run(x, pw, *, bias=None, residual=None, out_dtype=None):
+    from xqt_b200 import native, prepack
+    from xqt_b200.ops.w4a16 import bind_w4a16_decode
+
+    dev = torch.device("cuda", 0)
+    mv = lambda t: None if t is None else t.to(dev)
+    tiled = prepack.lanes_w4(mv(pw.qweight), mv(pw.scales), mv(pw.zero_points), group_size=pw.metadata.group_size,
+                             nibble_signed=pw.metadata.nibble_signed)
+    run = bind_w4a16_decode(tiled, rows=int(x.shape[0]), dtype=x.dtype, bias=mv(bias), out_dtype=out_dtype)
+    out = run(mv(x), None, mv(residual))
+    torch.cuda.synchronize()
+    assert native.workspace_status(dev) == 0
+    return out.cpu()
+
+
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+@pytest.mark.parametrize("n,k", [(128, 128), (128, 256), (4096, 4096), (1024, 4096), (4096, 14336), (14336, 4096),
+                                 (200, 512), (72, 768), (512, 1792), (1792, 4096)])
+def test_decode_lanes_shapes(m, n, k):
+    if (n, k) in {(4096, 14336), (14336, 4096)} and m not in (1, 16):
+        pytest.skip("large shapes: first and last M only")
+    x, pw = _synthetic(n, k, m, seed=800 + m)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=False)
+    out = _lanes_run(x, pw)
+    assert oracle.rel_l2(out, ref) <= TOL
+    assert torch.equal(out, _lanes_run(x, pw))          # fixed reduction order: bit-reproducible
+
+
+@pytest.mark.parametrize("m", [3, 9, 13])
+def test_decode_lanes_ragged_m(m):
+    x, pw = _synthetic(392, 1280, m, seed=820 + m)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=False)
+    assert oracle.rel_l2(_lanes_run(x, pw), ref) <= TOL
+
+
+@pytest.mark.parametrize("group", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("symmetric", [False, True])
+def test_decode_lanes_groups_dtypes_epilogue(group, dtype, symmetric):
+    n, k, m = 392, 1280, 13
+    x, pw = _synthetic(n, k, m, seed=60 + group, dtype=dtype, symmetric=symmetric, group=group,
+                       param_dtype=torch.float32 if group == 64 else torch.bfloat16)
+    bias = torch.randn((n,), generator=seeded(8))
+    residual = torch.randn((m, n), generator=seeded(9)).to(dtype)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=group, signed=symmetric, bias=bias,
+                      residual=residual)
+    out = _lanes_run(x, pw, bias=bias, residual=residual)
+    assert oracle.rel_l2(out, ref) <= TOL
+
+
+@pytest.mark.parametrize("param_dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_decode_lanes_fractional_zero_points_and_fp32_output(param_dtype):
+    """Zero points need not be integers here (the zero point only enters the fp32 fold), and the
+    unrounded fp32 sums of a K-sharded layer come from the same kernel."""
+
+    from xqt_b200.contracts import PackedWeight
+
+    n, k, m = 264, 768, 5
+    x, pw = _synthetic(n, k, m, seed=77, param_dtype=param_dtype)
+    zeros = (pw.zero_points.float() + 0.25).to(param_dtype)
+    pw2 = PackedWeight(qweight=pw.qweight, scales=pw.scales, zero_points=zeros, metadata=pw.metadata)
+    ref = oracle.gemm(x, pw.qweight, pw.scales, zeros, group_size=128, signed=False)
+    assert oracle.rel_l2(_lanes_run(x, pw2), ref) <= TOL
+    out32 = _lanes_run(x, pw2, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32
+    ref32 = oracle.gemm(x.float(), pw.qweight, pw.scales, zeros, group_size=128, signed=False)
+    assert oracle.rel_l2(out32, ref32.float()) <= 1e-4
+
+
+def test_decode_lanes_is_the_default_decode_layout():
+    from xqt_b200.ops.w4a16 import prepare_decode
+
+    x, pw = _synthetic(256, 512, 2, seed=5)
+    dev = torch.device("cuda", 0)
+    tiled = prepare_decode(pw.qweight.to(dev), pw.scales.to(dev), pw.zero_points.to(dev), group_size=128,
+                           nibble_signed=False)
+    assert tiled.layout == "lanes"
+    forced = prepare_decode(pw.qweight.to(dev), pw.scales.to(dev), pw.zero_points.to(dev), group_size=128,
+                            nibble_signed=False, layout="rows128")
+    assert forced.layout == "rows128"
+
+
 # ---------------------------------------------------------------------------- tcgen05 GEMM (M > 16)
 
 

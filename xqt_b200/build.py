@@ -23,7 +23,7 @@ STAMP = PACKAGE / "libxqt_b200.so.key"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # -fmad=false: no implicit multiply-add contraction, so fp32 results that the tests compare bit for
 # bit (rotation, quantisation) do not depend on the compiler; the kernels spell out fmaf where they want it
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-fmad=false", "-Xcompiler", "-fPIC", "-shared"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-fmad=false", "--threads", "8", "-Xcompiler", "-fPIC", "-shared"]
 
 
 def sources() -> list[pathlib.Path]:

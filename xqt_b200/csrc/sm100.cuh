@@ -100,6 +100,49 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(map) : "memory");
 }
 
+// ---------------------------------------------------------------- thread-block clusters
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
+  return r;
+}
+// Cluster-wide barrier in its split form.  Every thread of every CTA of the cluster takes part in
+// each phase; the hardware schedules the CTAs of a cluster together, so the wait cannot outlast them.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+// address of this CTA's shared-memory location `saddr` as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t caddr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(caddr), "f"(v) : "memory");
+}
+
+// ---------------------------------------------------------------- wide loads
+// 32 bytes per thread from global memory that is read once: no L1 allocation, first in line for
+// L2 eviction.  The address must be 32-byte aligned.
+__device__ __forceinline__ void ldg256_stream(uint32_t (&r)[8], const void* p) {
+  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(p));
+}
+__device__ __forceinline__ void ldg128_stream(uint32_t (&r)[4], const void* p) {
+  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "l"(p));
+}
+__device__ __forceinline__ void ldg64_stream(uint32_t (&r)[2], const void* p) {
+  asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "l"(p));
+}
+
 // ---------------------------------------------------------------- tensor memory
 // allocate `cols` (power of two >= 32) columns; the base address is written to *slot (shared)
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {

@@ -47,6 +47,10 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_decode_tc_workspace_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_tc_supported": (_I, [_I] * 4),
     "xqt_b200_w4a16_decode_tc": (_I, [_P] * 6 + [_I] * 8 + [_P, _Z, _P]),
+    "xqt_b200_w4a16_decode_lanes_supported": (_I, [_I] * 4),
+    "xqt_b200_w4a16_decode_lanes_plan": (_I, [_I] * 4 + [ctypes.POINTER(_I), ctypes.POINTER(_I)]),
+    "xqt_b200_w4a16_decode_lanes_set_plan": (_I, [_I, _I]),
+    "xqt_b200_w4a16_decode_lanes": (_I, [_P] * 6 + [_I] * 8 + [_P, _P]),
     "xqt_b200_w4a16_decode_tiled_static": (_I, [_P] * 6 + [_I] * 8 + [_P]),
     "xqt_b200_w4a16_decode_static_scratch_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_static_max_n": (_I, []),
@@ -147,11 +151,30 @@ def workspace(device: torch.device, nbytes: int, tag: str = "run") -> torch.Tens
     return buffer
 
 
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device 32-bit word (zero until a kernel's bounded wait runs out) handed to the entry
+    points that take a status pointer instead of a workspace."""
+
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(index)
+    if word is None:
+        word = torch.zeros(64, dtype=torch.int32, device=torch.device("cuda", index))
+        _status_words[index] = word
+    return word
+
+
 def workspace_status(device: torch.device) -> int:
-    """Status word of the current stream's scratch buffer (0 = every bounded wait completed)."""
+    """Worst status word of the current stream's scratch buffers and of the device's status word
+    (0 = every bounded wait completed)."""
 
     index = device.index if device.index is not None else torch.cuda.current_device()
     worst = 0
+    word = _status_words.get(index)
+    if word is not None:
+        worst = int(word[0].item()) & 0xFFFFFFFF
     for (dev_index, stream, _tag), buffer in list(_workspaces.items()):
         if dev_index != index or stream != stream_handle(device):
             continue
@@ -164,5 +187,5 @@ def workspace_status(device: torch.device) -> int:
 
 __all__ = [
     "ACT", "BF16", "DTYPE_CODE", "FP16", "FP32", "LIBRARY_PATH", "SIGNATURES", "VARIANT", "VARIANT_NAMES",
-    "available", "check", "library", "ptr", "stream_handle", "version", "workspace", "workspace_status",
+    "available", "check", "library", "ptr", "status_word", "stream_handle", "version", "workspace", "workspace_status",
 ]

@@ -6,8 +6,8 @@ gates with one vectorised kernel (xqt/kernels/ops/_impl/cute/convrot_w8a8_sm89.p
 convrot_w8a8_sm89_kernel.cu:756-837).
 
 Per call and rank: one linear for the concatenated ``[gate; up]`` shard, one SwiGLU kernel, one
-linear for the down shard; at M <= 16 the linears are the tcgen05 decode kernel, above it the
-tcgen05 GEMM.  With more than one rank gate/up are split over N, down over K, and the fp32 partial
+linear for the down shard; at M <= 16 the linears are the cluster split-K decode kernel, above it
+the tcgen05 GEMM.  With more than one rank gate/up are split over N, down over K, and the fp32 partial
 sums of down are added with one NCCL all-reduce and rounded once.
 """
 
@@ -74,7 +74,7 @@ class _Linear:
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         m = int(x.shape[0])
         odt = self.dtype if out_dtype is None else out_dtype
-        if m <= 16 and (odt == self.dtype or self.tiled.layout == "rows128"):
+        if m <= 16 and (odt == self.dtype or self.tiled.layout in ("rows128", "lanes")):
             run = self._bound.get((m, odt))
             if run is None:
                 run = bind_w4a16_decode(self.tiled, rows=m, dtype=self.dtype, out_dtype=odt)
@@ -104,7 +104,7 @@ class W4A16SwiGLUMLP:
         if peer_reduce is None:
             peer_reduce = os.environ.get("XQT_B200_PEER_REDUCE", "1") not in {"0", ""}
         self._peer = None
-        if world > 1 and peer_reduce and self.down.tiled.layout == "rows128":
+        if world > 1 and peer_reduce and self.down.tiled.layout in ("rows128", "lanes"):
             from ..parallel import PeerAllReduce
 
             self._peer = PeerAllReduce(device, 16 * self.hidden, group)
@@ -129,7 +129,8 @@ class W4A16SwiGLUMLP:
             "implementation": "b200_w4a16_swiglu_mlp", "world": self.world,
             "reduction": "none" if self.world == 1 else ("peer_allreduce_kernel (M <= 16) / NCCL all-reduce" if self._peer else "NCCL all-reduce"),
             "decode_layout": self.gate_up.tiled.layout, "hidden": self.hidden, "inter_local": self.inter_local,
-            "kernels": {"m<=16": "w4a16_decode_tc_kernel" if self.gate_up.tiled.layout == "rows128" else "w4a16_decode_kernel",
+            "kernels": {"m<=16": {"lanes": "w4a16_decode_cl_kernel", "rows128": "w4a16_decode_tc_kernel"}.get(
+                            self.gate_up.tiled.layout, "w4a16_decode_kernel"),
                         "m>16": "gemm_w4a16_kernel", "gating": "swiglu_kernel"},
         }
 

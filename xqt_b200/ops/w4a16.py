@@ -211,6 +211,8 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
         raise XQTBackendError("B200 W4A16 decode out_dtype must be the activation dtype or float32")
     lib = native.library()
     use_tc = tiled.layout == "rows128"
+    if tiled.layout == "lanes":
+        return _bind_decode_lanes(tiled, rows=rows, dtype=dtype, bias=bias, odt=odt)
     if use_tc:
         if not tiled.integer_zero_points:
             raise XQTBackendError("the tcgen05 decode kernel needs integer zero points in [0, 119]")
@@ -261,13 +263,67 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
     return run
 
 
+def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None, odt: torch.dtype):
+    """``bind_w4a16_decode`` for the ``lanes`` layout (cluster split-K kernel: no workspace)."""
+
+    device = tiled.weights.device
+    n, k = tiled.n, tiled.k
+    lib = native.library()
+    if not lib.xqt_b200_w4a16_decode_lanes_supported(rows, n, k, tiled.group_size):
+        raise XQTBackendError(f"B200 W4A16 decode does not cover M={rows}, N={n}, K={k}, group={tiled.group_size}")
+    if tiled.params.dtype not in native.DTYPE_CODE or not tiled.weights.is_contiguous() or not tiled.params.is_contiguous():
+        raise XQTBackendError("B200 W4A16 decode: tiled tensors must be contiguous, params fp16/bf16/fp32")
+    bias32 = None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous()
+    if bias32 is not None and bias32.numel() != n:
+        raise XQTBackendError("B200 W4A16 bias must have N elements")
+    fn = lib.xqt_b200_w4a16_decode_lanes
+    head = (tiled.weights.data_ptr(), tiled.params.data_ptr(), native.ptr(bias32))
+    tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), native.DTYPE_CODE[dtype],
+            native.DTYPE_CODE[tiled.params.dtype], native.DTYPE_CODE[odt])
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    status = native.status_word(device)
+    status_ptr = status.data_ptr()
+    keep = (tiled, bias32, status)  # noqa: F841 - the closure owns references
+
+    def run(x: torch.Tensor, out: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
+        if x.dtype != dtype or x.ndim != 2 or x.shape[0] != rows or x.shape[1] != k or not x.is_contiguous() \
+                or x.device != device:
+            raise XQTBackendError("bound B200 W4A16 decode: activation shape, dtype, device or layout mismatch")
+        if torch.cuda.current_device() != index:
+            raise XQTBackendError("bound B200 W4A16 decode: make the weight's device current before calling")
+        if out is None:
+            out = torch.empty((rows, n), device=device, dtype=odt)
+        if residual is not None and (residual.dtype != dtype or tuple(residual.shape) != (rows, n)
+                                     or not residual.is_contiguous() or odt != dtype):
+            raise XQTBackendError("bound B200 W4A16 decode: residual must be contiguous [M,N] in the activation dtype")
+        code = fn(x.data_ptr(), *head, native.ptr(residual), out.data_ptr(), *tail, status_ptr,
+                  torch.cuda.current_stream(device).cuda_stream)
+        if code != 0:
+            native.check(code, "xqt_b200_w4a16_decode_lanes")
+        return out
+
+    return run
+
+
 def prepare_decode(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tensor | None, *,
-                   group_size: int, nibble_signed: bool, k: int | None = None):
-    """Build the decode execution layout of a canonical W4 layer: the tcgen05 layout when the
-    layer qualifies (group 64/128, integer zero points), else the mma.sync layout."""
+                   group_size: int, nibble_signed: bool, k: int | None = None, layout: str = "auto"):
+    """Build the decode execution layout of a canonical W4 layer.  ``auto``: the cluster split-K
+    layout (``lanes``) when the layer qualifies (group 64/128, K a multiple of 128 within the
+    kernel's range); else the tcgen05 layout (``rows128``: group 64/128, integer zero points); else
+    the stream-K mma.sync layout (``tile128``).  A layout name forces that layout."""
 
     from .. import prepack
 
+    n, kk = int(qweight.shape[0]), int(qweight.shape[1]) * 2 if k is None else int(k)
+    if layout not in ("auto", "lanes", "rows128", "tile128"):
+        raise XQTBackendError(f"unknown decode layout {layout!r}")
+    if layout == "lanes" or (layout == "auto" and group_size in (64, 128) and kk % 128 == 0 and
+                             native.library().xqt_b200_w4a16_decode_lanes_supported(16, n, kk, int(group_size))):
+        return prepack.lanes_w4(qweight, scales, zero_points, group_size=group_size, nibble_signed=nibble_signed, k=k)
+    if layout == "tile128":
+        return prepack.tile_w4(qweight, scales, zero_points, group_size=group_size, nibble_signed=nibble_signed, k=k)
+    if layout == "rows128":
+        return prepack.rows_w4(qweight, scales, zero_points, group_size=group_size, nibble_signed=nibble_signed, k=k)
     if group_size in (64, 128):
         tiled = prepack.rows_w4(qweight, scales, zero_points, group_size=group_size, nibble_signed=nibble_signed, k=k)
         if tiled.integer_zero_points:

@@ -15,6 +15,17 @@ pack kernel xqt/kernels/jit/csrc/quantization/awq_w4a16_sm89_kernel.cu:405-479).
            one half of an ``mma.m16n8k16`` B fragment wants.  Rows past N are zero.
   params   ``[tiles][kblocks][128/group][128 channels][2]`` = (scale, zero point) in the dtype of
            the canonical scales (zero point 0 when the weight is symmetric).
+
+``b200_w4_lanes_v1`` (cluster split-K decode GEMV, the default decode layout):
+  weights  uint8 ``[N/128 tiles][K/128 kblocks][4 warps][2 row tiles][32 lanes][32 bytes]``
+           Lane ``4*r + c`` of (warp ``w``, row tile ``t``) holds, for the eight ``mma.m16n8k16`` steps
+           ``j`` of the block, one 32-bit word each.  Its nibble positions 0..7 carry channels
+           ``128*tile + 32*w + 16*t + r + (0,8,0,8,0,8,0,8)`` at ``k = 128*kblock + 32*(j//2) + 8*c +
+           4*(j%2) + (0,0,2,2,1,1,3,3)``: ``(word >> 4*i) & 0x000f000f`` is register ``i`` of the A
+           fragment, and the 16 bytes of activations a lane needs for two steps are contiguous.
+           Codes are unsigned; two's-complement nibbles are stored as ``code + 8``.  Rows past N are zero.
+  params   ``[tiles][kblocks][128/group][4 warps][8 r][4][2]``: the (scale, zero point) pairs of the
+           four channels ``32*w + 16*t + 8*h + r`` a lane's accumulators belong to, index ``2*t + h``.
 """
 
 from __future__ import annotations
@@ -35,8 +46,10 @@ class TiledW4:
     """Decode execution layout of one W4 layer (see module docstring).
 
     ``layout`` is ``"tile128"`` (weights ``[tiles, kblocks, 16, 32, 16]``, lane-major, for the
-    mma.sync decode kernel) or ``"rows128"`` (weights ``[tiles, kblocks, 4, 128, 16]``, one 16-byte
-    chunk of 32 K per channel, for the tcgen05 decode kernel whose threads each own a channel).
+    stream-K mma.sync decode kernel), ``"rows128"`` (weights ``[tiles, kblocks, 4, 128, 16]``, one
+    16-byte chunk of 32 K per channel, for the tcgen05 decode kernel whose threads each own a
+    channel) or ``"lanes"`` (weights ``[tiles, kblocks, 4, 2, 32, 32]``, params
+    ``[tiles, kblocks, 128/group, 4, 8, 4, 2]``, for the cluster split-K decode kernel).
     """
 
     weights: torch.Tensor      # uint8 [tiles, kblocks, 16, 32, 16]
@@ -122,9 +135,74 @@ def rows_w4(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tens
                    integer_zero_points=integer)
 
 
+_LANE_SLOT_ORDER = (0, 2, 1, 3)
+
+
+def lanes_w4(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Tensor | None, *,
+             group_size: int, nibble_signed: bool, k: int | None = None) -> TiledW4:
+    """canonical tensors -> ``b200_w4_lanes_v1`` (see module docstring); pure index shuffling."""
+
+    if qweight.ndim != 2 or qweight.dtype != torch.uint8:
+        raise XQTBackendError("lanes_w4 expects canonical uint8 [N, K/2] storage")
+    n, padded_k = int(qweight.shape[0]), int(qweight.shape[1]) * 2
+    k = padded_k if k is None else int(k)
+    if k != padded_k or k % KBLOCK != 0:
+        raise XQTBackendError("the B200 decode layout needs K == padded_K and K a multiple of 128")
+    if group_size not in (64, 128):
+        raise XQTBackendError("the lanes layout serves group_size 64 or 128")
+    groups = k // group_size
+    if tuple(scales.shape) != (n, groups):
+        raise XQTBackendError(f"scales must be [{n},{groups}]")
+    tiles, kblocks, per_block = -(-n // TILE_ROWS), k // KBLOCK, KBLOCK // group_size
+    rows = tiles * TILE_ROWS
+    codes = torch.stack((qweight & 0x0F, qweight >> 4), dim=-1).reshape(n, k)
+    if nibble_signed:
+        codes = codes ^ 8
+    if rows != n:
+        codes = torch.nn.functional.pad(codes, (0, 0, 0, rows - n))
+    # channel = 32w + 16t + 8h + r; k = 128kb + 32q + 8c + 4jj + slot
+    c = codes.reshape(tiles, 4, 2, 2, 8, kblocks, 4, 4, 2, 4)      # [T, w, t, h, r, kb, q, c, jj, slot]
+    c = c.permute(0, 5, 1, 2, 4, 7, 6, 8, 9, 3)                     # [T, kb, w, t, r, c, q, jj, slot, h]
+    c = c[..., list(_LANE_SLOT_ORDER), :]
+    nib = c.reshape(tiles, kblocks, 4, 2, 32, 8, 8)                 # [.., lane, word j, nibble p = 2*slot' + h]
+    weights = (nib[..., 0::2] | (nib[..., 1::2] << 4)).reshape(tiles, kblocks, 4, 2, 32, 32).contiguous()
+
+    def laned(param: torch.Tensor) -> torch.Tensor:
+        q = param
+        if rows != n:
+            q = torch.nn.functional.pad(q, (0, 0, 0, rows - n))
+        q = q.reshape(tiles, 4, 2, 2, 8, kblocks, per_block)       # [T, w, t, h, r, kb, sub]
+        return q.permute(0, 5, 6, 1, 4, 2, 3).reshape(tiles, kblocks, per_block, 4, 8, 4)
+
+    zeros = torch.zeros_like(scales) if zero_points is None else zero_points.to(scales.dtype)
+    params = torch.stack((laned(scales), laned(zeros)), dim=-1).contiguous()
+    return TiledW4(weights=weights, params=params, n=n, k=k, group_size=int(group_size),
+                   nibble_signed=bool(nibble_signed), has_zero_point=zero_points is not None, layout="lanes")
+
+
+def _unlane_w4(tiled: TiledW4) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
+    tiles, kblocks, per_block = tiled.tiles, tiled.k // KBLOCK, KBLOCK // tiled.group_size
+    w = tiled.weights.reshape(tiles, kblocks, 4, 2, 32, 8, 4)
+    nib = torch.stack((w & 0x0F, w >> 4), dim=-1).reshape(tiles, kblocks, 4, 2, 8, 4, 4, 2, 4, 2)
+    #                                                      [T, kb, w, t, r, c, q, jj, slot', h]
+    inverse = [list(_LANE_SLOT_ORDER).index(e) for e in range(4)]
+    nib = nib[..., inverse, :]
+    codes = nib.permute(0, 2, 3, 9, 4, 1, 6, 5, 7, 8).reshape(tiles * TILE_ROWS, tiled.k)[: tiled.n]
+    if tiled.nibble_signed:
+        codes = codes ^ 8
+    qweight = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
+    p = tiled.params.reshape(tiles, kblocks, per_block, 4, 8, 2, 2, 2)       # [T, kb, sub, w, r, t, h, 2]
+    p = p.permute(0, 3, 5, 6, 4, 1, 2, 7).reshape(tiles * TILE_ROWS, -1, 2)[: tiled.n]
+    scales = p[..., 0].contiguous()
+    zeros = p[..., 1].contiguous() if tiled.has_zero_point else None
+    return qweight, scales, zeros
+
+
 def untile_w4(tiled: TiledW4) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
     """Inverse of :func:`tile_w4` (used by the round-trip test and by checkpoint export)."""
 
+    if tiled.layout == "lanes":
+        return _unlane_w4(tiled)
     tiles, kblocks = tiled.tiles, tiled.k // KBLOCK
     weights = tiled.weights
     if tiled.layout == "rows128":
@@ -141,4 +219,4 @@ def untile_w4(tiled: TiledW4) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor 
     return qweight, scales, zeros
 
 
-__all__ = ["KBLOCK", "TILE_ROWS", "TiledW4", "rows_w4", "tile_w4", "untile_w4"]
+__all__ = ["KBLOCK", "TILE_ROWS", "TiledW4", "lanes_w4", "rows_w4", "tile_w4", "untile_w4"]
