@@ -25,6 +25,20 @@ namespace xqt_b200 {
 
 inline int launch_status() { return (int)cudaGetLastError(); }
 
+// Opt a kernel in to more than 48 KiB of dynamic shared memory.  The attribute belongs to the
+// (function, device) pair, so it is set once per device the process launches on, with that device
+// current.
+#define XQT_SMEM_OPT_IN(kern, bytes)                                                                    \
+  do {                                                                                                  \
+    static bool configured__[64] = {};                                                                  \
+    int dev__ = 0;                                                                                      \
+    XQT_CUDA(cudaGetDevice(&dev__));                                                                    \
+    if (dev__ < 0 || dev__ >= 64 || !configured__[dev__]) {                                             \
+      XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes)));  \
+      if (dev__ >= 0 && dev__ < 64) configured__[dev__] = true;                                         \
+    }                                                                                                   \
+  } while (0)
+
 __host__ __device__ constexpr int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 template <typename T>

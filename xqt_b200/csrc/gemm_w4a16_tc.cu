@@ -12,8 +12,9 @@
 // relative error of at most 2^-12 per weight, i.e. ~1e-4 rel-L2 on the output, against the 1e-3
 // bar; rounding the weights to bf16 (8-bit significand) instead would cost ~8e-4.  Both MMA
 // operands are therefore fp16: bf16 activations are first converted to fp16 by a small
-// element-wise kernel into the caller's scratch buffer (exact inside the fp16 range, saturating at
-// +-65504 outside it), once per call rather than once per weight tile.
+// element-wise kernel into the caller's scratch buffer, once per call rather than once per weight
+// tile: exact for 2^-14 <= |x| <= 65504 (smaller values lose bits to fp16's subnormals), NaN kept,
+// anything larger clamped to +-65504 with bit 256 set in the status word.
 // Envelope: group size 64 or 128, K a multiple of 64, integer zero points; anything else is served
 // by the generic CUDA-core kernel.  Reference arithmetic: xqt/kernels/ops/gemm/reference.py:263-271,527.
 #include <cstdlib>
@@ -312,22 +313,29 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tm_a, const W4GemmParams p
 
 // ----------------------------------------------------------------------------------------- host
 
-// bf16 -> fp16, saturating; 8 elements per thread
-__global__ void __launch_bounds__(256) bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ src, __half* __restrict__ dst, size_t n8) {
+// bf16 -> fp16, 8 elements per thread.  NaN stays NaN.  A finite value (or infinity) beyond fp16's
+// range is clamped to +-65504 and reported: the kernel ORs kActivationRange into the status word, so
+// a caller that reads the status learns that the result is not the reference's.
+constexpr unsigned int kActivationRange = 256;
+__global__ void __launch_bounds__(256) bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ src, __half* __restrict__ dst, size_t n8,
+                                                          unsigned int* __restrict__ status) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
   const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
   const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
   uint4 o;
   __half2* out = reinterpret_cast<__half2*>(&o);
+  bool clipped = false;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     float2 f = __bfloat1622float2(in[j]);
-    f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
-    f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
+    clipped |= fabsf(f.x) > 65504.f || fabsf(f.y) > 65504.f;          // false for NaN
+    f.x = f.x != f.x ? f.x : fminf(fmaxf(f.x, -65504.f), 65504.f);
+    f.y = f.y != f.y ? f.y : fminf(fmaxf(f.y, -65504.f), 65504.f);
     out[j] = __floats2half2_rn(f.x, f.y);
   }
   reinterpret_cast<uint4*>(dst)[i] = o;
+  if (clipped) atomicOr(status, kActivationRange);
 }
 
 // Canonical int4 weights -> fp16 [N, K] row-major, value = fp16((code - zero) * scale) computed in
@@ -409,11 +417,7 @@ static int launch_w4gemm(const void* x, const void* qw, W4GemmParams p, cudaStre
   p.kblocks = p.k / kBK;
   const size_t smem_bytes = (size_t)p.stages * stage_bytes + 1024;
   auto kern = gemm_w4a16_kernel<BN, T>;
-  static bool configured = false;
-  if (!configured) {
-    XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
-    configured = true;
-  }
+  XQT_SMEM_OPT_IN(kern, kSmemBudget);
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int grid = sms > 0 ? sms : 148;
@@ -436,7 +440,7 @@ int w4a16_gemm_tc_launch(const void* x, const void* qw, const void* scales, cons
   if (act_dtype == XQT_B200_BF16) {
     __half* x16 = reinterpret_cast<__half*>(scratch);
     const size_t n8 = (size_t)m * k / 8;
-    bf16_to_f16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, x16, n8);
+    bf16_to_f16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, x16, n8, status);
     XQT_CUDA(cudaGetLastError());
     x = x16;
   }

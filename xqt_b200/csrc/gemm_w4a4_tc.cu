@@ -343,11 +343,7 @@ static int launch_w4a4(const void* a_codes, W4A4Params p, cudaStream_t stream) {
   p.kstages = p.k / kStageK;
   const size_t smem_bytes = (size_t)p.stages * kStageBytes + (size_t)nab * aux_bytes + 1024;
   auto kern = gemm_w4a4_kernel<OutT>;
-  static bool configured = false;
-  if (!configured) {
-    XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
-    configured = true;
-  }
+  XQT_SMEM_OPT_IN(kern, kSmemBudget);
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int grid = sms > 0 ? sms : 148;

@@ -302,11 +302,7 @@ int rotate_quant_launch(const void* x, const float* column_scale, void* codes, f
 #define XQT_RQ(TT)                                                                                               \
   do {                                                                                                           \
     auto kern = rotate_quant_kernel<TT>;                                                                         \
-    static bool configured = false;                                                                              \
-    if (!configured) {                                                                                           \
-      XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));             \
-      configured = true;                                                                                         \
-    }                                                                                                            \
+    XQT_SMEM_OPT_IN(kern, 200 * 1024);                                                                           \
     kern<<<m, kRqThreads, smem, stream>>>((const TT*)x, column_scale, (int8_t*)codes, scales, (TT*)x_rot, k,     \
                                           rot_kind, rot_block, mode, group);                                     \
   } while (0)

@@ -394,11 +394,7 @@ static int decode_launch_gp(const DecodeParams& p, int gp, int grid, size_t smem
 #define XQT_DEC_LAUNCH(GPV)                                                                              \
   do {                                                                                                   \
     auto kern = w4a16_decode_kernel<T, P, SIGNED, HAS_ZP, GPV>;                                          \
-    static bool configured = false;                                                                      \
-    if (!configured) {                                                                                   \
-      XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decode::kSmemBudget)); \
-      configured = true;                                                                                 \
-    }                                                                                                    \
+    XQT_SMEM_OPT_IN(kern, decode::kSmemBudget);                                                          \
     kern<<<grid, decode::kThreads, smem_bytes, stream>>>(p);                                             \
   } while (0)
   if (gp == 1) XQT_DEC_LAUNCH(1);

@@ -445,21 +445,27 @@ bool cl_plan_override(ClPlan& plan) {
   return true;
 }
 
-// How many K pieces a tile is cut into: enough warps (4 per piece and tile) to keep about 16
-// resident per SM, at least two 128-K blocks per piece.
+// How many K pieces a tile is cut into.  Measured on B200: the launch must fit one wave (16 warps
+// per SM at 128 registers), power-of-two clusters place better than odd ones, and 8-warp CTAs (two K
+// pieces per CTA, two CTAs per SM) beat both smaller and larger ones.  So: the largest power of two
+// P with tiles * 4 * P warps inside one wave and at least two 128-K blocks per piece, cut as
+// 2 x P/2 (1 x 1 when P is 1, 4 x 8 when P is 32).
 ClPlan cl_plan(int tiles, int kblocks, int m) {
   using namespace dcl;
   ClPlan plan;
   const int max_slice = m > 8 ? kMaxSliceBlocks16 : kMaxSliceBlocks8;
   if (!cl_plan_override(plan)) {
-    const int sms = cl_sm_count();
-    int want = (sms * 16 + tiles * 2) / (tiles * 4);
-    const int cap = kblocks >= 2 ? kblocks / 2 : 1;
-    if (want > cap) want = cap;
-    if (want > kMaxKW * kMaxCluster) want = kMaxKW * kMaxCluster;
-    if (want < 1) want = 1;
-    plan.kw = want <= kMaxCluster ? 1 : (want <= 2 * kMaxCluster ? 2 : 4);
-    plan.s = (want + plan.kw - 1) / plan.kw;
+    const int wave_warps = cl_sm_count() * 16;
+    int pieces = 1;
+    while (pieces < kMaxKW * kMaxCluster && (long long)tiles * 4 * (pieces * 2) <= wave_warps && pieces * 2 * 2 <= kblocks)
+      pieces *= 2;
+    plan.kw = pieces == 1 ? 1 : (pieces > 2 * kMaxCluster ? 4 : 2);
+    plan.s = pieces / plan.kw;
+    // a CTA's K slice (kblocks / s) must fit its shared memory: trade warp quads for CTAs
+    while ((kblocks + plan.s - 1) / plan.s + 1 > max_slice + 1 && plan.s < kMaxCluster) {
+      plan.s *= 2;
+      if (plan.kw > 1) plan.kw /= 2;
+    }
   }
   if (plan.kw < 1) plan.kw = 1;
   if (plan.kw > kMaxKW) plan.kw = kMaxKW;
@@ -468,8 +474,7 @@ ClPlan cl_plan(int tiles, int kblocks, int m) {
   if (plan.s > kMaxCluster) plan.s = kMaxCluster;
   while (plan.kw * plan.s > kblocks && plan.kw > 1) plan.kw >>= 1;
   while (plan.kw * plan.s > kblocks && plan.s > 1) --plan.s;
-  // a CTA's K slice must fit its shared memory: more CTAs per tile if it does not
-  while (plan.s < kMaxCluster && (kblocks + plan.s - 1) / plan.s + 1 > max_slice) ++plan.s;
+  while ((kblocks + plan.s - 1) / plan.s + 1 > max_slice + 1 && plan.s < kMaxCluster) ++plan.s;
   return plan;
 }
 
@@ -491,19 +496,13 @@ bool w4a16_decode_cl_supported(int m, int n, int k, int group_size) {
   if (!(m >= 1 && m <= 16 && n >= 1 && k >= kKB && k % kKB == 0 && (group_size == 64 || group_size == 128))) return false;
   const int max_slice = m > 8 ? kMaxSliceBlocks16 : kMaxSliceBlocks8;
   const int kblocks = k / kKB;
-  return (kblocks + kMaxCluster - 1) / kMaxCluster + 1 <= max_slice;
+  return (kblocks + kMaxCluster - 1) / kMaxCluster + 1 <= max_slice + 1;
 }
 
 template <typename T, typename P, int GK, int NT>
 static int dcl_launch(const DecodeClParams& p, int grid, int threads, int cluster, size_t smem_bytes, cudaStream_t stream) {
   auto kern = w4a16_decode_cl_kernel<T, P, GK, NT>;
-  static bool configured[64] = {};
-  int dev = 0;
-  XQT_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  XQT_SMEM_OPT_IN(kern, 200 * 1024);
   static int pdl = -1;
   if (pdl < 0) {
     const char* v = getenv("XQT_B200_PDL");

@@ -28,7 +28,7 @@
 // kernel (activations, scratch, outputs) only after griddepcontrol.wait.
 // The dequantised weight is an exact small integer, the scale is applied in fp32 to the fp32 group
 // sum, so the result equals the contract reference (xqt/kernels/ops/gemm/reference.py:263-271,527)
-// up to fp32 summation order.  Zero points must be integers in [0, 127] (true of every RTN / AWQ
+// up to fp32 summation order.  Zero points must be integers in [0, 119] (true of every RTN / AWQ
 // checkpoint); other weights are served by the mma.sync decode kernel.
 // Stream-K partition, partial-sum scratch, ticket-elected finisher and bounded waits are those of
 // w4a16_decode.cu.
@@ -40,31 +40,6 @@
 namespace xqt_b200 {
 
 using namespace sm100;
-
-#ifdef XQT_TRACE
-// instrumented build only: nanosecond timestamps of CTA 0 into the 256-byte status block
-#define XQT_TRACE_AT(slot)                                                                   \
-  do {                                                                                       \
-    if (blockIdx.x == 0) {                                                                   \
-      unsigned long long t__;                                                                \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                \
-      reinterpret_cast<unsigned long long*>(p.status)[(slot)] = t__;                         \
-    }                                                                                        \
-  } while (0)
-// per-iteration SM cycle stamps of CTA 0: trace[role][iteration < 24][point < 8], kept in the unused
-// tail of the partial-sum scratch (slots of CTAs >= 160)
-#define XQT_TRACE_CLK(role, iter, point)                                                     \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && (iter) < 24u) {                                                   \
-      long long c__;                                                                         \
-      asm volatile("mov.u64 %0, %%clock64;" : "=l"(c__)::"memory");                          \
-      reinterpret_cast<long long*>(p.partials + (size_t)160 * 2 * 2048)[((role) * 24 + (iter)) * 8 + (point)] = c__; \
-    }                                                                                        \
-  } while (0)
-#else
-#define XQT_TRACE_AT(slot) do { } while (0)
-#define XQT_TRACE_CLK(role, iter, point) do { } while (0)
-#endif
 
 namespace dtc {
 constexpr int kTileRows = 128;
@@ -217,7 +192,6 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
   const bool small = p.total * (long long)(grid + 1) < 0x7fffffffLL;
   const long long s_begin = div_nn((long long)cta * p.total, grid, small), s_end = div_nn((long long)(cta + 1) * p.total, grid, small);
   const int ns = p.nstages;
-  if (tid == 0) XQT_TRACE_AT(1);
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   float* red = reinterpret_cast<float*>(stages + (size_t)ns * p.stage_bytes);   // [kWG-1][16][128] fp32
   auto full_bar = [&](int s) { return smem_addr(&bars[s]); };
@@ -270,7 +244,6 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
     pr_ks = (int)(s_begin - pr_tile * p.spt);
     if (s_begin < s_end) {   // the first weights go out before the CTA-wide barrier, the rest right after it
       issue_weights();
-      XQT_TRACE_AT(3);
     }
   }
   if (warp == kFirstMmaWarp) {
@@ -281,7 +254,6 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
-  if (tid == 0) XQT_TRACE_AT(2);
   // Programmatic dependent launch: the next kernel of the stream may start its own set-up and
   // weight prefetch as soon as every CTA here has passed this point; everything of this kernel
   // that reads or writes data of the previous one comes after the dependency wait (the producer
@@ -324,12 +296,10 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
       }
       for (; s < s_end; ++s, ++pr_it) {
         guarded_wait(empty_bar(pr_slot), pr_phase ^ 1);
-        XQT_TRACE_CLK(3, pr_it, 0);
         issue_weights();
         issue_acts(pr_slot, pr_ks);
         advance();
       }
-      XQT_TRACE_AT(4);
     }
   } else if (warp >= kFirstMmaWarp) {
     // ------------------------------------------------------------------ MMA issuers
@@ -344,8 +314,6 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
         const int buf = it & (kNB - 1);
         const uint32_t bphase = (it / kNB) & 1;
         guarded_wait2(aready_bar(wg0, buf), bphase, aready_bar(wg0 + 1, buf), bphase);
-        if (warp == kFirstMmaWarp) XQT_TRACE_CLK(2, it, 0);
-        if (it == 0) XQT_TRACE_AT(5);
         tc_fence_after();
         // The instruction rate, not the arithmetic, bounds these M=128 x N=16 x K=16 steps (each
         // moves 4 KiB of A operand); the two units are interleaved only to keep the order fixed.
@@ -358,12 +326,9 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
             umma_ts_f16(tmem_base + d_col(wg, buf), tmem_base + a_col(wg, buf) + kk * 8, bdesc, kIdesc, kk != 0 ? 1u : 0u);
           }
         }
-        if (warp == kFirstMmaWarp) XQT_TRACE_CLK(2, it, 1);
         umma_commit(dready_bar(wg0, buf));
         umma_commit(empty_bar(slot));   // this issuer's reads of the stage (activations) are done; the weights
                                         // were consumed by the threads before they signalled the units ready
-        if (warp == kFirstMmaWarp) XQT_TRACE_CLK(2, it, 2);
-        if (it == 0) XQT_TRACE_AT(6);
         if (++slot == ns) slot = 0;
       }
     }
@@ -425,14 +390,11 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
       // Lane 0 polls for its warp (512 threads polling the same barriers queue up behind one another),
       // the warp barrier hands the observation to the other lanes.
       const bool due = iw - drained >= (uint32_t)kNB;
-      if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 5);
       if (lane == 0) {
         if (due) guarded_wait2(full_bar(slot), phase, dready_bar(wg, drained & (kNB - 1)), (drained / kNB) & 1);
         else guarded_wait(full_bar(slot), phase);
       }
-      if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 6);
       __syncwarp();
-      if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 0);
       if (++slot == ns) { slot = 0; phase ^= 1; }
 #pragma unroll
       for (int uu = 0; uu < kUnitsPerWg; ++uu) {
@@ -458,18 +420,13 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
           for (int i = 0; i < 4; ++i) cols[w * 4 + i] = dq_col<T>(word, i, off2, magic);
         }
         tmem_st_32x32(tmem_base + lane_addr + a_col(wg, buf), cols);
-        if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 1);
         tmem_wait_st();
-        if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 3);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(aready_bar(wg, buf));
-        if ((tid & 127) == 0 && wg < 2) XQT_TRACE_CLK(wg, it, 4);
         if (buf == 0) s_even = sc; else s_odd = sc;
         ++iw;
       }
-      if (tid == 0 && it == 0) XQT_TRACE_AT(7);
-      if (tid == 0 && s == s_end - 1) XQT_TRACE_AT(8);
       const bool tile_end = (ks == p.spt - 1);
       const long long cur_tile = tile;
       if (++ks == p.spt) { ks = 0; ++tile; }
@@ -477,7 +434,6 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
 
       // ---------------------------------------------------------------- end of this CTA's run in `tile`
       while (drained < iw) drain(false);
-      if (tid == 0 && s == s_end - 1) XQT_TRACE_AT(9);
       // combine the warpgroups' sums (fixed order)
       if (wg != 0) {
 #pragma unroll
@@ -572,11 +528,9 @@ w4a16_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const DecodeTcP
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
     }
   }
-  if (tid == 0) XQT_TRACE_AT(10);
   tc_fence_before();
   __syncthreads();
   if (warp == kFirstMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
-  if (tid == 0) XQT_TRACE_AT(11);
 }
 
 // --------------------------------------------------------------------------------------- host side
@@ -643,13 +597,7 @@ static int dtc_launch(const CUtensorMap& tm, const DecodeTcParams& p, int group_
 #define XQT_DTC(SG, GKV)                                                                                     \
   do {                                                                                                       \
     auto kern = w4a16_decode_tc_kernel<T, P, SG, GKV>;                                                       \
-    static bool configured[64] = {};                                                                         \
-    int dev = 0;                                                                                             \
-    XQT_CUDA(cudaGetDevice(&dev));                                                                           \
-    if (dev < 0 || dev >= 64 || !configured[dev]) {                                                          \
-      XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dtc::kSmemBudget));   \
-      if (dev >= 0 && dev < 64) configured[dev] = true;                                                      \
-    }                                                                                                        \
+    XQT_SMEM_OPT_IN(kern, dtc::kSmemBudget);                                                                 \
     cudaLaunchConfig_t cfg = {};                                                                             \
     cfg.gridDim = dim3((unsigned)grid);                                                                      \
     cfg.blockDim = dim3(dtc::kThreads);                                                                      \

@@ -312,11 +312,7 @@ static int gemv_dispatch_kw(const GemvPlan& p, const void* x, const void* qw, co
 #define XQT_GEMV_LAUNCH(KWV)                                                                              \
   do {                                                                                                    \
     auto kern = w4a16_gemv_kernel<T, SIGNED, HAS_ZP, KWV>;                                                \
-    static bool configured = false; /* opt in once to the largest dynamic shared memory any plan uses */  \
-    if (!configured) {                                                                                    \
-      XQT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));       \
-      configured = true;                                                                                  \
-    }                                                                                                     \
+    XQT_SMEM_OPT_IN(kern, 96 * 1024); /* the largest dynamic shared memory any plan uses */               \
     kern<<<grid, block, p.smem, stream>>>((const T*)x, (const uint8_t*)qw, scales, zeros, bias,           \
                                           (const T*)residual, (T*)out, m, n, k, param_dtype, p.kc,        \
                                           p.splits, partials, tickets);                                   \

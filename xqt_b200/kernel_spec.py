@@ -69,15 +69,17 @@ class CapabilityRequirement:
         return cls(DeviceType.CUDA, min_sm, max_sm)
 
     def is_satisfied_by(self, platform: PlatformInfo) -> bool:
-        if self.device != platform.device:
+        """Same device kind, and -- for CUDA with a known compute capability -- inside the
+        inclusive ``[min_cuda_arch, max_cuda_arch]`` window (an open end is unbounded)."""
+
+        if platform.device != self.device:
             return False
-        if self.device == DeviceType.CUDA and platform.cuda_arch_major is not None:
-            arch = (platform.cuda_arch_major, platform.cuda_arch_minor or 0)
-            if self.min_cuda_arch is not None and arch < self.min_cuda_arch:
-                return False
-            if self.max_cuda_arch is not None and arch > self.max_cuda_arch:
-                return False
-        return True
+        if self.device != DeviceType.CUDA or platform.cuda_arch_major is None:
+            return True
+        have = (platform.cuda_arch_major, platform.cuda_arch_minor or 0)
+        low = self.min_cuda_arch if self.min_cuda_arch is not None else have
+        high = self.max_cuda_arch if self.max_cuda_arch is not None else have
+        return low <= have <= high
 
 
 @dataclass(frozen=True, slots=True)

@@ -13,17 +13,26 @@ registry.py:845-977,1200-1383).  ``default_registry()`` holds the B200 rows as `
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, fields
 from typing import Any, Callable, Iterable
 
 from .contracts import EpilogueSpec, GemmProblem, QuantSpec
 
 MATURITIES = frozenset({"executable", "metadata_only", "planned", "reference_guarded", "experimental"})
+SCOPES = frozenset({"contract", "precision"})
 GemmExecutor = Callable[..., Any]
+
+
+def _admits(allowed: tuple[str, ...], value: str, *, wildcard: bool = True) -> bool:
+    """``value`` is listed, or the list holds the wildcard ``"any"`` (where one is honoured)."""
+
+    return value in allowed or (wildcard and "any" in allowed)
 
 
 @dataclass(frozen=True, slots=True)
 class GemmCapability:
+    """What a row can serve.  Field names and defaults are the schema xqt's dispatcher and reports read."""
+
     architectures: tuple[str, ...] = ("any",)
     weight_dtypes: tuple[str, ...] = ("fp32",)
     activation_dtypes: tuple[str, ...] = ("fp32",)
@@ -33,36 +42,31 @@ class GemmCapability:
     min_sm: int | None = None
 
     def supports(self, problem: GemmProblem, quant: QuantSpec, epilogue: EpilogueSpec) -> bool:
-        if "any" not in self.architectures and problem.arch not in self.architectures:
+        # dtypes are exact matches; architecture, scale mode, phase and epilogue accept "any"
+        listed = (
+            _admits(self.architectures, problem.arch),
+            _admits(self.weight_dtypes, quant.weight_dtype, wildcard=False),
+            _admits(self.activation_dtypes, quant.activation_dtype, wildcard=False),
+            _admits(self.scale_modes, quant.scale_mode),
+            _admits(self.phases, problem.phase),
+            _admits(self.epilogues, epilogue.activation),
+        )
+        if not all(listed):
             return False
-        if quant.weight_dtype not in self.weight_dtypes:
-            return False
-        if quant.activation_dtype not in self.activation_dtypes:
-            return False
-        if quant.scale_mode not in self.scale_modes and "any" not in self.scale_modes:
-            return False
-        if problem.phase not in self.phases and "any" not in self.phases:
-            return False
-        if epilogue.activation not in self.epilogues and "any" not in self.epilogues:
-            return False
-        if self.min_sm is not None and (problem.sm is None or problem.sm < self.min_sm):
-            return False
-        return True
+        return self.min_sm is None or (problem.sm is not None and problem.sm >= self.min_sm)
 
     def to_dict(self) -> dict[str, Any]:
-        return {
-            "architectures": list(self.architectures),
-            "weight_dtypes": list(self.weight_dtypes),
-            "activation_dtypes": list(self.activation_dtypes),
-            "scale_modes": list(self.scale_modes),
-            "phases": list(self.phases),
-            "epilogues": list(self.epilogues),
-            "min_sm": self.min_sm,
-        }
+        out: dict[str, Any] = {}
+        for item in fields(self):
+            value = getattr(self, item.name)
+            out[item.name] = list(value) if isinstance(value, tuple) else value
+        return out
 
 
 @dataclass(frozen=True, slots=True)
 class GemmKernelRegistration:
+    """One row of the table: identity, capability, tuning metadata and (when executable) the callable."""
+
     name: str
     backend: str
     maturity: str
@@ -80,84 +84,80 @@ class GemmKernelRegistration:
     executor: GemmExecutor | None = field(default=None, compare=False, repr=False)
 
     def __post_init__(self) -> None:
+        problems = []
         if not self.name.strip():
-            raise ValueError("GemmKernelRegistration.name must be non-empty")
+            problems.append("name is empty")
         if self.maturity not in MATURITIES:
-            raise ValueError(f"unsupported GEMM maturity: {self.maturity!r}")
+            problems.append(f"maturity {self.maturity!r} is not one of {sorted(MATURITIES)}")
+        if self.scope not in SCOPES:
+            problems.append(f"scope {self.scope!r} is not one of {sorted(SCOPES)}")
         if self.priority < 0:
-            raise ValueError("kernel priority must be non-negative")
-        if any(int(item) <= 0 for item in self.alignment):
-            raise ValueError("kernel alignment values must be positive")
-        if self.tile_shape is not None and any(int(item) <= 0 for item in self.tile_shape):
-            raise ValueError("tile_shape values must be positive")
+            problems.append("priority is negative")
+        for label, values in (("alignment", self.alignment), ("tile_shape", self.tile_shape or ())):
+            if any(int(v) <= 0 for v in values):
+                problems.append(f"{label} holds a non-positive entry")
         if self.maturity == "executable" and self.executor is None:
-            raise ValueError("executable GEMM registration requires an executor")
-        if self.scope not in {"contract", "precision"}:
-            raise ValueError("GEMM registration scope must be contract or precision")
+            problems.append("an executable row needs an executor")
+        if problems:
+            raise ValueError(f"GEMM registration {self.name!r}: " + "; ".join(problems))
 
     @property
     def executable(self) -> bool:
-        return self.maturity == "executable" and self.executor is not None
+        return self.executor is not None and self.maturity == "executable"
 
     def supports(self, problem: GemmProblem, quant: QuantSpec, epilogue: EpilogueSpec) -> bool:
         return self.capability.supports(problem, quant, epilogue)
 
     def to_dict(self) -> dict[str, Any]:
-        return {
-            "name": self.name,
-            "backend": self.backend,
-            "maturity": self.maturity,
-            "kernel_family": self.kernel_family,
-            "layout": self.layout,
-            "tile_shape": None if self.tile_shape is None else list(self.tile_shape),
-            "warp_count": self.warp_count,
-            "stage_count": self.stage_count,
-            "alignment": list(self.alignment),
-            "priority": self.priority,
-            "implementation": self.implementation,
-            "scope": self.scope,
-            "executable": self.executable,
-            "capability": self.capability.to_dict(),
-        }
+        out: dict[str, Any] = {}
+        for item in fields(self):
+            if item.name in ("executor", "capability", "selection_reason"):
+                continue
+            value = getattr(self, item.name)
+            out[item.name] = list(value) if isinstance(value, tuple) else value
+        out["executable"] = self.executable
+        out["capability"] = self.capability.to_dict()
+        return out
 
 
 class GemmKernelRegistry:
+    """Rows by name, in insertion order.  ``register`` refuses a second, different row of the same
+    name (ValueError; the identical row is a no-op), ``replace`` swaps an existing row (KeyError if
+    there is none), ``matching`` lists the contract-scope rows that support a request, best priority first."""
+
     def __init__(self, entries: Iterable[GemmKernelRegistration] = ()) -> None:
-        self._entries: dict[str, GemmKernelRegistration] = {}
-        for entry in entries:
-            self.register(entry)
+        self._rows: dict[str, GemmKernelRegistration] = {}
+        for row in entries:
+            self.register(row)
 
     def register(self, entry: GemmKernelRegistration) -> None:
-        existing = self._entries.get(entry.name)
-        if existing is not None:
-            if existing == entry:
-                return
+        present = self._rows.setdefault(entry.name, entry)
+        if present is not entry and present != entry:
             raise ValueError(
-                f"Conflicting GEMM kernel registration for {entry.name!r}: "
-                f"existing backend={existing.backend!r}, incoming backend={entry.backend!r}"
-            )
-        self._entries[entry.name] = entry
+                f"GEMM kernel {entry.name!r} is already registered with a different definition "
+                f"(backend {present.backend!r}; the incoming row has backend {entry.backend!r})")
 
     def replace(self, entry: GemmKernelRegistration) -> None:
-        if entry.name not in self._entries:
-            raise KeyError(f"cannot replace unknown GEMM kernel registration: {entry.name!r}")
-        self._entries[entry.name] = entry
+        self.get(entry.name)                     # KeyError when the row does not exist
+        self._rows[entry.name] = entry
 
     def get(self, name: str) -> GemmKernelRegistration:
-        try:
-            return self._entries[name]
-        except KeyError as exc:
-            raise KeyError(f"unknown GEMM kernel registration: {name!r}") from exc
+        row = self._rows.get(name)
+        if row is None:
+            raise KeyError(f"no GEMM kernel registration named {name!r}")
+        return row
 
     def entries(self) -> tuple[GemmKernelRegistration, ...]:
-        return tuple(self._entries.values())
+        return tuple(self._rows.values())
 
     def matching(self, problem, quant, epilogue) -> tuple[GemmKernelRegistration, ...]:
-        found = [e for e in self._entries.values() if e.scope == "contract" and e.supports(problem, quant, epilogue)]
-        return tuple(sorted(found, key=lambda e: e.priority, reverse=True))
+        rows = (row for row in self._rows.values() if row.scope == "contract")
+        able = [row for row in rows if row.supports(problem, quant, epilogue)]
+        able.sort(key=lambda row: -row.priority)          # stable: insertion order breaks ties
+        return tuple(able)
 
     def to_dict(self) -> list[dict[str, Any]]:
-        return [entry.to_dict() for entry in self.entries()]
+        return [row.to_dict() for row in self._rows.values()]
 
 
 # ------------------------------------------------------------------------------- B200 rows
