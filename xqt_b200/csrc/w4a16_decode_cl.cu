@@ -63,9 +63,11 @@ struct DecodeClParams {
   unsigned int* status; // may be null
   int m, n, k, out_f32;
   int kblocks, pieces, kw;
+  int per, rem;         // kblocks = pieces * per + rem: piece i starts at i * per + min(i, rem)
   int xrow_bytes;       // shared-memory row stride of x
   int off_xsum, off_redl, off_redc;   // byte offsets inside dynamic shared memory
   int own_max;          // tokens a CTA can own: ceil(8*NT / S)
+  int prefetch;         // 1: request each warp's whole piece into L2 at kernel start
   float base_off;       // B (+ 8 when the stored nibbles were two's complement)
 };
 
@@ -151,7 +153,8 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t smem_s = smem_addr(smem);
   const uint32_t xbar = smem_s;                       // mbarrier of the activation copy
-  const uint32_t xs_s = smem_s + 128;                 // x rows
+  const uint32_t zero_s = smem_s + 128;               // 256 bytes of zeros: the activation row of tokens >= M
+  const uint32_t xs_s = smem_s + 384;                 // x rows 0..M-1
   const uint32_t xsum_s = smem_s + p.off_xsum;        // [slice blocks][SUB][16] fp32
   const uint32_t redl_s = smem_s + p.off_redl;        // [KW-1][MP][kRedStride] fp32
   const uint32_t redc_s = smem_s + p.off_redc;        // [S][own_max][kRedStride] fp32
@@ -161,12 +164,12 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   const int r = lane >> 2, c = lane & 3;
   const int nthreads = blockDim.x;
   const uint32_t S = cluster_nctarank(), rank = cluster_ctarank();
-  const int tile = blockIdx.x / S;
+  const int tile = (int)cluster_id_x();
 
-  const int kb0 = (int)((rank * p.kw + kwi) * p.kblocks / p.pieces);
-  const int kb1 = (int)((rank * p.kw + kwi + 1) * p.kblocks / p.pieces);
-  const int cta_kb0 = (int)(rank * p.kw * p.kblocks / p.pieces);
-  const int cta_kb1 = (int)((rank + 1) * p.kw * p.kblocks / p.pieces);
+  auto piece_start = [&](int piece) { return piece * p.per + min(piece, p.rem); };
+  const int piece = (int)rank * p.kw + kwi;
+  const int kb0 = piece_start(piece), kb1 = piece_start(piece + 1);
+  const int cta_kb0 = piece_start((int)rank * p.kw), cta_kb1 = piece_start(((int)rank + 1) * p.kw);
   const int nkb = kb1 - kb0;
 
   const uint8_t* wbase = p.wt + ((size_t)tile * p.kblocks * 4 + w) * 2048 + lane * 32;
@@ -176,25 +179,34 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   // register ring: packed weights of two A tiles and the parameters of one 128-K block per slot
   uint32_t wq[3][2][8];
   uint32_t pr[3][SUB][PR];
-  auto load = [&](auto slot_c, int kb) {
+  const uint8_t* wp = wbase + (size_t)kb0 * 8192;            // next block to request
+  const uint8_t* pp = pbase + (size_t)kb0 * kPrmBlockBytes;
+  auto load = [&](auto slot_c) {
     constexpr int slot = decltype(slot_c)::value;
-    const uint8_t* wp = wbase + (size_t)kb * 8192;
     ldg256_stream(wq[slot][0], wp);
     ldg256_stream(wq[slot][1], wp + 1024);
-    const uint8_t* pp = pbase + (size_t)kb * kPrmBlockBytes;
 #pragma unroll
     for (int sub = 0; sub < SUB; ++sub) {
       if constexpr (P32) ldg64_stream(pr[slot][sub], pp + sub * 1024);
       else ldg128_stream(pr[slot][sub], pp + sub * 512);
     }
+    wp += 8192;
+    pp += kPrmBlockBytes;
   };
   using I0 = std::integral_constant<int, 0>;
   using I1 = std::integral_constant<int, 1>;
   using I2 = std::integral_constant<int, 2>;
 
   // the first weights are on their way before anything else happens
-  if (nkb > 0) load(I0{}, kb0);
-  if (nkb > 1) load(I1{}, kb0 + 1);
+  if (nkb > 0) load(I0{});
+  if (nkb > 1) load(I1{});
+  // ... and the rest of this warp's piece is requested into L2 right away (one bulk prefetch per
+  // block and lane: the warp's 2 KiB of a block are contiguous), so that the whole layer is in
+  // flight from HBM from the first microsecond and the register ring only has to cover L2 latency
+  for (int i = 2 + lane; i < nkb && p.prefetch; i += 32) {
+    bulk_prefetch_l2(p.wt + (((size_t)tile * p.kblocks + kb0 + i) * 4 + w) * 2048, 2048);
+    bulk_prefetch_l2(p.prm + ((size_t)tile * p.kblocks + kb0 + i) * kPrmBlockBytes + w * (kPrmBlockBytes / 4), kPrmBlockBytes / 4);
+  }
 
   if (tid == 0) {
     mbar_init(xbar, 1);
@@ -203,17 +215,10 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   if (S > 1) cluster_arrive_relaxed();   // phase 0: "this CTA runs"; waited for before the first remote store
   grid_launch_dependents();
 
-  // rows M..MP-1 of the activation slice are zeros
   const int slice_kb = cta_kb1 - cta_kb0;
   const int slice_bytes = slice_kb * 256;
-  {
-    const int chunks = slice_bytes >> 4;
-    for (int i = tid; i < (MP - p.m) * chunks; i += nthreads) {
-      const int row = p.m + i / chunks, ch = i - (i / chunks) * chunks;
-      cl_sts128z(xs_s + row * p.xrow_bytes + ch * 16);
-    }
-  }
-  __syncthreads();                        // barrier initialised, zero rows written
+  if (tid < 16) cl_sts128z(zero_s + tid * 16);
+  __syncthreads();                        // barrier initialised, zero row written
   grid_dependency_wait();                 // x, residual and out may belong to the kernel before this one
   if (tid == 0) {
     mbar_expect_tx(xbar, (uint32_t)(p.m * slice_bytes));
@@ -233,7 +238,8 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
     for (int i = 0; i < 4; ++i) asm volatile("mov.b32 %0, %1;\n" : "=r"(ones[i]) : "n"(Tr::kOnes));
     for (int item = warp; item < slice_kb * NT; item += nwarps) {
       const int kbl = item / NT, nt = item - kbl * NT;
-      const uint32_t xrow = xs_s + (nt * 8 + r) * p.xrow_bytes + kbl * 256 + c * 16;
+      const int row = nt * 8 + r;
+      const uint32_t xrow = (row < p.m ? xs_s + row * p.xrow_bytes + kbl * 256 : zero_s) + c * 16;
 #pragma unroll
       for (int sub = 0; sub < SUB; ++sub) {
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
@@ -266,10 +272,19 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   asm volatile("mov.b32 %0, %1;\n" : "=r"(magic) : "n"(Tr::kMagic));
   const float base_off = p.base_off;
 
-  auto compute = [&](auto slot_c, int kb) {
+  // this lane's activation row per n-tile (token 8*nt + r) and its advance per block: rows of
+  // tokens >= M all read the zero row and do not advance
+  uint32_t xrow[NT], xstep[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int row = nt * 8 + r;
+    xrow[nt] = (row < p.m ? xs_s + row * p.xrow_bytes + (kb0 - cta_kb0) * 256 : zero_s) + c * 16;
+    xstep[nt] = row < p.m ? 256u : 0u;
+  }
+  uint32_t xsum_a = xsum_s + ((kb0 - cta_kb0) * SUB * 16 + 2 * c) * 4;
+
+  auto compute = [&](auto slot_c) {
     constexpr int slot = decltype(slot_c)::value;
-    const int kbl = kb - cta_kb0;
-    const uint32_t xrow = xs_s + r * p.xrow_bytes + kbl * 256 + c * 16;
 #pragma unroll
     for (int sub = 0; sub < SUB; ++sub) {
       float tmp[2][NT][4];
@@ -285,7 +300,7 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
         const int j = sub * STEPS + jj;
         if ((j & 1) == 0) {
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) cl_lds128(xb[nt], xrow + nt * 8 * p.xrow_bytes + (j >> 1) * 64);
+          for (int nt = 0; nt < NT; ++nt) cl_lds128(xb[nt], xrow[nt] + (j >> 1) * 64);
         }
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
@@ -301,7 +316,7 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
       // y += s * (group sum - (B + z) * sum_k x)
       float2 xs2[NT];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) xs2[nt] = cl_lds64f(xsum_s + (((kbl * SUB + sub) * 16) + nt * 8 + 2 * c) * 4);
+      for (int nt = 0; nt < NT; ++nt) xs2[nt] = cl_lds64f(xsum_a + (sub * 16 + nt * 8) * 4);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
 #pragma unroll
@@ -323,21 +338,24 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
         }
       }
     }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) xrow[nt] += xstep[nt];
+    xsum_a += SUB * 16 * 4;
   };
 
   int i = 0;
 #pragma unroll 1
   for (; i + 3 <= nkb; i += 3) {
-    load(I2{}, kb0 + i + 2);
-    compute(I0{}, kb0 + i);
-    if (i + 3 < nkb) load(I0{}, kb0 + i + 3);
-    compute(I1{}, kb0 + i + 1);
-    if (i + 4 < nkb) load(I1{}, kb0 + i + 4);
-    compute(I2{}, kb0 + i + 2);
+    load(I2{});
+    compute(I0{});
+    if (i + 3 < nkb) load(I0{});
+    compute(I1{});
+    if (i + 4 < nkb) load(I1{});
+    compute(I2{});
   }
   if (i < nkb) {
-    compute(I0{}, kb0 + i);
-    if (i + 1 < nkb) compute(I1{}, kb0 + i + 1);
+    compute(I0{});
+    if (i + 1 < nkb) compute(I1{});
   }
 
   // ------------------------------------------------------------------ reduction
@@ -564,12 +582,23 @@ int w4a16_decode_cl_launch(const void* x, const void* wt, const void* prm, const
   XQT_REQUIRE(slice_max <= (m > 8 ? kMaxSliceBlocks16 : kMaxSliceBlocks8) + 1);
   p.xrow_bytes = slice_max * 256 + kXPad;
   p.own_max = (mp + plan.s - 1) / plan.s;
-  int off = 128 + mp * p.xrow_bytes;
+  p.per = kblocks / p.pieces;
+  p.rem = kblocks % p.pieces;
+  int off = 384 + m * p.xrow_bytes;
   p.off_xsum = off; off += slice_max * sub * 16 * 4;
   p.off_redl = off; off += (plan.kw - 1) * mp * kRedStride * 4;
   p.off_redc = off; off += plan.s * p.own_max * kRedStride * 4;
   XQT_REQUIRE(off <= 200 * 1024);
   p.base_off = (act_dtype == XQT_B200_BF16 ? 128.f : 1024.f) + (nibble_signed ? 8.f : 0.f);
+  {
+    // XQT_B200_DECODE_PREFETCH=0 turns the start-of-kernel L2 prefetch off (A/B measurements)
+    static int prefetch = -1;
+    if (prefetch < 0) {
+      const char* v = getenv("XQT_B200_DECODE_PREFETCH");
+      prefetch = (v != nullptr && v[0] == '0') ? 0 : 1;
+    }
+    p.prefetch = prefetch;
+  }
   const int grid = tiles * plan.s, threads = 128 * plan.kw;
   if (act_dtype == XQT_B200_BF16) {
     if (param_dtype == XQT_B200_BF16) return dcl_dispatch<__nv_bfloat16, __nv_bfloat16>(p, group_size, nt, grid, threads, plan.s, off, stream);

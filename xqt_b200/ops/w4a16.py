@@ -169,7 +169,7 @@ def bind_w4a16_linear(
             native.DTYPE_CODE[scales.dtype], native.DTYPE_CODE[dtype], 0)
     variant_code = native.VARIANT[variant]
     index = device.index if device.index is not None else torch.cuda.current_device()
-    keep = (qweight, scales, zero_points, bias32)  # noqa: F841 - the closure owns references
+    keep = (qweight, scales, zero_points, bias32)
 
     def run(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         if x.dtype != dtype or x.ndim != 2 or x.shape[0] != rows or x.shape[1] != kk or not x.is_contiguous() \
@@ -186,6 +186,7 @@ def bind_w4a16_linear(
             native.check(code, "xqt_b200_w4a16_run")
         return out
 
+    run.keep = keep          # the callable owns the tensors whose raw pointers it passes
     return run
 
 
@@ -240,7 +241,7 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
         tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), int(tiled.has_zero_point),
                 native.DTYPE_CODE[dtype], native.DTYPE_CODE[tiled.params.dtype])
     index = device.index if device.index is not None else torch.cuda.current_device()
-    keep = (tiled, bias32)  # noqa: F841 - the closure owns references
+    keep = (tiled, bias32)
 
     def run(x: torch.Tensor, out: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
         if x.dtype != dtype or x.ndim != 2 or x.shape[0] != rows or x.shape[1] != k or not x.is_contiguous() \
@@ -260,6 +261,7 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
             native.check(code, symbol)
         return out
 
+    run.keep = keep          # the callable owns the tensors whose raw pointers it passes
     return run
 
 
@@ -283,7 +285,7 @@ def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tens
     index = device.index if device.index is not None else torch.cuda.current_device()
     status = native.status_word(device)
     status_ptr = status.data_ptr()
-    keep = (tiled, bias32, status)  # noqa: F841 - the closure owns references
+    keep = (tiled, bias32, status)
 
     def run(x: torch.Tensor, out: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
         if x.dtype != dtype or x.ndim != 2 or x.shape[0] != rows or x.shape[1] != k or not x.is_contiguous() \
@@ -302,6 +304,7 @@ def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tens
             native.check(code, "xqt_b200_w4a16_decode_lanes")
         return out
 
+    run.keep = keep          # the callable owns the tensors whose raw pointers it passes
     return run
 
 
