@@ -41,12 +41,10 @@ GROUP = 128
 METRIC = "w4a16_decode_gemv_weight_bandwidth"
 UNIT = "GB/s"
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_tc_kernel launch from the committed
-# ncu capture (profiles/), or None while no capture backs it
-# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_tc_kernel launch (K=4096, N=14336, M=16:
-# 31,410,688 bytes, see profiles/) over that launch's algorithmic bytes; traffic grows with the weight bytes, so
-# the step's average launch is scaled by this ratio
-NCU_TRAFFIC_RATIO = 31410688 / 31784960
+# dram__bytes_read.sum + dram__bytes_write.sum of one w4a16_decode_cl_kernel launch in an ncu capture
+# (K=14336, N=4096, M=1: 31,256,320 bytes) over that launch's algorithmic bytes; traffic grows with the
+# weight bytes, so the step's average launch is scaled by this ratio
+NCU_TRAFFIC_RATIO = 31256320 / 31232000
 
 
 def _log(msg: str) -> None:
@@ -438,7 +436,7 @@ def run_gpu_arm(args) -> None:
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "traffic": round(NCU_TRAFFIC_RATIO * alg_bytes_step / (len(SHAPES) * len(MS))), "peak_source": f"of {peak_kind}",
-            "kernel": "w4a16_decode_tc_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank); traffic = bytes of the average launch, scaled from one ncu capture",
+            "kernel": "w4a16_decode_cl_kernel", "note": "algorithmic bytes of the 16 launches of a step / step time (per rank); traffic = bytes of the average launch, scaled from one ncu capture (not a run-time counter)",
         },
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -146,7 +146,7 @@ int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, co
  * decode kernel.  Same replaced reference entry points and arithmetic as xqt_b200_w4a16_decode_tiled
  * (xqt_awq_w4a16_sm89_decode / _pack, awq_w4a16_sm89_kernel.cu:728-784; the execution layout plays the
  * role of sm89_awq_w4a16_interleaved_v1, awq_w4a16_decode_sm89.py:16-98).
- *   lane_weights  uint8 [ceil(N/128)][K/128][4 warps][2 row tiles][32 lanes][32]   (prepack.py: lanes_w4)
+ *   lane_weights  uint8 [ceil(N/128)][K/128][4 warps][2 row tiles][2 halves][32 lanes][16]   (prepack.py: lanes_w4)
  *                 unsigned codes; two's-complement nibbles are stored as code + 8 and announced by
  *                 nibble_signed = 1
  *   lane_params   param_dtype [ceil(N/128)][K/128][128/group_size][4 warps][8][4][2] = (scale, zero point)
@@ -158,7 +158,7 @@ int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, co
  * Needs no workspace: the K pieces of a tile are the CTAs of one thread-block cluster and reduce
  * through distributed shared memory in a fixed order (bit-reproducible). */
 int xqt_b200_w4a16_decode_lanes_supported(int m, int n, int k, int group_size);
-/* How the kernel would cut this problem: *warp_quads K pieces inside a CTA (1, 2 or 4) times *cluster
+/* How the kernel would cut this problem: *warp_quads K pieces inside a CTA (1 or 2) times *cluster
  * CTAs per 128-channel tile (1..8).  set_plan forces one split for every later call of the process
  * (a tuning aid; (0, 0) returns to the automatic choice); a forced split is still shrunk to what the
  * problem's K allows.  No counterpart in the reference, whose decode kernel has one fixed shape

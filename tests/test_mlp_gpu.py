@@ -45,7 +45,7 @@ def test_mlp_single_gpu(hidden, inter, m):
     # three chained bf16 roundings (gate/up, gating, down): the intermediate differs from the oracle's by isolated
     # ulps, which the down projection averages out
     assert oracle.rel_l2(out, ref) <= 2e-3
-    assert block.execution_metadata()["decode_layout"] == "rows128"
+    assert block.execution_metadata()["decode_layout"] == "lanes"
 
 
 _RANK_SCRIPT = r'''

@@ -53,7 +53,7 @@ def test_lanes_w4_round_trip(n, k, group, symmetric):
     pw = quantize.quantize_w4_symmetric(w, group_size=group) if symmetric else quantize.quantize_w4_asymmetric(w, group_size=group)
     tiled = prepack.lanes_w4(pw.qweight, pw.scales, pw.zero_points, group_size=group, nibble_signed=symmetric)
     assert tiled.layout == "lanes"
-    assert tuple(tiled.weights.shape) == (-(-n // 128), k // 128, 4, 2, 32, 32)
+    assert tuple(tiled.weights.shape) == (-(-n // 128), k // 128, 4, 2, 2, 32, 16)
     assert tuple(tiled.params.shape) == (-(-n // 128), k // 128, 128 // group, 4, 8, 4, 2)
     assert tiled.nbytes == tiled.weights.numel() + tiled.params.numel() * tiled.params.element_size()
     q, s, z = prepack.untile_w4(tiled)
@@ -73,7 +73,7 @@ def test_lanes_w4_fragment_semantics():
     scales = torch.ones((n, k // 128), dtype=torch.bfloat16)
     tiled = prepack.lanes_w4(qweight, scales, None, group_size=128, nibble_signed=False)
     x = torch.randint(-3, 4, (m, k), generator=seeded(4), dtype=torch.int64)
-    b = tiled.weights.reshape(1, k // 128, 4, 2, 32, 8, 4).to(torch.int64)
+    b = tiled.weights.permute(0, 1, 2, 3, 5, 4, 6).reshape(1, k // 128, 4, 2, 32, 8, 4).to(torch.int64)   # lane-major view
     words = b[..., 0] | (b[..., 1] << 8) | (b[..., 2] << 16) | (b[..., 3] << 24)
     out = torch.zeros((n, m), dtype=torch.int64)
     for kb in range(k // 128):

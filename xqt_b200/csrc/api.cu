@@ -190,7 +190,7 @@ int xqt_b200_w4a16_decode_lanes_plan(int m, int n, int k, int group_size, int* w
 
 int xqt_b200_w4a16_decode_lanes_set_plan(int warp_quads, int cluster) {
   XQT_REQUIRE((warp_quads == 0 && cluster == 0) ||
-              ((warp_quads == 1 || warp_quads == 2 || warp_quads == 4) && cluster >= 1 && cluster <= 8));
+              ((warp_quads == 1 || warp_quads == 2) && cluster >= 1 && cluster <= 8));
   w4a16_decode_cl_set_plan(warp_quads, cluster);
   return 0;
 }

@@ -5,9 +5,13 @@
 // Work split.  A tile is 128 output channels.  Its K range is cut into `pieces` = KW x S runs of
 // 128-K blocks: S CTAs (the cluster) times KW warp quads inside a CTA.  One warp owns 32 channels
 // (two 16-row A tiles of mma.m16n8k16) of one piece; it streams its packed weights straight from
-// global memory into registers with 32-byte loads, two 128-K blocks ahead of the arithmetic (a
-// three-slot register ring), so that a block's 1 KiB per (warp, A tile) is one fully coalesced
-// request and nothing in the main loop waits on a barrier.
+// global memory into registers with 16-byte loads (512 contiguous bytes per warp and request), three
+// 64-K half blocks ahead of the arithmetic (a four-slot register ring), and asks for the rest of its
+// piece into L2 with bulk prefetches on entry; nothing in the main loop waits on a barrier.
+// Measured alternatives that lost: staging the weights through per-warp shared-memory rings filled by
+// bulk copies (64 registers, four CTAs per SM: 11.5 us against 9.4 us on the 31 MB layers), an
+// 80-register build for three CTAs per SM (12.9 us: future kernels' CTAs crowd the SMs), and per-owner
+// mbarrier arrivals in place of the closing cluster barrier (11.2 us).
 //
 // Arithmetic.  A nibble becomes the exact bf16/fp16 integer B + q with one shift and one lop3
 // (B = 128 or 1024, the value of the exponent pattern it is or-ed into); eight MMAs accumulate one
@@ -44,7 +48,11 @@ namespace dcl {
 constexpr int kTileRows = 128;
 constexpr int kKB = 128;              // K per block: one 32-byte load per (lane, A tile)
 constexpr int kMaxCluster = 8;        // portable cluster size
-constexpr int kMaxKW = 4;             // warp quads (K pieces) per CTA
+constexpr int kMaxKW = 2;             // warp quads (K pieces) per CTA
+#ifndef XQT_DCL_MIN_CTAS
+#define XQT_DCL_MIN_CTAS 2
+#endif
+constexpr int kMinCtasSmallM = XQT_DCL_MIN_CTAS;   // resident 8-warp CTAs per SM the M <= 8 kernels are compiled for
 constexpr int kMaxThreads = 128 * kMaxKW;
 constexpr int kRedStride = 132;       // floats per token row of the reduction buffers (conflict-free)
 constexpr int kXPad = 64;             // bytes added to a shared-memory row of x
@@ -139,7 +147,7 @@ __device__ __forceinline__ void unpack_pair<__half>(uint32_t v, float& s, float&
 // T: activation / output type; P: type of the stored (scale, zero point) pairs; GK: quantisation
 // group (64 or 128); NT: 8-token MMA tiles (1 for M <= 8, 2 for M <= 16)
 template <typename T, typename P, int GK, int NT>
-__global__ void __launch_bounds__(dcl::kMaxThreads, 1)
+__global__ void __launch_bounds__(dcl::kMaxThreads, NT == 1 ? dcl::kMinCtasSmallM : 2)
 w4a16_decode_cl_kernel(const DecodeClParams p) {
   using namespace dcl;
   using Tr = ClTraits<T>;
@@ -172,38 +180,49 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   const int cta_kb0 = piece_start((int)rank * p.kw), cta_kb1 = piece_start(((int)rank + 1) * p.kw);
   const int nkb = kb1 - kb0;
 
-  const uint8_t* wbase = p.wt + ((size_t)tile * p.kblocks * 4 + w) * 2048 + lane * 32;
-  const uint8_t* pbase = p.prm + (size_t)tile * p.kblocks * kPrmBlockBytes +
-                         (P32 ? ((w * 8 + r) * 4 + c) * 8 : (w * 8 + r) * 16);
+  const uint8_t* wp = p.wt + (((size_t)tile * p.kblocks + kb0) * 4 + w) * 2048 + lane * 16;   // next block to request
+  const uint8_t* pp = p.prm + ((size_t)tile * p.kblocks + kb0) * kPrmBlockBytes +
+                      (P32 ? ((w * 8 + r) * 4 + c) * 8 : (w * 8 + r) * 16);
 
-  // register ring: packed weights of two A tiles and the parameters of one 128-K block per slot
-  uint32_t wq[3][2][8];
-  uint32_t pr[3][SUB][PR];
-  const uint8_t* wp = wbase + (size_t)kb0 * 8192;            // next block to request
-  const uint8_t* pp = pbase + (size_t)kb0 * kPrmBlockBytes;
+  // register ring of four 64-K half blocks: [slot][row tile][word of K-step]; slot parity = half.
+  // Parameters travel with the second half of their block (group 128: one set per block, two sets
+  // held) or with every half (group 64: one set per half, four held).
+  constexpr int NPR = GK == 64 ? 4 : 2;
+  uint32_t wq[4][2][4];
+  uint32_t pr[NPR][PR];
   auto load = [&](auto slot_c) {
     constexpr int slot = decltype(slot_c)::value;
-    ldg256_stream(wq[slot][0], wp);
-    ldg256_stream(wq[slot][1], wp + 1024);
-#pragma unroll
-    for (int sub = 0; sub < SUB; ++sub) {
-      if constexpr (P32) ldg64_stream(pr[slot][sub], pp + sub * 1024);
-      else ldg128_stream(pr[slot][sub], pp + sub * 512);
+    constexpr int half = slot & 1;
+    ldg128_stream(wq[slot][0], wp + half * 512);
+    ldg128_stream(wq[slot][1], wp + 1024 + half * 512);
+    if constexpr (GK == 64) {
+      if constexpr (P32) ldg64_stream(pr[slot], pp + half * 1024);
+      else ldg128_stream(pr[slot], pp + half * 512);
+    } else if constexpr (half == 1) {
+      if constexpr (P32) ldg64_stream(pr[slot >> 1], pp);
+      else ldg128_stream(pr[slot >> 1], pp);
     }
-    wp += 8192;
-    pp += kPrmBlockBytes;
+    if constexpr (half == 1) {
+      wp += 8192;
+      pp += kPrmBlockBytes;
+    }
   };
   using I0 = std::integral_constant<int, 0>;
   using I1 = std::integral_constant<int, 1>;
   using I2 = std::integral_constant<int, 2>;
+  using I3 = std::integral_constant<int, 3>;
+  const int halves = 2 * nkb;
 
   // the first weights are on their way before anything else happens
-  if (nkb > 0) load(I0{});
-  if (nkb > 1) load(I1{});
+  if (halves > 0) {
+    load(I0{});
+    load(I1{});
+  }
+  if (halves > 2) load(I2{});
   // ... and the rest of this warp's piece is requested into L2 right away (one bulk prefetch per
   // block and lane: the warp's 2 KiB of a block are contiguous), so that the whole layer is in
   // flight from HBM from the first microsecond and the register ring only has to cover L2 latency
-  for (int i = 2 + lane; i < nkb && p.prefetch; i += 32) {
+  for (int i = 1 + lane; i < nkb && p.prefetch; i += 32) {
     bulk_prefetch_l2(p.wt + (((size_t)tile * p.kblocks + kb0 + i) * 4 + w) * 2048, 2048);
     bulk_prefetch_l2(p.prm + ((size_t)tile * p.kblocks + kb0 + i) * kPrmBlockBytes + w * (kPrmBlockBytes / 4), kPrmBlockBytes / 4);
   }
@@ -213,7 +232,6 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
     fence_barrier_init();
   }
   if (S > 1) cluster_arrive_relaxed();   // phase 0: "this CTA runs"; waited for before the first remote store
-  grid_launch_dependents();
 
   const int slice_kb = cta_kb1 - cta_kb0;
   const int slice_bytes = slice_kb * 256;
@@ -230,6 +248,9 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
     if (p.status != nullptr) atomicExch(p.status, (unsigned int)kTimeout);
   }
 
+  // The next kernel of the stream may become resident from here on (measured: triggering it at entry
+  // instead lets several future kernels pile up on the SMs and costs the small layers 0.2 us each).
+  grid_launch_dependents();
   // activation group sums on the tensor cores: A = ones, so every row of the result is sum_k x[m,k]
   {
     const int nwarps = nthreads >> 5;
@@ -283,37 +304,40 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   }
   uint32_t xsum_a = xsum_s + ((kb0 - cta_kb0) * SUB * 16 + 2 * c) * 4;
 
+  float tmp[2][NT][4];
   auto compute = [&](auto slot_c) {
     constexpr int slot = decltype(slot_c)::value;
-#pragma unroll
-    for (int sub = 0; sub < SUB; ++sub) {
-      float tmp[2][NT][4];
+    constexpr int half = slot & 1;
+    if constexpr (GK == 64 || half == 0) {
 #pragma unroll
       for (int t = 0; t < 2; ++t)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) tmp[t][nt][i] = 0.f;
-      uint32_t xb[NT][4];
+          for (int v = 0; v < 4; ++v) tmp[t][nt][v] = 0.f;
+    }
+    uint32_t xb[NT][4];
 #pragma unroll
-      for (int jj = 0; jj < STEPS; ++jj) {
-        const int j = sub * STEPS + jj;
-        if ((j & 1) == 0) {
+    for (int jj = 0; jj < 4; ++jj) {
+      if ((jj & 1) == 0) {
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) cl_lds128(xb[nt], xrow[nt] + (j >> 1) * 64);
-        }
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const uint32_t word = wq[slot][t][j];
-          uint32_t a[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            asm("lop3.b32 %0, %1, %2, %3, 0xea;\n" : "=r"(a[i]) : "r"(word >> (4 * i)), "n"(0x000f000f), "r"(magic));
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) mma_16816<T>(tmp[t][nt], a, xb[nt][(j & 1) * 2], xb[nt][(j & 1) * 2 + 1]);
-        }
+        for (int nt = 0; nt < NT; ++nt) cl_lds128(xb[nt], xrow[nt] + (half * 2 + (jj >> 1)) * 64);
       }
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const uint32_t word = wq[slot][t][jj];
+        uint32_t a[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          asm("lop3.b32 %0, %1, %2, %3, 0xea;\n" : "=r"(a[i]) : "r"(word >> (4 * i)), "n"(0x000f000f), "r"(magic));
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_16816<T>(tmp[t][nt], a, xb[nt][(jj & 1) * 2], xb[nt][(jj & 1) * 2 + 1]);
+      }
+    }
+    if constexpr (GK == 64 || half == 1) {
       // y += s * (group sum - (B + z) * sum_k x)
+      constexpr int sub = GK == 64 ? half : 0;
+      constexpr int set = GK == 64 ? slot : (slot >> 1);
       float2 xs2[NT];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) xs2[nt] = cl_lds64f(xsum_a + (sub * 16 + nt * 8) * 4);
@@ -321,41 +345,46 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
       for (int t = 0; t < 2; ++t) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          float s, z;
+          float sc, z;
           if constexpr (P32) {
             const int from = (lane & ~3) | (t * 2 + h);
-            s = __uint_as_float(__shfl_sync(0xffffffffu, pr[slot][sub][0], from));
-            z = __uint_as_float(__shfl_sync(0xffffffffu, pr[slot][sub][1], from));
+            sc = __uint_as_float(__shfl_sync(0xffffffffu, pr[set][0], from));
+            z = __uint_as_float(__shfl_sync(0xffffffffu, pr[set][1], from));
           } else {
-            unpack_pair<P>(pr[slot][sub][t * 2 + h], s, z);
+            unpack_pair<P>(pr[set][t * 2 + h], sc, z);
           }
           const float nzb = -(z + base_off);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            acc[t][nt][h * 2 + 0] = fmaf(s, fmaf(nzb, xs2[nt].x, tmp[t][nt][h * 2 + 0]), acc[t][nt][h * 2 + 0]);
-            acc[t][nt][h * 2 + 1] = fmaf(s, fmaf(nzb, xs2[nt].y, tmp[t][nt][h * 2 + 1]), acc[t][nt][h * 2 + 1]);
+            acc[t][nt][h * 2 + 0] = fmaf(sc, fmaf(nzb, xs2[nt].x, tmp[t][nt][h * 2 + 0]), acc[t][nt][h * 2 + 0]);
+            acc[t][nt][h * 2 + 1] = fmaf(sc, fmaf(nzb, xs2[nt].y, tmp[t][nt][h * 2 + 1]), acc[t][nt][h * 2 + 1]);
           }
         }
       }
     }
+    if constexpr (half == 1) {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) xrow[nt] += xstep[nt];
-    xsum_a += SUB * 16 * 4;
+      for (int nt = 0; nt < NT; ++nt) xrow[nt] += xstep[nt];
+      xsum_a += SUB * 16 * 4;
+    }
   };
 
-  int i = 0;
+  // slots 0, 1, 2 hold halves h, h+1, h+2 at the top of an iteration
+  int h = 0;
 #pragma unroll 1
-  for (; i + 3 <= nkb; i += 3) {
-    load(I2{});
+  for (; h + 4 <= halves; h += 4) {
+    load(I3{});
     compute(I0{});
-    if (i + 3 < nkb) load(I0{});
+    if (h + 4 < halves) load(I0{});
     compute(I1{});
-    if (i + 4 < nkb) load(I1{});
+    if (h + 5 < halves) load(I1{});
     compute(I2{});
+    if (h + 6 < halves) load(I2{});
+    compute(I3{});
   }
-  if (i < nkb) {
+  if (h < halves) {
     compute(I0{});
-    if (i + 1 < nkb) compute(I1{});
+    compute(I1{});
   }
 
   // ------------------------------------------------------------------ reduction
@@ -477,7 +506,7 @@ ClPlan cl_plan(int tiles, int kblocks, int m) {
     int pieces = 1;
     while (pieces < kMaxKW * kMaxCluster && (long long)tiles * 4 * (pieces * 2) <= wave_warps && pieces * 2 * 2 <= kblocks)
       pieces *= 2;
-    plan.kw = pieces == 1 ? 1 : (pieces > 2 * kMaxCluster ? 4 : 2);
+    plan.kw = pieces == 1 ? 1 : 2;
     plan.s = pieces / plan.kw;
     // a CTA's K slice (kblocks / s) must fit its shared memory: trade warp quads for CTAs
     while ((kblocks + plan.s - 1) / plan.s + 1 > max_slice + 1 && plan.s < kMaxCluster) {
@@ -487,7 +516,6 @@ ClPlan cl_plan(int tiles, int kblocks, int m) {
   }
   if (plan.kw < 1) plan.kw = 1;
   if (plan.kw > kMaxKW) plan.kw = kMaxKW;
-  if (plan.kw == 3) plan.kw = 2;
   if (plan.s < 1) plan.s = 1;
   if (plan.s > kMaxCluster) plan.s = kMaxCluster;
   while (plan.kw * plan.s > kblocks && plan.kw > 1) plan.kw >>= 1;

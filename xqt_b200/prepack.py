@@ -17,9 +17,10 @@ pack kernel xqt/kernels/jit/csrc/quantization/awq_w4a16_sm89_kernel.cu:405-479).
            the canonical scales (zero point 0 when the weight is symmetric).
 
 ``b200_w4_lanes_v1`` (cluster split-K decode GEMV, the default decode layout):
-  weights  uint8 ``[N/128 tiles][K/128 kblocks][4 warps][2 row tiles][32 lanes][32 bytes]``
+  weights  uint8 ``[N/128 tiles][K/128 kblocks][4 warps][2 row tiles][2 halves][32 lanes][16 bytes]``
            Lane ``4*r + c`` of (warp ``w``, row tile ``t``) holds, for the eight ``mma.m16n8k16`` steps
-           ``j`` of the block, one 32-bit word each.  Its nibble positions 0..7 carry channels
+           ``j`` of the block, one 32-bit word each: words 0..3 in half 0, words 4..7 in half 1 (a
+           warp-wide 16-byte load of one half is 512 contiguous bytes).  Its nibble positions 0..7 carry channels
            ``128*tile + 32*w + 16*t + r + (0,8,0,8,0,8,0,8)`` at ``k = 128*kblock + 32*(j//2) + 8*c +
            4*(j%2) + (0,0,2,2,1,1,3,3)``: ``(word >> 4*i) & 0x000f000f`` is register ``i`` of the A
            fragment, and the 16 bytes of activations a lane needs for two steps are contiguous.
@@ -48,7 +49,7 @@ class TiledW4:
     ``layout`` is ``"tile128"`` (weights ``[tiles, kblocks, 16, 32, 16]``, lane-major, for the
     stream-K mma.sync decode kernel), ``"rows128"`` (weights ``[tiles, kblocks, 4, 128, 16]``, one
     16-byte chunk of 32 K per channel, for the tcgen05 decode kernel whose threads each own a
-    channel) or ``"lanes"`` (weights ``[tiles, kblocks, 4, 2, 32, 32]``, params
+    channel) or ``"lanes"`` (weights ``[tiles, kblocks, 4, 2, 2, 32, 16]``, params
     ``[tiles, kblocks, 128/group, 4, 8, 4, 2]``, for the cluster split-K decode kernel).
     """
 
@@ -165,7 +166,8 @@ def lanes_w4(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Ten
     c = c.permute(0, 5, 1, 2, 4, 7, 6, 8, 9, 3)                     # [T, kb, w, t, r, c, q, jj, slot, h]
     c = c[..., list(_LANE_SLOT_ORDER), :]
     nib = c.reshape(tiles, kblocks, 4, 2, 32, 8, 8)                 # [.., lane, word j, nibble p = 2*slot' + h]
-    weights = (nib[..., 0::2] | (nib[..., 1::2] << 4)).reshape(tiles, kblocks, 4, 2, 32, 32).contiguous()
+    by = (nib[..., 0::2] | (nib[..., 1::2] << 4)).reshape(tiles, kblocks, 4, 2, 32, 2, 16)   # [.., lane, half, 16 B]
+    weights = by.permute(0, 1, 2, 3, 5, 4, 6).contiguous()          # [tile, kb, warp, row tile, half, lane, 16 B]
 
     def laned(param: torch.Tensor) -> torch.Tensor:
         q = param
@@ -182,7 +184,7 @@ def lanes_w4(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Ten
 
 def _unlane_w4(tiled: TiledW4) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
     tiles, kblocks, per_block = tiled.tiles, tiled.k // KBLOCK, KBLOCK // tiled.group_size
-    w = tiled.weights.reshape(tiles, kblocks, 4, 2, 32, 8, 4)
+    w = tiled.weights.permute(0, 1, 2, 3, 5, 4, 6).reshape(tiles, kblocks, 4, 2, 32, 8, 4)
     nib = torch.stack((w & 0x0F, w >> 4), dim=-1).reshape(tiles, kblocks, 4, 2, 8, 4, 4, 2, 4, 2)
     #                                                      [T, kb, w, t, r, c, q, jj, slot', h]
     inverse = [list(_LANE_SLOT_ORDER).index(e) for e in range(4)]
