@@ -197,6 +197,10 @@ int xqt_b200_w4a16_decode_tiled_static(const void* activation, const void* tiled
                                        int act_dtype, int param_dtype, xqt_b200_stream_t stream);
 size_t xqt_b200_w4a16_decode_static_scratch_bytes(void);
 int xqt_b200_w4a16_decode_static_max_n(void);
+/* Copies the status word of the built-in scratch of the current device to *host_status (host pointer)
+ * and synchronises `stream`; it describes the LAST call of xqt_b200_w4a16_decode_tiled_static on that
+ * device (each call clears it first): 0 = every bounded wait completed.  Allocates nothing. */
+int xqt_b200_w4a16_decode_static_status(unsigned int* host_status, xqt_b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * Activation prologue shared by the W8A8 and W4A4 linears: block-diagonal Hadamard rotation,
@@ -284,10 +288,15 @@ int xqt_b200_lowrank_down_tc(const void* rotated, const void* down, float* la, i
  *                buffers from call to call (the hand-shake has no exit barrier)
  *   output[count] = round(sum over ranks in rank order + bias[i mod n]); count, n multiples of 4
  * Every rank launches it on its own GPU after its GEMV on the same stream.  The wait for the peers
- * is bounded; a timeout is reported through the status word at workspace[0] (>= 256 bytes). */
+ * is bounded: after spin_limit polls of a peer's flag (0 = the default, 2^22) the kernel stores 128
+ * to *status, stops waiting and finishes normally; the output is then NOT the sum and the call must be
+ * treated as failed.  status may be device memory or pinned host memory (then the host sees a timeout
+ * without synchronising).  `call` comes from the host, so a launch must not be captured into a CUDA
+ * graph: a replay would reuse the call number and its hand-shake would pass at once. */
 int xqt_b200_peer_allreduce(const void* const* partials, void* const* flags, int rank, int world,
                             unsigned int call, long long count, int n, const float* bias, void* output,
-                            int out_dtype, void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream);
+                            int out_dtype, unsigned int spin_limit, unsigned int* status,
+                            xqt_b200_stream_t stream);
 
 /* SwiGLU gating between the projections of an MLP: output[m, i] = silu(gate_up[m, i]) * gate_up[m, inter + i],
  * evaluated in fp32 and rounded once.  gate_up is [M, 2*inter] (the gate and up projections fused

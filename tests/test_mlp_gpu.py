@@ -103,3 +103,67 @@ def test_mlp_two_ranks_nccl(tmp_path):
         ref = omlp.forward(x, w(gate), w(up), w(down), group_size=128)
         y = torch.load(tmp_path / f"y{m}.pt", weights_only=True)
         assert oracle.rel_l2(y, ref) <= 2e-3
+
+
+def test_peer_allreduce_bounded_wait_reports_timeout_and_returns():
+    """One GPU plays rank 0 of two; "rank 1" never launches, so its flag stays unset.  With a short
+    poll limit the kernel must give up, store 128 to the (pinned host) status word and finish through
+    its normal path; once the flag is set a second call produces the sum."""
+
+    import ctypes
+
+    from xqt_b200 import native
+
+    lib = native.library()
+    dev = torch.device("cuda", 0)
+    count = n = 256
+    partial = [torch.full((count,), 1.0, device=dev), torch.full((count,), 2.0, device=dev)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(2)]
+    out = torch.zeros(count, dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(16, dtype=torch.int32).pin_memory()
+    array = ctypes.c_void_p * 2
+    partials, flag_ptrs = array(*(t.data_ptr() for t in partial)), array(*(t.data_ptr() for t in flags))
+    stream = native.stream_handle(dev)
+
+    def call(number, limit):
+        code = lib.xqt_b200_peer_allreduce(partials, flag_ptrs, 0, 2, number, count, n, None, out.data_ptr(),
+                                           native.BF16, limit, status.data_ptr(), stream)
+        assert code == 0
+        torch.cuda.synchronize()
+
+    call(1, 2000)                                   # about a millisecond of polling, then it gives up
+    assert int(status[0]) == 128
+    assert int(flags[1][0].item()) == 1             # rank 0 did signal its peer
+    status.zero_()
+    flags[0][1] = 2                                 # "rank 1" signals call 2
+    torch.cuda.synchronize()
+    call(2, 2000)
+    assert int(status[0]) == 0
+    assert torch.equal(out.float().cpu(), torch.full((count,), 3.0))
+
+
+def test_peer_allreduce_refuses_graph_capture_and_surfaces_timeouts():
+    """Host-side guards of PeerAllReduce that need no peer: a recorded timeout raises on the next
+    use, and a captured call is refused (the call number is a host counter)."""
+
+    from xqt_b200.errors import XQTBackendError
+    from xqt_b200.parallel import PeerAllReduce
+
+    obj = PeerAllReduce.__new__(PeerAllReduce)
+    obj._host_status = torch.zeros(16, dtype=torch.int32).pin_memory()
+    obj._host_status[0] = 128
+    with pytest.raises(XQTBackendError):
+        obj.check()
+    assert int(obj._host_status[0]) == 0            # reported once, then cleared
+    obj.check()
+
+
+def test_static_decode_status_is_readable():
+    import ctypes
+
+    from xqt_b200 import native
+
+    value = ctypes.c_uint(77)
+    with torch.cuda.device(0):
+        code = native.library().xqt_b200_w4a16_decode_static_status(ctypes.byref(value), native.stream_handle(torch.device("cuda", 0)))
+    assert code == 0 and value.value == 0

@@ -45,7 +45,8 @@ int w4a4_dense_launch(const void*, const float*, const void*, const float*, cons
                       int, int, int, int, void*, size_t, cudaStream_t);
 int lowrank_down_tc_launch(const void*, const void*, float*, int, int, int, unsigned int*, cudaStream_t);
 int peer_allreduce_launch(const void* const*, void* const*, int, int, unsigned int, long long, int, const float*, void*, int,
-                          unsigned int*, cudaStream_t);
+                          unsigned int, unsigned int*, cudaStream_t);
+int w4a16_decode_static_status(unsigned int*, cudaStream_t);
 }  // namespace xqt_b200
 
 using namespace xqt_b200;
@@ -226,6 +227,11 @@ int xqt_b200_w4a16_decode_tiled_static(const void* activation, const void* tiled
 
 size_t xqt_b200_w4a16_decode_static_scratch_bytes(void) { return w4a16_decode_static_scratch_bytes(); }
 
+int xqt_b200_w4a16_decode_static_status(unsigned int* host_status, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(host_status != nullptr);
+  return w4a16_decode_static_status(host_status, (cudaStream_t)stream);
+}
+
 int xqt_b200_w4a16_decode_static_max_n(void) { return w4a16_decode_static_max_n(); }
 
 int xqt_b200_rotate_quantize(const void* activation, const float* column_scale, void* codes, float* scales,
@@ -295,11 +301,11 @@ int xqt_b200_lowrank_down_tc(const void* rotated, const void* down, float* la, i
 }
 
 int xqt_b200_peer_allreduce(const void* const* partials, void* const* flags, int rank, int world, unsigned int call,
-                            long long count, int n, const float* bias, void* output, int out_dtype, void* workspace,
-                            size_t workspace_bytes, xqt_b200_stream_t stream) {
-  XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
-  return peer_allreduce_launch(partials, flags, rank, world, call, count, n, bias, output, out_dtype,
-                               reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
+                            long long count, int n, const float* bias, void* output, int out_dtype,
+                            unsigned int spin_limit, unsigned int* status, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(status != nullptr);
+  return peer_allreduce_launch(partials, flags, rank, world, call, count, n, bias, output, out_dtype, spin_limit, status,
+                               (cudaStream_t)stream);
 }
 
 int xqt_b200_swiglu(const void* gate_up, void* output, int m, int inter, int dtype, xqt_b200_stream_t stream) {

@@ -13,8 +13,10 @@
 // numbers only grow; partial buffers are used alternately (call e uses slot e & 1), so a rank can
 // only overwrite a slot two calls later, after every peer has signalled the call in between, which
 // a peer does only after its own kernel of the earlier call has finished reading.  No exit barrier
-// is needed.  The wait is bounded: after kSpin polls the kernel records a status word, skips the
-// wait and finishes (the output is then not the sum; the host reads the status).
+// is needed.  The wait is bounded: after `spin_limit` polls (kSpin when the caller passes 0) the kernel
+// records kTimeout in the status word -- which may live in pinned host memory, so that the host sees
+// it without a synchronisation -- skips the wait and finishes through its normal path; the output is
+// then not the sum and the caller must treat the call as failed.
 #include "common.cuh"
 
 namespace xqt_b200 {
@@ -35,6 +37,7 @@ struct PeerReduceParams {
   const float* bias;                      // [n] or null
   void* out;                              // [count] in T
   unsigned int* status;
+  unsigned int spin_limit;                // polls before the wait for a peer gives up
 };
 
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
@@ -58,8 +61,8 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReducePar
     unsigned int spins = 0;
     // call numbers only grow: "signalled this call or a later one"
     while ((int)(ld_acquire_sys(f) - p.call) < 0) {
-      if (++spins >= kSpin) {
-        atomicExch(p.status, (unsigned int)kTimeout);
+      if (++spins >= p.spin_limit) {
+        st_release_sys(p.status, (unsigned int)kTimeout);   // device or pinned host memory
         break;
       }
     }
@@ -90,8 +93,8 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReducePar
 }
 
 int peer_allreduce_launch(const void* const* partials, void* const* flags, int rank, int world, unsigned int call,
-                          long long count, int n, const float* bias, void* out, int out_dtype, unsigned int* status,
-                          cudaStream_t stream) {
+                          long long count, int n, const float* bias, void* out, int out_dtype, unsigned int spin_limit,
+                          unsigned int* status, cudaStream_t stream) {
   using namespace par;
   XQT_REQUIRE(world >= 2 && world <= kMaxWorld && rank >= 0 && rank < world && call > 0);
   XQT_REQUIRE(count > 0 && count % 4 == 0 && n > 0 && n % 4 == 0 && count % n == 0);
@@ -105,6 +108,7 @@ int peer_allreduce_launch(const void* const* partials, void* const* flags, int r
     p.flags[r] = reinterpret_cast<unsigned int*>(flags[r]);
   }
   p.rank = rank; p.world = world; p.call = call; p.count = count; p.n = n; p.bias = bias; p.out = out; p.status = status;
+  p.spin_limit = spin_limit == 0 ? kSpin : spin_limit;
   const long long vecs = count / 4;
   long long blocks = (vecs + 255) / 256;
   if (blocks > 148) blocks = 148;

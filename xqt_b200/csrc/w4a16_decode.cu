@@ -485,6 +485,18 @@ static int decode_static_scratch(unsigned char** out) {
 }
 
 size_t w4a16_decode_static_scratch_bytes() { return decode_static::kBytes; }
+
+// status word of the built-in scratch of the current device (the last call's: every call clears it)
+int w4a16_decode_static_status(unsigned int* host_status, cudaStream_t stream) {
+  unsigned char* ws = nullptr;
+  {
+    const int rc = decode_static_scratch(&ws);
+    if (rc != 0) return rc;
+  }
+  XQT_CUDA(cudaMemcpyAsync(host_status, ws, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
+  XQT_CUDA(cudaStreamSynchronize(stream));
+  return 0;
+}
 int w4a16_decode_static_max_n() { return decode_static::kMaxTiles * decode::kTileRows; }
 
 int w4a16_decode_launch_static(const void* x, const void* wt, const void* sz, const float* bias, const void* residual,

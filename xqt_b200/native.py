@@ -19,10 +19,7 @@ import torch
 
 from .errors import CudaCallError, NativeLibraryError
 
-import os
-
-# XQT_B200_LIBRARY points at an alternative build of the same ABI (e.g. an instrumented one)
-LIBRARY_PATH = pathlib.Path(os.environ.get("XQT_B200_LIBRARY") or pathlib.Path(__file__).resolve().parent / "libxqt_b200.so")
+LIBRARY_PATH = pathlib.Path(__file__).resolve().parent / "libxqt_b200.so"
 
 FP16, BF16, FP32 = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
@@ -64,7 +61,8 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a4_dense_preferred": (_I, [_I] * 3),
     "xqt_b200_w4a4_dense": (_I, [_P] * 8 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_lowrank_down_tc": (_I, [_P] * 3 + [_I] * 3 + [_P, _Z, _P]),
-    "xqt_b200_peer_allreduce": (_I, [_P, _P, _I, _I, ctypes.c_uint, ctypes.c_longlong, _I, _P, _P, _I, _P, _Z, _P]),
+    "xqt_b200_peer_allreduce": (_I, [_P, _P, _I, _I, ctypes.c_uint, ctypes.c_longlong, _I, _P, _P, _I, ctypes.c_uint, _P, _P]),
+    "xqt_b200_w4a16_decode_static_status": (_I, [ctypes.POINTER(ctypes.c_uint), _P]),
     "xqt_b200_swiglu": (_I, [_P, _P, _I, _I, _I, _P]),
     "xqt_b200_workspace_status": (_I, [_P, ctypes.POINTER(ctypes.c_uint), _P]),
 }

@@ -179,6 +179,9 @@ class PeerAllReduce:
         self._flags = array(*flag_ptrs)
         self._call = 0
         self._native = native
+        # the kernel reports a peer that never signalled here; pinned, so the host reads it without a sync
+        self._host_status = torch.zeros(16, dtype=torch.int32).pin_memory()
+        self.spin_limit = 0          # 0 = the kernel's default bound (2^22 polls)
         torch.cuda.synchronize(device)
         dist.barrier(group)          # every rank's zeros are in place before anybody signals
 
@@ -196,17 +199,31 @@ class PeerAllReduce:
         native = self._native
         if n % 4 or dtype not in (torch.float16, torch.bfloat16):
             raise XQTBackendError("PeerAllReduce: N must be a multiple of 4 and the output fp16 or bf16")
+        if torch.cuda.is_current_stream_capturing():
+            # the call number is a host-side counter passed by value: a replayed graph would repeat it,
+            # its wait would pass at once and it would sum partials that are still being written
+            raise XQTBackendError("PeerAllReduce.reduce cannot be captured into a CUDA graph")
+        self.check()
         self._call += 1
         if out is None:
             out = torch.empty((rows, n), device=self.device, dtype=dtype)
-        scratch = native.workspace(self.device, 256, "peer")
         with torch.cuda.device(self.device):
             code = native.library().xqt_b200_peer_allreduce(
                 self._partials[self._call & 1], self._flags, self.rank, self.world, self._call & 0xFFFFFFFF or 1, rows * n, n,
-                native.ptr(bias), out.data_ptr(), native.DTYPE_CODE[dtype], scratch.data_ptr(), scratch.numel(),
-                native.stream_handle(self.device))
+                native.ptr(bias), out.data_ptr(), native.DTYPE_CODE[dtype], int(self.spin_limit),
+                self._host_status.data_ptr(), native.stream_handle(self.device))
         native.check(code, "xqt_b200_peer_allreduce")
         return out
+
+    def check(self) -> None:
+        """Raise if a finished ``reduce`` gave up waiting for a peer (its output was not the sum).
+        Called at the start of every ``reduce``; call it after a synchronisation to check the last one."""
+
+        if int(self._host_status[0]) != 0:
+            code = int(self._host_status[0])
+            self._host_status.zero_()
+            raise XQTBackendError(f"PeerAllReduce: a rank did not signal within the wait bound (status {code}); "
+                                  "the affected outputs are not valid")
 
 
 def _default_swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
