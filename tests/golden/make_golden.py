@@ -51,7 +51,12 @@ def _install_omegaconf_stub() -> None:
     module.MISSING = "???"
     module.DictConfig = dict
     module.ListConfig = list
-    module.__getattr__ = lambda name: _Any()
+    def _module_getattr(name):
+        if name.startswith("__"):          # inspect / importlib probe dunder attributes of every module
+            raise AttributeError(name)
+        return _Any()
+
+    module.__getattr__ = _module_getattr
     errors = types.ModuleType("omegaconf.errors")
     errors.OmegaConfBaseException = Exception
     module.errors = errors
@@ -75,6 +80,7 @@ def main() -> None:
     from xqt.kernels.ops.gemm import layout as L
     from xqt.kernels.ops.gemm import quantize as Q
     from xqt.kernels.ops.gemm import reference as R
+    from xqt.contracts import weight_only as WO
 
     # ------------------------------------------------------------------ packing
     codes_u = torch.randint(0, 16, (6, 37), generator=gen(1), dtype=torch.int64)
@@ -109,10 +115,11 @@ def main() -> None:
         wp = torch.nn.functional.pad(w, (0, padded_k - k))
         grouped = wp.reshape(n, padded_k // group, group)
         if signed:
-            absmax = grouped.abs().amax(dim=2, keepdim=True)
-            scale = torch.where(absmax > 0, absmax / 7.0, torch.ones_like(absmax)).to(param_dtype)
-            codes = torch.clamp(torch.round(grouped / scale.float()), -8, 7).to(torch.int8).reshape(n, padded_k)
-            packed = L.pack_int4_signed(codes)
+            # the reference's own symmetric RTN (xqt/contracts/weight_only.py:40-71): packed signed
+            # nibbles, fp32 scale [N, G, 1]
+            packed, scale, padded_ref = WO._quantize_grouped_weight(
+                w, bits=4, group_size=group, input_features=k, output_features=n)
+            assert padded_ref == padded_k and param_dtype == torch.float32
             zeros = None
         else:
             lo, hi = grouped.amin(2, keepdim=True), grouped.amax(2, keepdim=True)
@@ -221,18 +228,42 @@ def main() -> None:
         input_features=128, output_features=24, group_size=64, padded_input_features=padded, quant_dtype="int4",
     )
     xs = torch.randn((7, 128), generator=gen(72))
-    # per-token fake-quant of ConvRot W4A4 (convrot_4bit.py:669-679), evaluated with its own formula
-    amax = xs.abs().amax(dim=-1, keepdim=True)
-    a_scale = torch.clamp(amax / 7.0, min=1e-6)
-    a_codes = torch.clamp(torch.round(xs / a_scale), min=-8, max=7)
+    # per-token fake-quant of ConvRot W4A4: the artifact's own methods (convrot_4bit.py:669-679)
+    lin4 = torch.nn.Linear(128, 24, bias=False)
+    with torch.no_grad():
+        lin4.weight.copy_(wsvd)
+    art4 = C4.ConvRotMixedPrecisionLinear.from_linear(lin4, rot_size=16, group_size=64)
+    a_scale = art4._activation_scale(xs)
+    a_fake = art4._quantize_rotated_activation(xs)
+    a_codes = torch.round(a_fake / a_scale)
     torch.save(
         {
             "w": wsvd, "down": down, "up": up, "residual": residual, "packed": packed, "scale": rscale,
             "bias": bias, "x": xs, "out_fp32": module(xs),
             "dequant": module.dequantize_residual(),
-            "act_scale_per_token": a_scale, "act_codes_per_token": a_codes,
+            "act_scale_per_token": a_scale, "act_codes_per_token": a_codes, "act_fake_quant_per_token": a_fake,
         },
         HERE / "svd_w4a4.pt",
+    )
+
+    # ------------------------------------------------------------------ the reference's own quantisers, called
+    wq1 = torch.randn((20, 200), generator=gen(80)) * 0.02
+    wq2 = torch.randn((16, 256), generator=gen(81)) * 0.02
+    wq2[3, 128:] = 0.0                                   # an all-zero group: scale 1
+    p1, s1, k1 = WO._quantize_grouped_weight(wq1, bits=4, group_size=64, input_features=200, output_features=20)
+    p2, s2, k2 = WO._quantize_grouped_weight(wq2, bits=4, group_size=128, input_features=256, output_features=16)
+    xa = torch.randn((5, 128), generator=gen(82))
+    rotated = art4._rotate_inputs(xa)
+    torch.save(
+        {
+            "wo_w1": wq1, "wo_packed1": p1, "wo_scale1": s1, "wo_padded1": torch.tensor(k1),
+            "wo_w2": wq2, "wo_packed2": p2, "wo_scale2": s2, "wo_padded2": torch.tensor(k2),
+            "convrot4_w": wsvd, "convrot4_packed_weight": art4.packed_weight, "convrot4_weight_scale": art4.weight_scale,
+            "convrot4_x": xa, "convrot4_x_rot16": rotated,
+            "convrot4_act_scale": art4._activation_scale(rotated),
+            "convrot4_act_fake_quant": art4._quantize_rotated_activation(rotated),
+        },
+        HERE / "quantizers.pt",
     )
     for path in sorted(HERE.glob("*.pt")):
         print(path.name, path.stat().st_size, "bytes")

@@ -138,6 +138,8 @@ def test_group_activation_quant_reduces_to_reference_per_token_formula(golden):
     codes, scale = w4a4.quantize_act_groups(g["x"], group_size=g["x"].shape[1])
     assert torch.equal(scale, g["act_scale_per_token"])
     assert torch.equal(codes.float(), g["act_codes_per_token"])
+    # the artifact's own fake-quantised activation (ConvRotMixedPrecisionLinear._quantize_rotated_activation)
+    assert torch.equal(codes.float() * scale, g["act_fake_quant_per_token"])
 
 
 def test_w4a4_two_forms_agree(golden):

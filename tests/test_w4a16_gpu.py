@@ -298,6 +298,36 @@ def test_decode_lanes_is_the_default_decode_layout():
     assert forced.layout == "rows128"
 
 
+@pytest.mark.parametrize("source", ["awq", "gptq"])
+def test_decode_of_an_imported_checkpoint_layer(source):
+    """HF AWQ / GPTQ int32 words -> canonical xqt_int4_nk_v1 (repack pinned bit for bit by the CPU golden
+    test) -> decode execution layout -> cluster decode kernel, against the oracle on the canonical form."""
+
+    from xqt_b200 import layout
+    from xqt_b200.ops.w4a16 import bind_w4a16_decode, prepare_decode
+
+    n, k, g, m = 256, 512, 128, 5
+    x = torch.randn((m, k), generator=seeded(91)).to(torch.bfloat16)
+    if source == "awq":      # words [K, N/8], scales / zero points [K/g, N]
+        words = torch.randint(-(2**31), 2**31 - 1, (k, n // 8), generator=seeded(92), dtype=torch.int64).to(torch.int32)
+        pw = layout.repack_awq_int4(words, logical_shape=(n, k), scales=torch.rand((k // g, n), generator=seeded(93)) * 0.01 + 0.002,
+                                    zero_points=torch.randint(0, 16, (k // g, n), generator=seeded(94)).to(torch.float32), group_size=g)
+        assert not pw.metadata.nibble_signed and pw.zero_points is not None
+    else:                    # words [K/8, N], scales [K/g, N], symmetric
+        words = torch.randint(-(2**31), 2**31 - 1, (k // 8, n), generator=seeded(95), dtype=torch.int64).to(torch.int32)
+        pw = layout.repack_gptq_int4(words, logical_shape=(n, k), scales=torch.rand((k // g, n), generator=seeded(96)) * 0.01 + 0.002,
+                                     group_size=g)
+        assert pw.metadata.nibble_signed and pw.zero_points is None
+    dev = torch.device("cuda", 0)
+    mv = lambda v: None if v is None else v.to(dev)
+    tiled = prepare_decode(mv(pw.qweight), mv(pw.scales), mv(pw.zero_points), group_size=g,
+                           nibble_signed=pw.metadata.nibble_signed)
+    assert tiled.layout == "lanes"
+    out = bind_w4a16_decode(tiled, rows=m, dtype=torch.bfloat16)(mv(x)).cpu()
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=g, signed=pw.metadata.nibble_signed)
+    assert oracle.rel_l2(out, ref) <= TOL
+
+
 # ---------------------------------------------------------------------------- tcgen05 GEMM (M > 16)
 
 

@@ -106,18 +106,27 @@ def test_dense_form_is_opt_in_and_close_to_the_integer_form():
     assert o16.rel_l2(dense.cpu(), integer.cpu()) <= 2e-3
 
 
-def test_config3_full_size():
+@pytest.mark.parametrize("factors", ["svd", "random"])
+def test_config3_full_size(factors):
     # x [4096,3072] with 1% outlier channels x20, randomized block-Hadamard 128, W [12288,3072], rank 32
     m, n, k, rank = 4096, 12288, 3072, 32
     rot = quantize.randomized_rotation(128, seed=3)
     x = _outliers(torch.randn((m, k), generator=seeded(3)), 33).to(torch.bfloat16)
     w = torch.randn((n, k), generator=seeded(4)) * 0.02
     w_rot = rot.apply(w)
-    # a truncated SVD of the full matrix takes ~10 s on the host; a seeded random rank-32 pair exercises the same path
-    down = (torch.randn((rank, k), generator=seeded(5)) * 0.05).to(torch.bfloat16)
-    up = (torch.randn((n, rank), generator=seeded(6)) * 0.05).to(torch.bfloat16)
-    residual = w_rot - up.float() @ down.float()
+    if factors == "svd":
+        # as the configuration states: rank-32 factors from a truncated SVD of W (the package's own
+        # svd_split, run on the GPU to keep the test short), residual = W - up @ down in fp32
+        down32, up32, residual = (t.cpu() for t in quantize.svd_split(w_rot.to(DEV), rank))
+        down, up = down32.to(torch.bfloat16), up32.to(torch.bfloat16)
+    else:
+        # a seeded random rank-32 pair: larger low-rank term than a Gaussian matrix's SVD gives
+        down = (torch.randn((rank, k), generator=seeded(5)) * 0.05).to(torch.bfloat16)
+        up = (torch.randn((n, rank), generator=seeded(6)) * 0.05).to(torch.bfloat16)
+        residual = w_rot - up.float() @ down.float()
     packed_w, scale = oracle.quantize_residual(residual, group_size=64)
+    packed_p, scale_p, _ = quantize.quantize_residual_int4(residual, group_size=64)
+    assert torch.equal(packed_p, packed_w) and torch.equal(scale_p, scale)      # product quantiser == oracle's
     layer = pack_svdq_w4a4_linear(None, down.to(DEV), up.to(DEV), None, packed_residual=packed_w.to(DEV),
                                   residual_scale=scale.to(DEV), rotation=rot)
     out = svdq_w4a4_linear(x.to(DEV), layer)

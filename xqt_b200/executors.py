@@ -14,6 +14,7 @@ xqt's ``GemmKernelRegistry`` (anything with ``register/replace/get``).
 from __future__ import annotations
 
 import os
+import weakref
 from dataclasses import replace as _dc_replace
 
 import torch
@@ -34,6 +35,39 @@ def _require_b200(device: torch.device) -> None:
     major, minor = torch.cuda.get_device_capability(device)
     if (major, minor) != (10, 0):
         raise XQTBackendError(f"B200 executor received sm_{major}{minor}")
+
+
+# Decode execution layouts derived from canonical weights, one per weight tensor.  Keyed on the
+# tensor object itself (weakly: the entry dies with the weight, so a recycled address can never hit a
+# stale layout) and checked against the tensor's version counter, the way xqt's runtime modules key
+# their prepacked W4A4 state on data_ptr/_version (xqt/runtime/modules/composite_add_w4a4.py:164-187).
+_decode_layouts: "weakref.WeakKeyDictionary[torch.Tensor, dict]" = weakref.WeakKeyDictionary()
+
+
+def _decode_entry(weight) -> dict | None:
+    """The cached decode layout of ``weight`` (built on first use), or None when the layer is outside
+    the decode kernel's envelope or XQT_B200_DECODE_PREPACK=0 asks to keep only the canonical bytes."""
+
+    from .ops.w4a16 import prepare_decode
+
+    if os.environ.get("XQT_B200_DECODE_PREPACK", "1") in {"0", ""}:
+        return None
+    meta = weight.metadata
+    group, k = int(meta.group_size), int(meta.logical_shape[1])
+    if group not in (64, 128) or int(meta.padded_k) != k or k % 128:
+        return None
+    qweight, scales, zeros = weight.qweight, weight.scales, weight.zero_points
+    versions = (qweight._version, scales._version, None if zeros is None else zeros._version,
+                scales.data_ptr(), None if zeros is None else zeros.data_ptr())
+    entry = _decode_layouts.get(qweight)
+    if entry is None or entry["versions"] != versions:
+        if zeros is not None and zeros.dtype != scales.dtype:
+            zeros = zeros.to(scales.dtype)
+        tiled = prepare_decode(qweight, scales.contiguous(), None if zeros is None else zeros.contiguous(),
+                               group_size=group, nibble_signed=bool(meta.nibble_signed), k=k, layout="lanes")
+        entry = {"versions": versions, "tiled": tiled, "bound": {}}
+        _decode_layouts[qweight] = entry
+    return entry
 
 
 def b200_w4a16_executor(activation, weight, *, spec, weight_scales=None, activation_scales=None,
@@ -74,6 +108,28 @@ def b200_w4a16_executor(activation, weight, *, spec, weight_scales=None, activat
         raise XQTBackendError("W4A16 epilogue declares residual but no residual was supplied")
     if bias is not None and tuple(bias.shape) not in {(problem.n,), (1, problem.n)}:
         raise XQTBackendError("B200 W4A16 bias must have shape [N] or [1,N]")
+    # decode sizes: the cluster split-K kernel on the lane-ordered layout derived (once) from this weight
+    if (variant == "auto" and 1 <= problem.m <= 16 and spec.epilogue.activation == "none"
+            and native.library().xqt_b200_w4a16_decode_lanes_supported(
+                problem.m, problem.n, problem.k, int(weight.metadata.group_size))):
+        entry = _decode_entry(weight)
+        if entry is not None:
+            from .ops.w4a16 import bind_w4a16_decode
+
+            # one bound callable per (rows, dtype) and bias tensor; the bias is a weak key too
+            slot = entry["bound"].setdefault((problem.m, activation.dtype), {"plain": None, "biased": weakref.WeakKeyDictionary()})
+            if bias is None:
+                run = slot["plain"]
+            else:
+                hit = slot["biased"].get(bias)
+                run = hit[1] if hit is not None and hit[0] == bias._version else None
+            if run is None:
+                run = bind_w4a16_decode(entry["tiled"], rows=problem.m, dtype=activation.dtype, bias=bias)
+                if bias is None:
+                    slot["plain"] = run
+                else:
+                    slot["biased"][bias] = (bias._version, run)
+            return run(activation.contiguous(), output, None if residual is None else residual.contiguous())
     scales, zeros = weight.scales, weight.zero_points
     if zeros is not None and zeros.dtype != scales.dtype:
         zeros = zeros.to(scales.dtype)
