@@ -149,7 +149,9 @@ int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, co
  *   lane_weights  uint8 [ceil(N/128)][K/128][4 warps][2 row tiles][2 halves][32 lanes][16]   (prepack.py: lanes_w4)
  *                 unsigned codes; two's-complement nibbles are stored as code + 8 and announced by
  *                 nibble_signed = 1
- *   lane_params   param_dtype [ceil(N/128)][K/128][128/group_size][4 warps][8][4][2] = (scale, zero point)
+ *   lane_scales   param_dtype [ceil(N/128)][K/128][128/group_size][4 warps][8][4]: the scales of the four
+ *                 channels 32w + 16t + 8h + r (index 2t + h) a lane's accumulators belong to
+ *   lane_zeros    zero points in the same order, or NULL for symmetric weights
  *   group_size in {64, 128}; K a multiple of 128; 1 <= M <= 16; any zero point (integer or not).
  *   output        [M, N] act_dtype, or fp32 (out_dtype = XQT_B200_FP32: unrounded partial sums of a
  *                 K-sharded layer, then no residual)
@@ -165,8 +167,8 @@ int xqt_b200_w4a16_decode_lanes_supported(int m, int n, int k, int group_size);
  * (awq_w4a16_sm89_kernel.cu:26-60). */
 int xqt_b200_w4a16_decode_lanes_plan(int m, int n, int k, int group_size, int* warp_quads, int* cluster);
 int xqt_b200_w4a16_decode_lanes_set_plan(int warp_quads, int cluster);
-int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights, const void* lane_params,
-                                const float* bias, const void* residual, void* output, int m, int n, int k,
+int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights, const void* lane_scales,
+                                const void* lane_zeros, const float* bias, const void* residual, void* output, int m, int n, int k,
                                 int group_size, int nibble_signed, int act_dtype, int param_dtype,
                                 int out_dtype, unsigned int* status, xqt_b200_stream_t stream);
 

@@ -99,7 +99,8 @@ def test_registry_conflicts_and_replace():
         reg.replace(replace(b200_rows()[0], name="unknown_row"))
     with pytest.raises(ValueError):
         replace(b200_rows()[0], maturity="executable")             # executable needs an executor
-    assert [e.name for e in reg.matching(_spec().problem, _spec().quant, _spec().epilogue)] == [B200_W4A16]
+    # the SVD dual-path row serves the same request shape (it needs a low-rank pair) and ranks below W4A16
+    assert [e.name for e in reg.matching(_spec().problem, _spec().quant, _spec().epilogue)] == [B200_W4A16, "sm100_svd_w4a4_b200"]
     other_arch = GemmProblem(m=4, n=8, k=256, sm=89)
     assert reg.matching(other_arch, _spec().quant, _spec().epilogue) == ()
 
@@ -119,7 +120,7 @@ def test_dispatch_runs_fake_executor_and_reports():
     assert result.report.native and result.report.selected_kernel == B200_W4A16
     assert result.report.shape_variant == "gemv_m_le_16" and result.report.group_size == 128
     assert calls[0]["variant"] == "gemv" and float(result.output[0, 0]) == 7.0
-    assert result.report.to_dict()["fallback_chain"] == [B200_W4A16]
+    assert result.report.to_dict()["fallback_chain"] == [B200_W4A16, "sm100_svd_w4a4_b200"]
 
 
 def test_dispatch_without_executable_row_raises_and_never_falls_back_to_cpu():
@@ -204,3 +205,102 @@ def test_w8a8_executor_validates_before_touching_the_gpu():
         b200_w8a8_executor(x, w, spec=_w8a8_spec(), weight_scales=ws, weight_zero_points=torch.zeros(8))
     with pytest.raises(XQTBackendError, match="bias only"):
         b200_w8a8_executor(x, w, spec=_w8a8_spec(), weight_scales=ws, residual=torch.zeros((4, 8)))
+
+
+def test_svd_contract_and_executor_reject_what_they_cannot_serve():
+    from xqt_b200.executors import SVDGemmContract, b200_svd_w4a4_executor
+
+    spec = _spec()
+    with pytest.raises(ValueError):
+        SVDGemmContract(main_spec=spec, rank=0)
+    with pytest.raises(ValueError):
+        SVDGemmContract(main_spec=spec, rank=4, fusion_boundary="somewhere")
+    with pytest.raises(ValueError):
+        SVDGemmContract(main_spec=spec, rank=4, outlier_channels=(1, 1))
+    contract = SVDGemmContract(main_spec=spec, rank=4, fusion_boundary="fuse_up")
+    assert contract.to_dict()["fusion_boundary"] == "fuse_up" and contract.to_dict()["rank"] == 4
+    pw = quantize.quantize_w4_asymmetric(torch.randn((8, 256), generator=seeded(1)), group_size=128)
+    x = torch.zeros((4, 256), dtype=torch.bfloat16)
+    with pytest.raises(XQTBackendError, match="low_rank_down"):
+        b200_svd_w4a4_executor(x, pw, spec=spec)                       # a plain W4A16 request: next candidate
+    with pytest.raises(XQTBackendError, match="symmetric signed residual"):
+        b200_svd_w4a4_executor(x, pw, spec=spec, low_rank_down=torch.zeros((4, 256)), low_rank_up=torch.zeros((8, 4)))
+
+
+def test_reference_named_ops_resolve_through_the_kernel_namespace():
+    from xqt_b200 import kernel_spec
+    from xqt_b200.ops import awq, w4a4, w8a8
+
+    platform = kernel_spec.PlatformInfo("cuda", 10, 0)
+    assert kernel_spec.select_kernel("quantization.awq_w4a16_decode", platform=platform).load() is awq.awq_w4a16_decode
+    assert kernel_spec.select_kernel("quantization.convrot_w8a8_linear", platform=platform).load() is w8a8.convrot_w8a8_linear
+    assert kernel_spec.select_kernel("quantization.svdq_w4a4_linear", platform=platform).load() is w4a4.svdq_w4a4_linear
+    assert not kernel_spec.select_kernel("quantization.awq_w4a16_decode", platform=platform).is_available(
+        kernel_spec.PlatformInfo("cuda", 8, 9))
+    # argument names and order of xqt's ops (awq_w4a16_sm89.py:152-302, convrot_w8a8_sm89.py:365-448,
+    # svdq_w4a4_sm89.py:471-479,963-969,1203-1270)
+    import inspect
+
+    assert list(inspect.signature(awq.awq_w4a16_decode).parameters) == ["inputs", "qweight", "scales", "scaled_zeros", "output"]
+    assert list(inspect.signature(awq.bind_awq_w4a16_decode).parameters) == [
+        "qweight", "scales", "scaled_zeros", "rows", "input_features", "output_features", "dtype", "device", "bias"]
+    assert list(inspect.signature(w8a8.convrot_w8a8_linear).parameters)[:5] == [
+        "inputs", "packed", "rotated_input_features", "rot_size", "workspace"]
+    assert list(inspect.signature(w8a8.bind_convrot_w8a8_linear).parameters)[:5] == [
+        "packed", "workspace", "rows", "rotated_input_features", "rot_size"]
+    assert list(inspect.signature(w4a4.pack_svdq_w4a4_linear).parameters)[:6] == [
+        "residual_weight", "down_weight", "up_weight", "bias", "smooth", "norm_weight"]
+    assert list(inspect.signature(w4a4.allocate_w4a4_workspace).parameters) == ["rows", "packed", "with_lora_rank", "with_row_scales"]
+    assert list(inspect.signature(w4a4.bind_svdq_w4a4_linear).parameters) == ["packed", "workspace", "rows", "lora_scale"]
+    with pytest.raises(XQTBackendError):
+        w4a4.pack_svdq_w4a4_linear(torch.zeros((8, 128)), None, None, smooth=torch.ones(128))
+
+
+def test_install_into_the_reference_registry_and_dispatch_with_its_own_dispatcher():
+    """With an xqt checkout importable (``XQT_REFERENCE_PATH`` or an installed package): the B200 rows go
+    into xqt's own default registry as xqt's own row class, and xqt's ``dispatch_gemm`` reaches a (fake)
+    executor swapped into the B200 row when asked for ``GemmProblem(sm=100)``."""
+
+    import os
+    import sys
+
+    path = os.environ.get("XQT_REFERENCE_PATH")
+    if path and path not in sys.path:
+        sys.path.insert(0, path)
+    xreg = pytest.importorskip("xqt.kernels.ops.gemm.registry")
+    from xqt.kernels.ops.gemm import contracts as xc
+    from xqt.kernels.ops.gemm import dispatch as xd
+    from xqt.kernels.ops.gemm import layout as xl
+
+    from xqt_b200.executors import install_b200_executors
+
+    registry = xreg.default_registry()
+    promoted = install_b200_executors(registry, require_native=False) or ()
+    from xqt_b200 import native
+
+    if not native.available():
+        pytest.skip("the shared library is not built here")
+    assert B200_W4A16 in promoted
+    row = registry.get(B200_W4A16)
+    assert type(row) is xreg.GemmKernelRegistration and row.executable
+    calls = []
+
+    def fake(activation, weight, *, spec, **kwargs):
+        calls.append((type(weight).__module__, spec.problem.arch))
+        return torch.full((spec.problem.m, spec.problem.n), 3.0, dtype=torch.bfloat16)
+
+    registry.replace(replace(row, executor=fake))
+    try:
+        codes = torch.randint(0, 16, (8, 256), generator=seeded(2), dtype=torch.int64).to(torch.uint8)
+        quant = xc.QuantSpec(weight_dtype="int4", activation_dtype="bf16", output_dtype="bf16", weight_granularity="groupwise",
+                             group_size=128, symmetric=False, weight_zero_point=True, weight_scale_source="weight_offline",
+                             storage_layout="xqt_int4_nk_v1")
+        weight = xl.build_packed_weight(xl.pack_int4_unsigned(codes), logical_shape=(8, 256), spec=quant,
+                                        scales=torch.ones((8, 2)), zero_points=torch.full((8, 2), 8.0), padded_k=256)
+        spec = xc.GemmSpec(problem=xc.GemmProblem(m=4, n=8, k=256, sm=100), quant=quant,
+                           epilogue=xc.EpilogueSpec(output_dtype="bf16"))
+        result = xd.dispatch_gemm(torch.zeros((4, 256), dtype=torch.bfloat16), weight, spec=spec, registry=registry)
+        assert result.report.selected_kernel == B200_W4A16 and float(result.output[0, 0]) == 3.0
+        assert calls == [("xqt.kernels.ops.gemm.contracts", "sm_100")]
+    finally:
+        registry.replace(row)

@@ -54,7 +54,7 @@ def test_lanes_w4_round_trip(n, k, group, symmetric):
     tiled = prepack.lanes_w4(pw.qweight, pw.scales, pw.zero_points, group_size=group, nibble_signed=symmetric)
     assert tiled.layout == "lanes"
     assert tuple(tiled.weights.shape) == (-(-n // 128), k // 128, 4, 2, 2, 32, 16)
-    assert tuple(tiled.params.shape) == (-(-n // 128), k // 128, 128 // group, 4, 8, 4, 2)
+    assert tuple(tiled.params.shape) == (1 if symmetric else 2, -(-n // 128), k // 128, 128 // group, 4, 8, 4)
     assert tiled.nbytes == tiled.weights.numel() + tiled.params.numel() * tiled.params.element_size()
     q, s, z = prepack.untile_w4(tiled)
     assert torch.equal(q, pw.qweight) and torch.equal(s, pw.scales)
@@ -102,5 +102,5 @@ def test_lanes_w4_fragment_semantics():
     t2 = prepack.lanes_w4(qweight, s2, s2 + 0.5, group_size=128, nibble_signed=False)
     for (kb, w, r, t, h) in [(0, 0, 0, 0, 0), (1, 3, 7, 1, 1), (1, 2, 5, 0, 1)]:
         ch = 32 * w + 16 * t + 8 * h + r
-        assert float(t2.params[0, kb, 0, w, r, 2 * t + h, 0]) == float(s2[ch, kb])
-        assert float(t2.params[0, kb, 0, w, r, 2 * t + h, 1]) == float(s2[ch, kb]) + 0.5
+        assert float(t2.params[0, 0, kb, 0, w, r, 2 * t + h]) == float(s2[ch, kb])
+        assert float(t2.params[1, 0, kb, 0, w, r, 2 * t + h]) == float(s2[ch, kb]) + 0.5

@@ -20,8 +20,8 @@ int w4a16_decode_tc_launch(const void*, const void*, const void*, const float*, 
                            int, int, int, int, void*, size_t, cudaStream_t);
 size_t w4a16_decode_tc_workspace_bytes();
 bool w4a16_decode_tc_supported(int m, int n, int k, int group_size);
-int w4a16_decode_cl_launch(const void*, const void*, const void*, const float*, const void*, void*, int, int, int, int,
-                           int, int, int, int, unsigned int*, cudaStream_t);
+int w4a16_decode_cl_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int, int,
+                           int, int, int, int, int, unsigned int*, cudaStream_t);
 bool w4a16_decode_cl_supported(int m, int n, int k, int group_size);
 void w4a16_decode_cl_set_plan(int kw, int s);
 void w4a16_decode_cl_get_plan(int m, int n, int k, int* kw, int* s);
@@ -196,17 +196,17 @@ int xqt_b200_w4a16_decode_lanes_set_plan(int warp_quads, int cluster) {
   return 0;
 }
 
-int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights, const void* lane_params,
-                                const float* bias, const void* residual, void* output, int m, int n, int k,
+int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights, const void* lane_scales,
+                                const void* lane_zeros, const float* bias, const void* residual, void* output, int m, int n, int k,
                                 int group_size, int nibble_signed, int act_dtype, int param_dtype, int out_dtype,
                                 unsigned int* status, xqt_b200_stream_t stream) {
   XQT_REQUIRE(m >= 0 && n > 0 && k > 0);
   XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
   XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
   if (m == 0) return 0;
-  XQT_REQUIRE(activation != nullptr && lane_weights != nullptr && lane_params != nullptr && output != nullptr);
+  XQT_REQUIRE(activation != nullptr && lane_weights != nullptr && lane_scales != nullptr && output != nullptr);
   XQT_REQUIRE(out_dtype == act_dtype || out_dtype == XQT_B200_FP32);
-  return w4a16_decode_cl_launch(activation, lane_weights, lane_params, bias, residual, output, m, n, k, group_size,
+  return w4a16_decode_cl_launch(activation, lane_weights, lane_scales, lane_zeros, bias, residual, output, m, n, k, group_size,
                                 nibble_signed, act_dtype, param_dtype, out_dtype == XQT_B200_FP32 ? 1 : 0, status,
                                 (cudaStream_t)stream);
 }

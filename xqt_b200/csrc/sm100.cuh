@@ -149,6 +149,11 @@ __device__ __forceinline__ void ldg128_stream(uint32_t (&r)[4], const void* p) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "l"(p));
 }
+__device__ __forceinline__ uint32_t ldg32_stream(const void* p) {
+  uint32_t r;
+  asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];\n" : "=r"(r) : "l"(p));
+  return r;
+}
 __device__ __forceinline__ void ldg64_stream(uint32_t (&r)[2], const void* p) {
   asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "l"(p));
 }

@@ -63,7 +63,8 @@ enum Status : unsigned int { kTimeout = 64 };
 
 struct DecodeClParams {
   const uint8_t* wt;    // [tiles][kblocks][4 warps][2 A tiles][32 lanes][32 B]
-  const uint8_t* prm;   // [tiles][kblocks][128/g][4 warps][8 rows][4 pairs][2] P
+  const uint8_t* scl;   // scales      [tiles][kblocks][128/g][4 warps][8 rows][4] P
+  const uint8_t* zer;   // zero points, same shape, or null (symmetric weights)
   const void* x;        // [M][K]
   const float* bias;
   const void* residual;
@@ -129,19 +130,17 @@ __device__ __forceinline__ void cl_sts128z(uint32_t addr) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(addr), "r"(0u) : "memory");
 }
 
-// (scale, zero point) of a 16-bit pair packed in one register
+// element `hi` (0 or 1) of two 16-bit parameters packed in one register
 template <typename P>
-__device__ __forceinline__ void unpack_pair(uint32_t v, float& s, float& z);
+__device__ __forceinline__ float unpack_half(uint32_t v, int hi);
 template <>
-__device__ __forceinline__ void unpack_pair<__nv_bfloat16>(uint32_t v, float& s, float& z) {
-  s = __uint_as_float(v << 16);
-  z = __uint_as_float(v & 0xffff0000u);
+__device__ __forceinline__ float unpack_half<__nv_bfloat16>(uint32_t v, int hi) {
+  return __uint_as_float(hi ? (v & 0xffff0000u) : (v << 16));
 }
 template <>
-__device__ __forceinline__ void unpack_pair<__half>(uint32_t v, float& s, float& z) {
-  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
-  s = f.x;
-  z = f.y;
+__device__ __forceinline__ float unpack_half<__half>(uint32_t v, int hi) {
+  const __half2 h = *reinterpret_cast<const __half2*>(&v);
+  return hi ? __high2float(h) : __low2float(h);
 }
 
 // T: activation / output type; P: type of the stored (scale, zero point) pairs; GK: quantisation
@@ -156,7 +155,7 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   constexpr int MP = 8 * NT;              // token rows held in shared memory
   constexpr bool P32 = sizeof(P) == 4;
   constexpr int PR = P32 ? 2 : 4;         // parameter registers per (slot, group)
-  constexpr int kPrmBlockBytes = SUB * 256 * (int)sizeof(P);
+  constexpr int kPrmBlockBytes = SUB * 128 * (int)sizeof(P);   // scales (or zero points) of one tile and 128-K block
 
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t smem_s = smem_addr(smem);
@@ -181,8 +180,11 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   const int nkb = kb1 - kb0;
 
   const uint8_t* wp = p.wt + (((size_t)tile * p.kblocks + kb0) * 4 + w) * 2048 + lane * 16;   // next block to request
-  const uint8_t* pp = p.prm + ((size_t)tile * p.kblocks + kb0) * kPrmBlockBytes +
-                      (P32 ? ((w * 8 + r) * 4 + c) * 8 : (w * 8 + r) * 16);
+  // a lane's four channels (32w + 16t + 8h + r, index 2t + h) are adjacent: one 8-byte load of 16-bit
+  // parameters; with fp32 parameters lane c loads entry c and the quad exchanges them by shuffle
+  const size_t poff = ((size_t)tile * p.kblocks + kb0) * kPrmBlockBytes + (P32 ? ((w * 8 + r) * 4 + c) * 4 : (w * 8 + r) * 8);
+  const uint8_t* sp = p.scl + poff;
+  const uint8_t* zp = p.zer != nullptr ? p.zer + poff : nullptr;
 
   // register ring of four 64-K half blocks: [slot][row tile][word of K-step]; slot parity = half.
   // Parameters travel with the second half of their block (group 128: one set per block, two sets
@@ -195,16 +197,22 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
     constexpr int half = slot & 1;
     ldg128_stream(wq[slot][0], wp + half * 512);
     ldg128_stream(wq[slot][1], wp + 1024 + half * 512);
-    if constexpr (GK == 64) {
-      if constexpr (P32) ldg64_stream(pr[slot], pp + half * 1024);
-      else ldg128_stream(pr[slot], pp + half * 512);
-    } else if constexpr (half == 1) {
-      if constexpr (P32) ldg64_stream(pr[slot >> 1], pp);
-      else ldg128_stream(pr[slot >> 1], pp);
+    if constexpr (GK == 64 || half == 1) {
+      constexpr int set = GK == 64 ? slot : (slot >> 1);
+      constexpr int sub_off = GK == 64 ? half * (kPrmBlockBytes / 2) : 0;
+      if constexpr (P32) {
+        pr[set][0] = ldg32_stream(sp + sub_off);
+        pr[set][1] = zp != nullptr ? ldg32_stream(zp + sub_off) : 0u;
+      } else {
+        ldg64_stream(*reinterpret_cast<uint32_t(*)[2]>(&pr[set][0]), sp + sub_off);
+        if (zp != nullptr) ldg64_stream(*reinterpret_cast<uint32_t(*)[2]>(&pr[set][2]), zp + sub_off);
+        else pr[set][2] = pr[set][3] = 0u;
+      }
     }
     if constexpr (half == 1) {
       wp += 8192;
-      pp += kPrmBlockBytes;
+      sp += kPrmBlockBytes;
+      if (zp != nullptr) zp += kPrmBlockBytes;
     }
   };
   using I0 = std::integral_constant<int, 0>;
@@ -224,7 +232,9 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
   // flight from HBM from the first microsecond and the register ring only has to cover L2 latency
   for (int i = 1 + lane; i < nkb && p.prefetch; i += 32) {
     bulk_prefetch_l2(p.wt + (((size_t)tile * p.kblocks + kb0 + i) * 4 + w) * 2048, 2048);
-    bulk_prefetch_l2(p.prm + ((size_t)tile * p.kblocks + kb0 + i) * kPrmBlockBytes + w * (kPrmBlockBytes / 4), kPrmBlockBytes / 4);
+    bulk_prefetch_l2(p.scl + ((size_t)tile * p.kblocks + kb0 + i) * kPrmBlockBytes + w * (kPrmBlockBytes / 4), kPrmBlockBytes / 4);
+    if (p.zer != nullptr)
+      bulk_prefetch_l2(p.zer + ((size_t)tile * p.kblocks + kb0 + i) * kPrmBlockBytes + w * (kPrmBlockBytes / 4), kPrmBlockBytes / 4);
   }
 
   if (tid == 0) {
@@ -351,7 +361,8 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
             sc = __uint_as_float(__shfl_sync(0xffffffffu, pr[set][0], from));
             z = __uint_as_float(__shfl_sync(0xffffffffu, pr[set][1], from));
           } else {
-            unpack_pair<P>(pr[set][t * 2 + h], sc, z);
+            sc = unpack_half<P>(pr[set][t], h);
+            z = unpack_half<P>(pr[set][2 + t], h);
           }
           const float nzb = -(z + base_off);
 #pragma unroll
@@ -590,18 +601,18 @@ static int dcl_dispatch(const DecodeClParams& p, int group_size, int nt, int gri
                  : dcl_launch<T, P, 64, 2>(p, grid, threads, cluster, smem, stream);
 }
 
-int w4a16_decode_cl_launch(const void* x, const void* wt, const void* prm, const float* bias, const void* residual,
+int w4a16_decode_cl_launch(const void* x, const void* wt, const void* scl, const void* zer, const float* bias, const void* residual,
                            void* out, int m, int n, int k, int group_size, int nibble_signed, int act_dtype,
                            int param_dtype, int out_f32, unsigned int* status, cudaStream_t stream) {
   using namespace dcl;
   XQT_REQUIRE(w4a16_decode_cl_supported(m, n, k, group_size));
-  XQT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)wt & 31) == 0 && ((uintptr_t)prm & 15) == 0);
+  XQT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)wt & 31) == 0 && ((uintptr_t)scl & 15) == 0 && ((uintptr_t)zer & 15) == 0);
   XQT_REQUIRE(!out_f32 || residual == nullptr);
   const int tiles = ceil_div(n, kTileRows), kblocks = k / kKB;
   const int nt = m > 8 ? 2 : 1, mp = 8 * nt, sub = kKB / group_size;
   const ClPlan plan = cl_plan(tiles, kblocks, m);
   DecodeClParams p;
-  p.wt = (const uint8_t*)wt; p.prm = (const uint8_t*)prm; p.x = x; p.bias = bias; p.residual = residual; p.out = out;
+  p.wt = (const uint8_t*)wt; p.scl = (const uint8_t*)scl; p.zer = (const uint8_t*)zer; p.x = x; p.bias = bias; p.residual = residual; p.out = out;
   p.status = status;
   p.m = m; p.n = n; p.k = k; p.out_f32 = out_f32;
   p.kblocks = kblocks; p.kw = plan.kw; p.pieces = plan.kw * plan.s;

@@ -14,15 +14,18 @@ xqt's ``GemmKernelRegistry`` (anything with ``register/replace/get``).
 from __future__ import annotations
 
 import os
-import weakref
+from dataclasses import dataclass
+from dataclasses import fields as _dc_fields
 from dataclasses import replace as _dc_replace
+from typing import Any
 
 import torch
 
 from . import native
 from .errors import XQTBackendError
 from .layout import validate_w4a16_packed_weight
-from .registry import B200_W4A16, B200_W8A8, GemmKernelRegistry, b200_rows
+from .weakid import WeakIdDict
+from .registry import B200_SVD_W4A4, B200_W4A16, B200_W8A8, GemmKernelRegistry, b200_rows
 
 _TORCH = {"fp16": torch.float16, "bf16": torch.bfloat16}
 
@@ -41,7 +44,7 @@ def _require_b200(device: torch.device) -> None:
 # tensor object itself (weakly: the entry dies with the weight, so a recycled address can never hit a
 # stale layout) and checked against the tensor's version counter, the way xqt's runtime modules key
 # their prepacked W4A4 state on data_ptr/_version (xqt/runtime/modules/composite_add_w4a4.py:164-187).
-_decode_layouts: "weakref.WeakKeyDictionary[torch.Tensor, dict]" = weakref.WeakKeyDictionary()
+_decode_layouts = WeakIdDict()
 
 
 def _decode_entry(weight) -> dict | None:
@@ -117,7 +120,7 @@ def b200_w4a16_executor(activation, weight, *, spec, weight_scales=None, activat
             from .ops.w4a16 import bind_w4a16_decode
 
             # one bound callable per (rows, dtype) and bias tensor; the bias is a weak key too
-            slot = entry["bound"].setdefault((problem.m, activation.dtype), {"plain": None, "biased": weakref.WeakKeyDictionary()})
+            slot = entry["bound"].setdefault((problem.m, activation.dtype), {"plain": None, "biased": WeakIdDict()})
             if bias is None:
                 run = slot["plain"]
             else:
@@ -198,7 +201,130 @@ def b200_w8a8_executor(activation, weight, *, spec, weight_scales=None, activati
     return w8a8_gemm(codes, a_scale, packed, output)
 
 
-_EXECUTORS = {B200_W4A16: b200_w4a16_executor, B200_W8A8: b200_w8a8_executor}
+@dataclass(frozen=True, slots=True)
+class SVDGemmContract:
+    """GEMM-side description of "quantised main + low-rank correction" (fields and checks of xqt's
+    ``SVDGemmContract``, xqt/kernels/ops/gemm/p4.py:612-640).  ``fusion_boundary`` says where a backend
+    may merge the low-rank branch into the main GEMM; the B200 kernel computes the down projection in
+    its own pass and fuses the up projection into the epilogue, i.e. it implements ``fuse_up`` and
+    accepts the other two values as requests it over-satisfies."""
+
+    main_spec: Any
+    rank: int
+    outlier_channels: tuple[int, ...] = ()
+    fusion_boundary: str = "separate_gemm"
+    outlier_mode: str = "correction"
+
+    def __post_init__(self) -> None:
+        if int(self.rank) < 1:
+            raise ValueError("SVD rank must be positive")
+        if self.fusion_boundary not in ("separate_gemm", "fuse_down", "fuse_up"):
+            raise ValueError("unsupported SVD fusion_boundary")
+        if self.outlier_mode not in ("correction", "replacement"):
+            raise ValueError("unsupported SVD outlier_mode")
+        channels = tuple(int(c) for c in self.outlier_channels)
+        k = int(self.main_spec.problem.k)
+        if len(set(channels)) != len(channels) or any(not 0 <= c < k for c in channels):
+            raise ValueError("SVD outlier_channels must be unique valid K indices")
+        object.__setattr__(self, "outlier_channels", channels)
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"main_spec": self.main_spec.to_dict(), "rank": int(self.rank), "outlier_channels": list(self.outlier_channels),
+                "fusion_boundary": self.fusion_boundary, "outlier_mode": self.outlier_mode}
+
+
+_svd_layers = WeakIdDict()      # residual qweight tensor -> (identity of the other tensors, packed layer)
+
+
+def b200_svd_w4a4_executor(activation, weight, *, spec, weight_scales=None, activation_scales=None,
+                           weight_zero_points=None, activation_zero_points=None, bias=None, residual=None,
+                           low_rank_down: torch.Tensor | None = None, low_rank_up: torch.Tensor | None = None,
+                           contract: SVDGemmContract | None = None, rotation=None,
+                           output: torch.Tensor | None = None) -> torch.Tensor:
+    """SVDQuant dual path behind the GEMM registry: ``weight`` is the int4 residual as a canonical signed
+    ``xqt_int4_nk_v1`` PackedWeight with group-64 scales (the composite artifact's ``packed_residual`` /
+    ``residual_scale``, xqt/contracts/composite.py:92-227), ``low_rank_down [r,K]`` / ``low_rank_up [N,r]``
+    the rank-r pair.  The activation (fp16 / bf16, already rotated unless ``rotation`` is given) is
+    quantised to int4 per (token, 64-K) inside the call, as xqt's native W4A4 path does
+    (xqt/kernels/ops/_impl/cute/svdq_w4a4_sm89.py:1203-1262); the sum is what ``reference_svd_dual_path``
+    computes (p4.py:687-767) up to that activation rounding."""
+
+    from .ops.w4a4 import GROUP, pack_svdq_w4a4_linear, svdq_w4a4_linear
+
+    if low_rank_down is None or low_rank_up is None:
+        raise XQTBackendError("B200 SVD W4A4 needs low_rank_down [r,K] and low_rank_up [N,r]")
+    if not hasattr(weight, "metadata"):
+        raise XQTBackendError("B200 SVD W4A4 requires the residual as a canonical PackedWeight")
+    quant, problem, meta = spec.quant, spec.problem, weight.metadata
+    if quant.weight_dtype != "int4" or quant.activation_dtype not in _TORCH or quant.output_dtype != quant.activation_dtype:
+        raise XQTBackendError("B200 SVD W4A4 serves int4 weights with fp16/bf16 activations and outputs")
+    if not meta.nibble_signed or int(meta.group_size) != GROUP or weight.zero_points is not None:
+        raise XQTBackendError("B200 SVD W4A4 needs a symmetric signed residual with group size 64")
+    if activation_scales is not None or activation_zero_points is not None or weight_zero_points is not None:
+        raise XQTBackendError("B200 SVD W4A4 quantises activations itself and takes no zero points")
+    if residual is not None or spec.epilogue.has_residual or spec.epilogue.activation != "none":
+        raise XQTBackendError("B200 SVD W4A4 epilogue supports bias only")
+    if not isinstance(activation, torch.Tensor) or activation.ndim != 2 or not activation.is_cuda:
+        raise XQTBackendError("B200 SVD W4A4 activation must be CUDA rank-2")
+    _require_b200(activation.device)
+    if activation.dtype != _TORCH[quant.activation_dtype] or tuple(activation.shape) != (problem.m, problem.k):
+        raise XQTBackendError("B200 SVD W4A4 activation does not match the GemmProblem / QuantSpec")
+    rank = int(low_rank_down.shape[0])
+    if tuple(low_rank_down.shape) != (rank, problem.k) or tuple(low_rank_up.shape) != (problem.n, rank):
+        raise XQTBackendError("low_rank_down must be [rank,K] and low_rank_up [N,rank]")
+    if contract is not None:
+        if int(contract.rank) != rank:
+            raise XQTBackendError("SVDGemmContract.rank disagrees with the low-rank factors")
+        if contract.outlier_channels:
+            raise XQTBackendError("B200 SVD W4A4 does not serve outlier-channel corrections")
+    scales = weight.scales if weight_scales is None else weight_scales
+    if scales is None or tuple(scales.shape) != (problem.n, problem.k // GROUP):
+        raise XQTBackendError("B200 SVD W4A4 needs residual scales [N, K/64]")
+    identity = (id(scales), scales._version, id(low_rank_down), low_rank_down._version, id(low_rank_up),
+                low_rank_up._version, None if bias is None else (id(bias), bias._version), activation.dtype, id(rotation))
+    hit = _svd_layers.get(weight.qweight)
+    if hit is None or hit[0] != identity or hit[2] != weight.qweight._version:
+        try:
+            layer = pack_svdq_w4a4_linear(None, low_rank_down, low_rank_up, bias, packed_residual=weight.qweight,
+                                          residual_scale=scales, dtype=activation.dtype, rotation=rotation,
+                                          device=activation.device)
+        except (TypeError, ValueError) as exc:
+            raise XQTBackendError(f"B200 SVD W4A4 packing rejected: {exc}") from exc
+        hit = (identity, layer, weight.qweight._version, (scales, low_rank_down, low_rank_up, bias))   # keeps the ids alive
+        _svd_layers[weight.qweight] = hit
+    result = svdq_w4a4_linear(activation.contiguous(), hit[1])
+    if output is not None:
+        output.copy_(result)
+        return output
+    return result
+
+
+_EXECUTORS = {B200_W4A16: b200_w4a16_executor, B200_W8A8: b200_w8a8_executor, B200_SVD_W4A4: b200_svd_w4a4_executor}
+
+
+def _rows_for(registry) -> tuple:
+    """The B200 rows as instances of the row class the target registry already holds (xqt's own
+    ``GemmKernelRegistration`` / ``GemmCapability`` when installing into xqt's table), else ours."""
+
+    rows = b200_rows()
+    try:
+        sample = next(iter(registry.entries()))
+    except (StopIteration, AttributeError, TypeError):
+        return rows
+    row_cls, cap_cls = type(sample), type(sample.capability)
+    if row_cls is type(rows[0]):
+        return rows
+    row_fields, cap_fields = set(_field_names(row_cls)), set(_field_names(cap_cls))
+    converted = []
+    for row in rows:
+        cap = cap_cls(**{f: getattr(row.capability, f) for f in _field_names(type(row.capability)) if f in cap_fields})
+        values = {f: getattr(row, f) for f in _field_names(type(row)) if f in row_fields and f != "capability"}
+        converted.append(row_cls(capability=cap, **values))
+    return tuple(converted)
+
+
+def _field_names(cls) -> tuple[str, ...]:
+    return tuple(f.name for f in _dc_fields(cls))
 
 
 def install_b200_executors(registry: GemmKernelRegistry | None = None, *, require_native: bool = True) -> tuple[str, ...]:
@@ -216,7 +342,7 @@ def install_b200_executors(registry: GemmKernelRegistry | None = None, *, requir
     elif not native.available():
         return ()
     promoted = []
-    for row in b200_rows():
+    for row in _rows_for(registry):
         try:
             registry.get(row.name)
         except KeyError:
@@ -229,4 +355,4 @@ def install_b200_executors(registry: GemmKernelRegistry | None = None, *, requir
     return tuple(promoted)
 
 
-__all__ = ["b200_w4a16_executor", "b200_w8a8_executor", "install_b200_executors"]
+__all__ = ["SVDGemmContract", "b200_svd_w4a4_executor", "b200_w4a16_executor", "b200_w8a8_executor", "install_b200_executors"]

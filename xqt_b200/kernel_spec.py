@@ -185,8 +185,10 @@ def get_kernel(op: str, backend: Optional[KernelBackend] = None) -> Callable[...
 SM100 = frozenset({CapabilityRequirement.cuda(min_sm=(10, 0), max_sm=(10, 0))})
 
 B200_KERNELS = (
-    KernelSpec("quantization.awq_w4a16_decode", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.w4a16:w4a16_decode_tiled", SM100,
-               "W4A16 decode (M<=16): tcgen05 / mma.sync persistent stream-K kernels"),
+    KernelSpec("quantization.awq_w4a16_decode", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.awq:awq_w4a16_decode", SM100,
+               "AWQ W4A16 decode (M<=16), xqt's signature: cluster split-K kernel on the lane-ordered layout"),
+    KernelSpec("quantization.w4a16_decode_tiled", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.w4a16:w4a16_decode_tiled", SM100,
+               "W4A16 decode (M<=16) on a TiledW4 execution layout (lanes / rows128 / tile128)"),
     KernelSpec("quantization.w4a16_linear", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.w4a16:w4a16_linear", SM100,
                "W4A16 linear on canonical xqt_int4_nk_v1 tensors, any M"),
     KernelSpec("quantization.convrot_w8a8_linear", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.w8a8:convrot_w8a8_linear", SM100,

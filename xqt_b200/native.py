@@ -47,7 +47,7 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_decode_lanes_supported": (_I, [_I] * 4),
     "xqt_b200_w4a16_decode_lanes_plan": (_I, [_I] * 4 + [ctypes.POINTER(_I), ctypes.POINTER(_I)]),
     "xqt_b200_w4a16_decode_lanes_set_plan": (_I, [_I, _I]),
-    "xqt_b200_w4a16_decode_lanes": (_I, [_P] * 6 + [_I] * 8 + [_P, _P]),
+    "xqt_b200_w4a16_decode_lanes": (_I, [_P] * 7 + [_I] * 8 + [_P, _P]),
     "xqt_b200_w4a16_decode_tiled_static": (_I, [_P] * 6 + [_I] * 8 + [_P]),
     "xqt_b200_w4a16_decode_static_scratch_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_static_max_n": (_I, []),

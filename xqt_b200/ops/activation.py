@@ -22,8 +22,11 @@ def _column_scale(rotation: Rotation, device: torch.device) -> torch.Tensor:
 
 
 def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, group_size: int = 64,
-                    return_rotated: bool = False):
-    """-> (codes int8 ``[M,K]``, scales fp32 ``[M]`` (bits=8) or ``[M, K/group]`` (bits=4)[, rotated x])."""
+                    return_rotated: bool = False, out: tuple | None = None):
+    """-> (codes int8 ``[M,K]``, scales fp32 ``[M]`` (bits=8) or ``[M, K/group]`` (bits=4)[, rotated x]).
+
+    ``out = (codes, scales[, rotated])`` supplies preallocated buffers whose leading ``M`` rows are
+    written (a workspace sized for at least M rows): the call then allocates nothing."""
 
     if x.ndim != 2 or x.dtype not in (torch.float16, torch.bfloat16) or not x.is_cuda:
         raise XQTBackendError("rotate_quantize expects a CUDA rank-2 fp16/bf16 activation")
@@ -36,9 +39,18 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
         raise XQTBackendError("the rotated dimension must be a multiple of the rotation block")
     if bits == 4 and k % group_size:
         raise XQTBackendError("K must be a multiple of the activation group size")
-    codes = torch.empty((m, k), device=device, dtype=torch.int8)
-    scales = torch.empty((m,) if bits == 8 else (m, k // group_size), device=device, dtype=torch.float32)
-    rotated = torch.empty_like(x) if return_rotated else None
+    if out is None:
+        codes = torch.empty((m, k), device=device, dtype=torch.int8)
+        scales = torch.empty((m,) if bits == 8 else (m, k // group_size), device=device, dtype=torch.float32)
+        rotated = torch.empty_like(x) if return_rotated else None
+    else:
+        codes, scales = out[0][:m], out[1][:m]
+        rotated = out[2][:m] if return_rotated else None
+        want_scales = (m,) if bits == 8 else (m, k // group_size)
+        if codes.dtype != torch.int8 or tuple(codes.shape) != (m, k) or not codes.is_contiguous() \
+                or scales.dtype != torch.float32 or tuple(scales.shape) != want_scales or not scales.is_contiguous() \
+                or (rotated is not None and (rotated.dtype != x.dtype or tuple(rotated.shape) != (m, k) or not rotated.is_contiguous())):
+            raise XQTBackendError("rotate_quantize: workspace buffers do not match the activation")
     if m:
         cs = None if rotation is None else _column_scale(rotation, device)
         with torch.cuda.device(device):

@@ -12,6 +12,7 @@ import torch
 
 from .. import native
 from ..errors import XQTBackendError
+from ..weakid import WeakIdDict
 
 
 def _check_cuda(name: str, tensor: torch.Tensor | None, device: torch.device) -> None:
@@ -23,7 +24,7 @@ def _check_cuda(name: str, tensor: torch.Tensor | None, device: torch.device) ->
         raise XQTBackendError(f"B200 W4A16 {name} must be contiguous")
 
 
-_integral_cache: dict[tuple[int, int], bool] = {}
+_integral_cache = WeakIdDict()      # zero-point tensor -> (version, answer); dies with the tensor
 
 
 def _integer_zero_points(zero_points: torch.Tensor | None) -> bool:
@@ -33,13 +34,12 @@ def _integer_zero_points(zero_points: torch.Tensor | None) -> bool:
 
     if zero_points is None:
         return True
-    key = (zero_points.data_ptr(), zero_points._version)
-    hit = _integral_cache.get(key)
-    if hit is None:
+    hit = _integral_cache.get(zero_points)
+    if hit is None or hit[0] != zero_points._version:
         z = zero_points.to(torch.float32)
-        hit = bool(((z == z.round()) & (z >= 0) & (z <= 1000)).all().item())
-        _integral_cache[key] = hit
-    return hit
+        hit = (zero_points._version, bool(((z == z.round()) & (z >= 0) & (z <= 1000)).all().item()))
+        _integral_cache[zero_points] = hit
+    return hit[1]
 
 
 def select_variant(m: int, n: int, k: int, padded_k: int, group_size: int, activation: str = "none",
@@ -279,7 +279,8 @@ def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tens
     if bias32 is not None and bias32.numel() != n:
         raise XQTBackendError("B200 W4A16 bias must have N elements")
     fn = lib.xqt_b200_w4a16_decode_lanes
-    head = (tiled.weights.data_ptr(), tiled.params.data_ptr(), native.ptr(bias32))
+    head = (tiled.weights.data_ptr(), tiled.params[0].data_ptr(),
+            tiled.params[1].data_ptr() if tiled.has_zero_point else 0, native.ptr(bias32))
     tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), native.DTYPE_CODE[dtype],
             native.DTYPE_CODE[tiled.params.dtype], native.DTYPE_CODE[odt])
     index = device.index if device.index is not None else torch.cuda.current_device()

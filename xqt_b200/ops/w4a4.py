@@ -61,6 +61,8 @@ def pack_svdq_w4a4_linear(
     up_weight: torch.Tensor | None,
     bias: torch.Tensor | None = None,
     *,
+    smooth: torch.Tensor | None = None,
+    norm_weight: torch.Tensor | None = None,
     packed_residual: torch.Tensor | None = None,
     residual_scale: torch.Tensor | None = None,
     dtype: torch.dtype = torch.bfloat16,
@@ -72,6 +74,10 @@ def pack_svdq_w4a4_linear(
     quantised with the artifact's own rule (scale = absmax/7, xqt/compression/quant/quantizers/svd.py:92-128).
     ``down_weight`` is ``[r,K]``, ``up_weight`` ``[N,r]`` (None for a layer without low-rank branch)."""
 
+    if smooth is not None or norm_weight is not None:
+        # xqt's sm_89 kernel can divide the activation by a per-channel smoothing vector and fuse an
+        # RMSNorm weight into its quantise prologue (svdq_w4a4_sm89.py:471-557); neither is served here
+        raise XQTBackendError("SVDQ W4A4 on B200 does not serve smooth / norm_weight prologues")
     if packed_residual is None:
         if residual_weight is None:
             raise XQTBackendError("pack_svdq_w4a4_linear needs residual_weight or packed_residual")
@@ -112,14 +118,81 @@ def pack_svdq_w4a4_linear(
         input_features=k, output_features=n, padded_input_features=k, rank=rank, dtype=dtype, rotation=rotation)
 
 
-def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, workspace=None, lora_scale: float = 1.0,
+@dataclass
+class W4A4Workspace:
+    """Per-call scratch of the linear (field names of xqt's, svdq_w4a4_sm89.py:399-409): activation codes
+    ``[rows, K]`` (int4 values in int8), their scales ``[rows, K/64]``, the low-rank activation
+    ``[ceil(rows/128)*128, 32]`` fp32, plus the rotated activation the low-rank branch reads."""
+
+    quantized_activation: torch.Tensor
+    activation_scales: torch.Tensor
+    lora_activation: torch.Tensor | None = None
+    row_scales: torch.Tensor | None = None
+    rotated_activation: torch.Tensor | None = None
+
+    @property
+    def padded_rows(self) -> int:
+        return int(self.quantized_activation.shape[0])
+
+
+def allocate_w4a4_workspace(rows: int, packed: PackedSVDQW4A4Linear, *, with_lora_rank: int = 0,
+                            with_row_scales: bool = False) -> W4A4Workspace:
+    """Scratch for calls of up to ``rows`` rows (cf. svdq_w4a4_sm89.py:963-1000).  ``with_lora_rank`` > 0
+    adds the buffers of the low-rank branch (any rank up to 32 uses the padded width 32)."""
+
+    if with_row_scales:
+        raise XQTBackendError("row-wise activation scales are not served by the B200 W4A4 kernels")
+    if int(with_lora_rank) > RANK_PAD:
+        raise XQTBackendError(f"SVDQ W4A4 on B200 supports rank <= {RANK_PAD}")
+    rows, k, device = int(rows), packed.padded_input_features, packed.qweight.device
+    lora = None
+    rotated = torch.empty((rows, k), dtype=packed.dtype, device=device)
+    if int(with_lora_rank) > 0:
+        lora = torch.zeros((-(-rows // TILE) * TILE, RANK_PAD), dtype=torch.float32, device=device)
+    return W4A4Workspace(
+        quantized_activation=torch.empty((rows, k), dtype=torch.int8, device=device),
+        activation_scales=torch.empty((rows, k // GROUP), dtype=torch.float32, device=device),
+        lora_activation=lora, rotated_activation=rotated)
+
+
+def native_w4a4_available(*, build: bool = False) -> bool:
+    """Whether the B200 W4A4 backend can run on the current device (cf. svdq_w4a4_sm89.py:152-168)."""
+
+    import os
+
+    if not torch.cuda.is_available() or torch.cuda.get_device_capability() != (10, 0):
+        return False
+    if os.environ.get("XQT_DISABLE_B200", "0") not in {"", "0"}:
+        return False
+    return native.available() if build else native.LIBRARY_PATH.exists()
+
+
+def native_w4a4_shape_supported(input_features: int, output_features: int) -> bool:
+    try:
+        return bool(native.library().xqt_b200_w4a4_supported(1, int(output_features), int(input_features)))
+    except Exception:  # noqa: BLE001 - a missing library means "not supported"
+        return False
+
+
+def native_convrot_w4a4_shape_supported(logical_input_features: int, rotated_input_features: int, output_features: int,
+                                        rot_size: int) -> bool:
+    size = int(rot_size)
+    return (0 < int(logical_input_features) <= int(rotated_input_features) and size >= 1 and (size & (size - 1)) == 0
+            and int(rotated_input_features) % max(size, GROUP) == 0
+            and native_w4a4_shape_supported(rotated_input_features, output_features))
+
+
+def native_w4a4_version() -> str:
+    return native.version()
+
+
+def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, workspace: W4A4Workspace | None = None, lora_scale: float = 1.0,
                      return_parts: bool = False, form: str = "auto"):
     """Full forward: rotation (``packed.rotation``; None = input already rotated), int4 activations
     per (token, 64-K), GEMM with per-group scales, low-rank branch, bias.  ``form``: ``integer``
     (tcgen05 int8 MMA, per-group int32 sums scaled in fp32), ``dense`` (operands expanded to fp16 once,
     dense fp16 MMA, faster from M = 256, rel-L2 up to 1.2e-3) or ``auto`` (the integer form)."""
 
-    del workspace
     if inputs.shape[-1] != packed.input_features or inputs.dtype != packed.dtype:
         raise XQTBackendError("SVDQ W4A4 input trailing dimension or dtype does not match the packed layer")
     x = inputs.reshape(-1, packed.input_features).contiguous()
@@ -129,8 +202,17 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
     if m == 0:
         return out.reshape(*inputs.shape[:-1], n)
     lib = native.library()
-    codes, scales, rotated = rotate_quantize(x, packed.rotation, bits=4, group_size=GROUP, return_rotated=True)
-    la = torch.zeros((-(-m // TILE) * TILE, RANK_PAD), device=device, dtype=torch.float32)
+    buffers = None
+    if workspace is not None:
+        if workspace.padded_rows < m or int(workspace.quantized_activation.shape[1]) != k \
+                or workspace.rotated_activation is None or (packed.rank and workspace.lora_activation is None):
+            raise ValueError("workspace extent does not match inputs / packed weights")
+        buffers = (workspace.quantized_activation, workspace.activation_scales, workspace.rotated_activation)
+    codes, scales, rotated = rotate_quantize(x, packed.rotation, bits=4, group_size=GROUP, return_rotated=True, out=buffers)
+    if workspace is not None and workspace.lora_activation is not None:
+        la = workspace.lora_activation          # rows past M stay zero: the kernels only write rows < M
+    else:
+        la = torch.zeros((-(-m // TILE) * TILE, RANK_PAD), device=device, dtype=torch.float32)
     stream = native.stream_handle(device)
     # auto keeps the integer form: it is the one that meets the 1e-3 parity bar at every K (the dense
     # form is about 3.5x faster at M >= 256 and within 1.2e-3)
@@ -148,7 +230,7 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
                 native.check(lib.xqt_b200_lowrank_down(rotated.data_ptr(), packed.down.data_ptr(), la.data_ptr(), m, k,
                                                        native.DTYPE_CODE[packed.dtype], stream), "xqt_b200_lowrank_down")
             if lora_scale != 1.0:
-                la.mul_(float(lora_scale))
+                la[:m].mul_(float(lora_scale))
         if dense:
             native.check(lib.xqt_b200_w4a4_dense(
                 codes.data_ptr(), scales.data_ptr(), packed.qweight.data_ptr(), packed.weight_scales.data_ptr(),
@@ -166,22 +248,36 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
 
 
 def convrot_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, rot_size: int | None = None,
-                        workspace=None) -> torch.Tensor:
-    """ConvRot W4A4 (no low-rank branch): same kernels with an empty rank-R term."""
+                        workspace: W4A4Workspace | None = None) -> torch.Tensor:
+    """ConvRot W4A4 (no low-rank branch): same kernels with an empty rank-R term
+    (cf. svdq_w4a4_sm89.py:1082-1100)."""
 
     if rot_size is not None and packed.rotation is not None and int(rot_size) != packed.rotation.block:
         raise XQTBackendError("rot_size disagrees with the rotation the layer was packed with")
     return svdq_w4a4_linear(inputs, packed, workspace=workspace)
 
 
-def bind_svdq_w4a4_linear(packed: PackedSVDQW4A4Linear, workspace=None, *, rows: int, lora_scale: float = 1.0):
-    def run(inputs: torch.Tensor) -> torch.Tensor:
-        if inputs.reshape(-1, packed.input_features).shape[0] != rows:
-            raise XQTBackendError("bound SVDQ W4A4 call: row count mismatch")
-        return svdq_w4a4_linear(inputs, packed, lora_scale=lora_scale)
+def bind_svdq_w4a4_linear(packed: PackedSVDQW4A4Linear, workspace: W4A4Workspace | None = None, *, rows: int,
+                          lora_scale: float = 1.0):
+    """Validated state for the steady-state path (cf. svdq_w4a4_sm89.py:1264-1318): the workspace owns the
+    codes, scales, rotated activation and low-rank activation, so a call allocates only its output."""
 
+    rows = int(rows)
+    if workspace is None:
+        workspace = allocate_w4a4_workspace(rows, packed, with_lora_rank=packed.rank)
+    if workspace.padded_rows < rows or (packed.rank and workspace.lora_activation is None):
+        raise ValueError("SVDQuant workspace does not match rows / rank")
+    k, dtype, device = packed.input_features, packed.dtype, packed.qweight.device
+
+    def run(inputs: torch.Tensor) -> torch.Tensor:
+        if inputs.dtype != dtype or inputs.device != device or inputs.shape[-1] != k or inputs.numel() != rows * k:
+            raise XQTBackendError("bound SVDQ W4A4 call: input shape, dtype or device mismatch")
+        return svdq_w4a4_linear(inputs, packed, workspace=workspace, lora_scale=lora_scale)
+
+    run.keep = (packed, workspace)
     return run
 
 
-__all__ = ["PackedSVDQW4A4Linear", "bind_svdq_w4a4_linear", "convrot_w4a4_linear", "pack_svdq_w4a4_linear",
-           "svdq_w4a4_linear"]
+__all__ = ["PackedSVDQW4A4Linear", "W4A4Workspace", "allocate_w4a4_workspace", "bind_svdq_w4a4_linear", "convrot_w4a4_linear",
+           "native_convrot_w4a4_shape_supported", "native_w4a4_available", "native_w4a4_shape_supported", "native_w4a4_version",
+           "pack_svdq_w4a4_linear", "svdq_w4a4_linear"]

@@ -79,41 +79,135 @@ def w8a8_gemm(codes: torch.Tensor, act_scale: torch.Tensor, packed: PackedConvRo
     return out
 
 
-def convrot_w8a8_linear(inputs: torch.Tensor, packed: PackedConvRotW8A8Linear, *,
-                        rotated_input_features: bool = False, rot_size: int = 256,
-                        rotation: Rotation | None = None, workspace=None) -> torch.Tensor:
-    """Full forward.  ``rotated_input_features=True`` means the caller already rotated the input
-    (the rotation is skipped, the rounding and quantisation are not)."""
+_REGULAR_SIZES = (1, 4, 16, 64, 256, 1024)
 
-    del workspace  # scratch is managed per stream by xqt_b200.native
-    if inputs.shape[-1] != packed.input_features:
-        raise XQTBackendError("ConvRot W8A8 input trailing dimension does not match input_features")
+
+def native_convrot_w8a8_available(dtype: torch.dtype, *, build: bool = False) -> bool:
+    """Whether the B200 W8A8 backend can run on the current device (cf. convrot_w8a8_sm89.py:128-149)."""
+
+    import os
+
+    if dtype not in (torch.float16, torch.bfloat16):
+        return False
+    if not torch.cuda.is_available() or torch.cuda.get_device_capability() != (10, 0):
+        return False
+    if os.environ.get("XQT_DISABLE_B200", "0") not in {"", "0"}:
+        return False
+    return native.available() if build else native.LIBRARY_PATH.exists()
+
+
+def native_convrot_w8a8_shape_supported(logical_input_features: int, rotated_input_features: int, output_features: int,
+                                        rot_size: int) -> bool:
+    """Same predicate shape as xqt's (convrot_w8a8_sm89.py:35-50); the B200 kernels take every regular
+    Hadamard order up to 1024 (xqt: 256 only), K a multiple of 16 and N a multiple of 8."""
+
+    logical_k, rotated_k = int(logical_input_features), int(rotated_input_features)
+    return (0 < logical_k <= rotated_k and int(output_features) > 0 and int(output_features) % 8 == 0
+            and int(rot_size) in _REGULAR_SIZES and rotated_k % max(int(rot_size), 16) == 0)
+
+
+def native_prerotated_w8a8_shape_supported(rotated_input_features: int, output_features: int) -> bool:
+    return int(rotated_input_features) > 0 and int(rotated_input_features) % 16 == 0 and int(output_features) > 0 \
+        and int(output_features) % 8 == 0
+
+
+def native_convrot_w8a8_version(dtype: torch.dtype) -> str:
+    del dtype
+    return native.version()
+
+
+@dataclass
+class ConvRotW8A8Workspace:
+    """Per-call scratch of the linear (cf. convrot_w8a8_sm89.py:168-176): int8 activation codes
+    ``[rows, padded K]`` and their per-token scales ``[rows]``."""
+
+    quantized_activation: torch.Tensor
+    activation_scales: torch.Tensor
+
+    @property
+    def padded_rows(self) -> int:
+        return int(self.quantized_activation.shape[0])
+
+
+def allocate_convrot_w8a8_workspace(rows: int, packed: PackedConvRotW8A8Linear) -> ConvRotW8A8Workspace:
+    device = packed.qweight.device
+    return ConvRotW8A8Workspace(
+        quantized_activation=torch.empty((int(rows), packed.padded_input_features), dtype=torch.int8, device=device),
+        activation_scales=torch.empty((int(rows),), dtype=torch.float32, device=device))
+
+
+def convrot_w8a8_linear(inputs: torch.Tensor, packed: PackedConvRotW8A8Linear, *,
+                        rotated_input_features: int | None = None, rot_size: int = 256,
+                        workspace: ConvRotW8A8Workspace | None = None, rotation: Rotation | None = None) -> torch.Tensor:
+    """Full forward, signature of xqt's op (convrot_w8a8_sm89.py:365-372).
+
+    ``rotated_input_features`` is the (padded) K the weight was rotated and quantised at; it must equal
+    ``packed.input_features`` (default).  ``rot_size`` is the regular Hadamard block; ``rot_size == 1``
+    means the caller already rotated the input (rounding and quantisation still happen).  ``rotation``
+    (an extension) supplies a non-regular rotation, e.g. a seeded Sylvester block.  With a ``workspace``
+    of at least the call's rows the prologue allocates nothing."""
+
     if inputs.dtype != packed.dtype:
-        raise XQTBackendError("ConvRot W8A8 input dtype disagrees with the packed layer")
-    x = inputs.reshape(-1, packed.input_features)
-    if packed.padded_input_features != packed.input_features:
-        x = torch.nn.functional.pad(x, (0, packed.padded_input_features - packed.input_features))
-    if rotated_input_features:
-        rot = None
-    else:
-        rot = rotation if rotation is not None else regular_rotation(int(rot_size))
-    codes, scales = rotate_quantize(x, rot, bits=8)
+        raise XQTBackendError("inputs must match the packed ConvRot W8A8 dtype")
+    if not inputs.is_cuda or inputs.device != packed.qweight.device:
+        raise XQTBackendError("inputs and packed weights must share a CUDA device")
+    rotated_k = packed.input_features if rotated_input_features is None else int(rotated_input_features)
+    if isinstance(rotated_input_features, bool) or rotated_k != packed.input_features:
+        raise XQTBackendError("native ConvRot W8A8 shape or rotation size is unsupported: rotated_input_features "
+                              "must be the K the layer was packed with")
+    logical_k = int(inputs.shape[-1])
+    if rotation is None:
+        supported = native_prerotated_w8a8_shape_supported(rotated_k, packed.output_features) if int(rot_size) == 1 else \
+            native_convrot_w8a8_shape_supported(logical_k, rotated_k, packed.output_features, int(rot_size))
+        if not supported:
+            raise XQTBackendError("native ConvRot W8A8 shape or rotation size is unsupported")
+    if logical_k > rotated_k:
+        raise XQTBackendError("ConvRot W8A8 input trailing dimension exceeds rotated_input_features")
+    x = inputs.reshape(-1, logical_k)
+    pad = packed.padded_input_features - logical_k
+    if pad:
+        x = torch.nn.functional.pad(x, (0, pad))
+    rot = rotation if rotation is not None else (None if int(rot_size) == 1 else regular_rotation(int(rot_size)))
+    out_buffers = None
+    if workspace is not None:
+        if workspace.padded_rows < x.shape[0] or int(workspace.quantized_activation.shape[1]) != packed.padded_input_features:
+            raise ValueError("workspace extent does not match inputs / packed weights")
+        out_buffers = (workspace.quantized_activation, workspace.activation_scales)
+    codes, scales = rotate_quantize(x, rot, bits=8, out=out_buffers)
     out = w8a8_gemm(codes, scales, packed)
     return out.reshape(*inputs.shape[:-1], packed.output_features)
 
 
-def bind_convrot_w8a8_linear(packed: PackedConvRotW8A8Linear, *, rows: int, rot_size: int = 256,
-                             rotated_input_features: bool = False, rotation: Rotation | None = None):
-    """Closure for a fixed row count (cf. convrot_w8a8_sm89.py:441-500)."""
+def bind_convrot_w8a8_linear(packed: PackedConvRotW8A8Linear, workspace: ConvRotW8A8Workspace | None = None, *, rows: int,
+                             rotated_input_features: int | None = None, rot_size: int = 256,
+                             rotation: Rotation | None = None):
+    """Validated state for the steady-state path (cf. convrot_w8a8_sm89.py:441-500): shapes, rotation
+    vector and scratch are fixed here; the callable makes the two library calls (prologue, GEMM) and
+    allocates only its output."""
+
+    rows = int(rows)
+    rotated_k = packed.input_features if rotated_input_features is None else int(rotated_input_features)
+    if rotated_k != packed.input_features or packed.padded_input_features != packed.input_features:
+        raise XQTBackendError("bound ConvRot W8A8: rotated_input_features must be the (unpadded) K of the packed layer")
+    if workspace is None:
+        workspace = allocate_convrot_w8a8_workspace(rows, packed)
+    if workspace.padded_rows < rows or int(workspace.quantized_activation.shape[1]) != packed.padded_input_features:
+        raise ValueError("workspace extent does not match rows / packed weights")
+    rot = rotation if rotation is not None else (None if int(rot_size) == 1 else regular_rotation(int(rot_size)))
+    device, k, n, dtype = packed.qweight.device, packed.input_features, packed.output_features, packed.dtype
+    buffers = (workspace.quantized_activation, workspace.activation_scales)
 
     def run(inputs: torch.Tensor) -> torch.Tensor:
-        if inputs.reshape(-1, packed.input_features).shape[0] != rows:
-            raise XQTBackendError("bound ConvRot W8A8 call: row count mismatch")
-        return convrot_w8a8_linear(inputs, packed, rotated_input_features=rotated_input_features, rot_size=rot_size,
-                                   rotation=rotation)
+        if inputs.dtype != dtype or inputs.device != device or inputs.shape[-1] != k or inputs.numel() != rows * k \
+                or not inputs.is_contiguous():
+            raise XQTBackendError("bound ConvRot W8A8 call: input shape, dtype, device or layout mismatch")
+        codes, scales = rotate_quantize(inputs.view(rows, k), rot, bits=8, out=buffers)
+        return w8a8_gemm(codes, scales, packed).view(*inputs.shape[:-1], n)
 
+    run.keep = (packed, workspace, rot)
     return run
 
 
-__all__ = ["PackedConvRotW8A8Linear", "bind_convrot_w8a8_linear", "convrot_w8a8_linear", "pack_convrot_w8a8_linear",
-           "w8a8_gemm"]
+__all__ = ["ConvRotW8A8Workspace", "PackedConvRotW8A8Linear", "allocate_convrot_w8a8_workspace", "bind_convrot_w8a8_linear",
+           "convrot_w8a8_linear", "native_convrot_w8a8_available", "native_convrot_w8a8_shape_supported",
+           "native_convrot_w8a8_version", "native_prerotated_w8a8_shape_supported", "pack_convrot_w8a8_linear", "w8a8_gemm"]

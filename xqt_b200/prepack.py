@@ -25,8 +25,10 @@ pack kernel xqt/kernels/jit/csrc/quantization/awq_w4a16_sm89_kernel.cu:405-479).
            4*(j%2) + (0,0,2,2,1,1,3,3)``: ``(word >> 4*i) & 0x000f000f`` is register ``i`` of the A
            fragment, and the 16 bytes of activations a lane needs for two steps are contiguous.
            Codes are unsigned; two's-complement nibbles are stored as ``code + 8``.  Rows past N are zero.
-  params   ``[tiles][kblocks][128/group][4 warps][8 r][4][2]``: the (scale, zero point) pairs of the
-           four channels ``32*w + 16*t + 8*h + r`` a lane's accumulators belong to, index ``2*t + h``.
+  params   ``[2 or 1][tiles][kblocks][128/group][4 warps][8 r][4]``: plane 0 the scales, plane 1 the zero
+           points (absent for symmetric weights) of the four channels ``32*w + 16*t + 8*h + r`` a lane's
+           accumulators belong to, index ``2*t + h``; the two planes are passed to the kernel as
+           separate arrays.
 """
 
 from __future__ import annotations
@@ -50,7 +52,7 @@ class TiledW4:
     stream-K mma.sync decode kernel), ``"rows128"`` (weights ``[tiles, kblocks, 4, 128, 16]``, one
     16-byte chunk of 32 K per channel, for the tcgen05 decode kernel whose threads each own a
     channel) or ``"lanes"`` (weights ``[tiles, kblocks, 4, 2, 2, 32, 16]``, params
-    ``[tiles, kblocks, 128/group, 4, 8, 4, 2]``, for the cluster split-K decode kernel).
+    ``[planes, tiles, kblocks, 128/group, 4, 8, 4]``, for the cluster split-K decode kernel).
     """
 
     weights: torch.Tensor      # uint8 [tiles, kblocks, 16, 32, 16]
@@ -176,8 +178,8 @@ def lanes_w4(qweight: torch.Tensor, scales: torch.Tensor, zero_points: torch.Ten
         q = q.reshape(tiles, 4, 2, 2, 8, kblocks, per_block)       # [T, w, t, h, r, kb, sub]
         return q.permute(0, 5, 6, 1, 4, 2, 3).reshape(tiles, kblocks, per_block, 4, 8, 4)
 
-    zeros = torch.zeros_like(scales) if zero_points is None else zero_points.to(scales.dtype)
-    params = torch.stack((laned(scales), laned(zeros)), dim=-1).contiguous()
+    planes = (laned(scales),) if zero_points is None else (laned(scales), laned(zero_points.to(scales.dtype)))
+    params = torch.stack(planes, dim=0).contiguous()
     return TiledW4(weights=weights, params=params, n=n, k=k, group_size=int(group_size),
                    nibble_signed=bool(nibble_signed), has_zero_point=zero_points is not None, layout="lanes")
 
@@ -193,10 +195,12 @@ def _unlane_w4(tiled: TiledW4) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor
     if tiled.nibble_signed:
         codes = codes ^ 8
     qweight = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
-    p = tiled.params.reshape(tiles, kblocks, per_block, 4, 8, 2, 2, 2)       # [T, kb, sub, w, r, t, h, 2]
-    p = p.permute(0, 3, 5, 6, 4, 1, 2, 7).reshape(tiles * TILE_ROWS, -1, 2)[: tiled.n]
-    scales = p[..., 0].contiguous()
-    zeros = p[..., 1].contiguous() if tiled.has_zero_point else None
+    def unlaned(plane: torch.Tensor) -> torch.Tensor:
+        q = plane.reshape(tiles, kblocks, per_block, 4, 8, 2, 2)              # [T, kb, sub, w, r, t, h]
+        return q.permute(0, 3, 5, 6, 4, 1, 2).reshape(tiles * TILE_ROWS, -1)[: tiled.n].contiguous()
+
+    scales = unlaned(tiled.params[0])
+    zeros = unlaned(tiled.params[1]) if tiled.has_zero_point else None
     return qweight, scales, zeros
 
 

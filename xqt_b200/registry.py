@@ -195,11 +195,14 @@ def b200_rows() -> tuple[GemmKernelRegistration, ...]:
         GemmKernelRegistration(
             name=B200_SVD_W4A4, backend="custom_cuda", maturity="metadata_only",
             capability=GemmCapability(
-                architectures=("sm_100",), weight_dtypes=("int4",), activation_dtypes=("int8",),
-                scale_modes=("w:groupwise/a:per_token",), epilogues=("none",), min_sm=100),
+                architectures=("sm_100",), weight_dtypes=("int4",), activation_dtypes=("fp16", "bf16"),
+                scale_modes=("w:groupwise/a:per_token", "w:groupwise/a:per_tensor", "w:groupwise/a:none"),
+                epilogues=("none",), min_sm=100),
             kernel_family="svd_w4a4_b200", layout="xqt_int4_nk_v1", tile_shape=(128, 128, 64), warp_count=8,
-            stage_count=4, priority=60, implementation="cuda_sm100a_svd_w4a4",
-            selection_reason="rotation + group-64 int4 activations, kind::i8 GEMM, rank-r low-rank branch",
+            stage_count=4, priority=55, implementation="cuda_sm100a_svd_w4a4",
+            selection_reason="int4 residual + rank-r pair (executor kwargs low_rank_down / low_rank_up): group-64 int4 "
+                             "activations quantised in the call, kind::i8 GEMM, low-rank up projection in the epilogue; "
+                             "below the W4A16 row, which serves the same request without a low-rank pair",
         ),
     )
 
