@@ -155,6 +155,12 @@ int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, co
  *   group_size in {64, 128}; K a multiple of 128; 1 <= M <= 16; any zero point (integer or not).
  *   output        [M, N] act_dtype, or fp32 (out_dtype = XQT_B200_FP32: unrounded partial sums of a
  *                 K-sharded layer, then no residual)
+ *   residual      [M, N] act_dtype or NULL; it may be the output buffer itself (in-place residual += projection:
+ *                 every element is read before it is written)
+ *   epilogue_flags  bit 0: round the projection to act_dtype BEFORE adding the residual -- the numerics of the
+ *                 unfused `residual + projection(x)` that AWQW4A16Linear.bind_residual keeps
+ *                 (xqt/runtime/modules/awq_w4a16_linear.py:665-737); 0: one rounding after the add
+ *                 (the GEMM contract, xqt/kernels/ops/gemm/reference.py:362-390)
  *   status        NULL, or a device word the kernel sets to 64 when the bounded wait for its
  *                 activation copy ran out (the result is then undefined; nothing hangs)
  * Needs no workspace: the K pieces of a tile are the CTAs of one thread-block cluster and reduce
@@ -170,7 +176,7 @@ int xqt_b200_w4a16_decode_lanes_set_plan(int warp_quads, int cluster);
 int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights, const void* lane_scales,
                                 const void* lane_zeros, const float* bias, const void* residual, void* output, int m, int n, int k,
                                 int group_size, int nibble_signed, int act_dtype, int param_dtype,
-                                int out_dtype, unsigned int* status, xqt_b200_stream_t stream);
+                                int out_dtype, int epilogue_flags, unsigned int* status, xqt_b200_stream_t stream);
 
 /* W4A16 decode with the scratch built into the library: same operation, arguments and result as
  * xqt_b200_w4a16_decode_tiled, minus the workspace pair.  It has no counterpart in the reference.
@@ -216,13 +222,23 @@ int xqt_b200_w4a16_decode_static_status(unsigned int* host_status, xqt_b200_stre
  *   rot_kind      0 none, 1 regular Hadamard (rot_block a power of 4), 2 Sylvester (power of 2)
  *   column_scale  [rot_block] fp32 = signs / sqrt(rot_block) (NULL when rot_kind == 0)
  *   quant_bits    8: per-token scale max(amax,1e-8)/127, codes in [-128,127], scales [M]
- *                 4: per (token, group_size) scale max(amax/7,1e-6), codes in [-8,7], scales [M, K/group_size]
+ *                 4: per (token, group_size) scale max(amax/7,1e-6), codes in [-8,7], scales [M, K/group_size];
+ *                    group_size 0: one scale per token (ConvRotMixedPrecisionLinear's own activation form,
+ *                    convrot_4bit.py:669-679), replicated into scales [M, K/64]
  *   codes         int8 [M, K] in both modes;  rotated: [M, K] act_dtype or NULL (the rotated, rounded
  *                 activation, input of the W4A4 low-rank branch)
  */
 int xqt_b200_rotate_quantize(const void* activation, const float* column_scale, void* codes,
                              float* scales, void* rotated, int m, int k, int rot_kind, int rot_block,
                              int quant_bits, int group_size, int act_dtype, xqt_b200_stream_t stream);
+
+/* Per-tensor dynamic int8 quantisation, the activation side of xqt's reference W8A8 linear Int8MmaLinear
+ * (xqt/contracts/int8_mma.py:135-149,308-319): scale = max(absmax(activation), eps) / 127,
+ * codes = clamp(rint(x / scale), -127, 127).  codes int8 [M,K]; row_scales fp32 [M] receives the scale
+ * once per row (the int8 GEMM below takes per-token scales); stats: two floats of caller scratch,
+ * [0] = absmax, [1] = scale after the call.  K a multiple of 8. */
+int xqt_b200_quantize_per_tensor(const void* activation, void* codes, float* row_scales, float* stats, int m,
+                                 int k, int act_dtype, float eps, xqt_b200_stream_t stream);
 
 /* W8A8 GEMM: output[m,n] = int32(sum_k a[m,k] w[n,k]) * act_scale[m] * weight_scale[n] (+ bias[n]).
  * Replaces xqt_convrot_w8a8_sm89_gemm / _small_gemm (convrot_w8a8_sm89_kernel.cu:506-755; the

@@ -24,4 +24,4 @@ the reference's per-token CPU formula (convrot_4bit.py:669-679) applied at the
 CUDA kernel's group granularity.
 """
 
-from . import mlp, rotation, w4a16, w4a4, w8a8  # noqa: F401
+from . import mlp, pattern, rotation, w4a16, w4a4, w8a8  # noqa: F401

@@ -102,8 +102,12 @@ def w4a4_forward(
     signs: torch.Tensor | None = None,
     bias=None,
     return_parts: bool = False,
+    act_group_size: int | None = None,
 ):
     """rotate -> group int4 activations -> int GEMM with per-slab scales -> + low rank -> + bias.
+
+    ``act_group_size`` (default: ``group_size``) is the span of one activation scale; ``K`` gives the
+    per-token form, whose one scale per row is applied to every weight slab.
 
     ``down`` / ``up`` are used at the precision they are given in (bf16 factors
     are upcast to fp32 exactly).  Output is cast once to ``x.dtype``.
@@ -113,10 +117,13 @@ def w4a4_forward(
         x_rot = x
     else:
         x_rot = rotation.rotate_fht(x, kind=rot_kind, block=rot_block, signs=signs)
-    q_a, s_a = quantize_act_groups(x_rot, group_size=group_size)
+    act_group = int(act_group_size or group_size)
+    q_a, s_a = quantize_act_groups(x_rot, group_size=act_group)
     m, k = q_a.shape
     n = packed.shape[0]
     groups = k // group_size
+    assert act_group % group_size == 0
+    s_a = s_a.repeat_interleave(act_group // group_size, dim=1)
     q_w = unpack_nibbles(packed, k, signed=True)
     # Per-slab integer partial sums are exact in fp32 (|sum| <= 64*8*8 = 4096).
     qa = q_a.to(torch.float32).reshape(m, groups, group_size)

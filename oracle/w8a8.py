@@ -45,6 +45,16 @@ def quantize_act_per_token(x_rot: torch.Tensor):
     return q, scale
 
 
+def quantize_act_per_tensor(x: torch.Tensor, *, eps: float = 1e-6):
+    """-> (q int8 [M,K], scale fp32 scalar): ``Int8MmaLinear`` (xqt/contracts/int8_mma.py:135-149,317-319):
+    ``scale = max(absmax, eps)/127``, ``q = clamp(round(x/scale), -127, 127)``."""
+
+    v = x.to(torch.float32)
+    scale = (v.reshape(-1).abs().amax().clamp_min(float(eps)) / 127.0).reshape(())
+    q = torch.round(v / scale).clamp(-127, 127).to(torch.int8)
+    return q, scale
+
+
 def gemm_reference(q_a, s_a, q_w, s_w, *, bias=None, out_dtype=torch.bfloat16):
     """Dequantise both operands, fp32 matmul (reference.py:511-533)."""
 

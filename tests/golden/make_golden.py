@@ -265,6 +265,24 @@ def main() -> None:
         },
         HERE / "quantizers.pt",
     )
+    # ------------------------------------------------------------------ Int8MmaLinear (per-tensor W8A8)
+    from xqt.contracts.int8_mma import Int8MmaLinear
+
+    lin8 = torch.nn.Linear(256, 24, bias=True)
+    with torch.no_grad():
+        lin8.weight.copy_(torch.randn((24, 256), generator=gen(90)) * 0.02)
+        lin8.bias.copy_(torch.randn((24,), generator=gen(91)))
+    mod8 = Int8MmaLinear.from_linear(lin8)
+    x8 = torch.randn((5, 256), generator=gen(92)).to(torch.bfloat16)
+    a_scale8 = Int8MmaLinear.activation_scale_from_inputs(x8, eps=mod8.eps)
+    torch.save(
+        {
+            "x": x8, "qweight_t": mod8.qweight_t, "weight_scale": mod8.weight_scale, "bias": mod8.bias,
+            "act_scale": a_scale8, "act_codes": torch.round(x8.to(torch.float32) / a_scale8).clamp(-127, 127).to(torch.int8),
+            "out": mod8(x8), "eps": torch.tensor(mod8.eps),
+        },
+        HERE / "int8_mma.pt",
+    )
     for path in sorted(HERE.glob("*.pt")):
         print(path.name, path.stat().st_size, "bytes")
 

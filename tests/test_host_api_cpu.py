@@ -175,7 +175,7 @@ def test_kernel_namespace_selection_and_conflicts(monkeypatch):
         replace(ours, target="xqt_b200.ops.w4a16:missing").load()
     with pytest.raises(KeyError):
         ks.select_kernel("quantization.nothing", table=table)
-    assert "quantization.svdq_w4a4_linear" in ks.registry.ops() and ks.ENGINE["min_capability"] == 100
+    assert "quantization.svdq_w4a4_linear" in ks.registry.ops() and "quantization.gemm_int4_dequant" in ks.registry.ops()
 
 
 def _w8a8_spec(m=4, n=8, k=64, out="bf16"):

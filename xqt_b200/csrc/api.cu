@@ -21,7 +21,7 @@ int w4a16_decode_tc_launch(const void*, const void*, const void*, const float*, 
 size_t w4a16_decode_tc_workspace_bytes();
 bool w4a16_decode_tc_supported(int m, int n, int k, int group_size);
 int w4a16_decode_cl_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int, int,
-                           int, int, int, int, int, unsigned int*, cudaStream_t);
+                           int, int, int, int, int, int, unsigned int*, cudaStream_t);
 bool w4a16_decode_cl_supported(int m, int n, int k, int group_size);
 void w4a16_decode_cl_set_plan(int kw, int s);
 void w4a16_decode_cl_get_plan(int m, int n, int k, int* kw, int* s);
@@ -47,6 +47,7 @@ int lowrank_down_tc_launch(const void*, const void*, float*, int, int, int, unsi
 int peer_allreduce_launch(const void* const*, void* const*, int, int, unsigned int, long long, int, const float*, void*, int,
                           unsigned int, unsigned int*, cudaStream_t);
 int w4a16_decode_static_status(unsigned int*, cudaStream_t);
+int quant_per_tensor_launch(const void*, void*, float*, float*, int, int, int, float, cudaStream_t);
 }  // namespace xqt_b200
 
 using namespace xqt_b200;
@@ -199,16 +200,16 @@ int xqt_b200_w4a16_decode_lanes_set_plan(int warp_quads, int cluster) {
 int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights, const void* lane_scales,
                                 const void* lane_zeros, const float* bias, const void* residual, void* output, int m, int n, int k,
                                 int group_size, int nibble_signed, int act_dtype, int param_dtype, int out_dtype,
-                                unsigned int* status, xqt_b200_stream_t stream) {
-  XQT_REQUIRE(m >= 0 && n > 0 && k > 0);
+                                int epilogue_flags, unsigned int* status, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(m >= 0 && n > 0 && k > 0 && (epilogue_flags & ~1) == 0);
   XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
   XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
   if (m == 0) return 0;
   XQT_REQUIRE(activation != nullptr && lane_weights != nullptr && lane_scales != nullptr && output != nullptr);
   XQT_REQUIRE(out_dtype == act_dtype || out_dtype == XQT_B200_FP32);
   return w4a16_decode_cl_launch(activation, lane_weights, lane_scales, lane_zeros, bias, residual, output, m, n, k, group_size,
-                                nibble_signed, act_dtype, param_dtype, out_dtype == XQT_B200_FP32 ? 1 : 0, status,
-                                (cudaStream_t)stream);
+                                nibble_signed, act_dtype, param_dtype, out_dtype == XQT_B200_FP32 ? 1 : 0, epilogue_flags,
+                                status, (cudaStream_t)stream);
 }
 
 int xqt_b200_w4a16_decode_tiled_static(const void* activation, const void* tiled_weights, const void* tiled_params,
@@ -241,6 +242,13 @@ int xqt_b200_rotate_quantize(const void* activation, const float* column_scale, 
   XQT_REQUIRE(activation != nullptr && codes != nullptr && scales != nullptr);
   return rotate_quant_launch(activation, column_scale, codes, scales, rotated, m, k, rot_kind, rot_block, quant_bits,
                              group_size, act_dtype, (cudaStream_t)stream);
+}
+
+int xqt_b200_quantize_per_tensor(const void* activation, void* codes, float* row_scales, float* stats, int m, int k,
+                                 int act_dtype, float eps, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(activation != nullptr && codes != nullptr && row_scales != nullptr && stats != nullptr);
+  return quant_per_tensor_launch(activation, codes, row_scales, stats, m, k, act_dtype, eps, (cudaStream_t)stream);
 }
 
 int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const float* act_scale,

@@ -15,7 +15,10 @@
 //   mode 8: per token,  scale = max(amax, 1e-8) / 127, q = clamp(rint(x/scale), -128, 127)
 //           (xqt/kernels/ops/gemm/quantize.py:75-107)
 //   mode 4: per (token, group), scale = max(amax/7, 1e-6), q = clamp(rint(x/scale), -8, 7)
-//           (convrot_4bit.py:669-679 at the group granularity of gemm_w4a4.cuh:534-624)
+//           (convrot_4bit.py:669-679 at the group granularity of gemm_w4a4.cuh:534-624);
+//           group == 0 selects the artifact's own per-token form (one scale per token,
+//           convrot_4bit.py:669-679), written to every 64-K slot of the scale row so that the
+//           group-64 GEMM consumes it unchanged
 // Codes are written as int8 in both modes (the int4 GEMM consumes int8 operands: Blackwell has no
 // int4 MMA).
 #include "common.cuh"
@@ -87,6 +90,23 @@ rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_sc
     const float sc = fmaxf(s_scale, 1e-8f);
     for (int i = tid; i < k; i += kRqThreads) {
       const float q = fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), -128.f), 127.f);
+      codes[(size_t)row * k + i] = (int8_t)(int)q;
+    }
+  } else if (group == 0) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((tid & 31) == 0) s_red[tid >> 5] = amax;
+    __syncthreads();
+    if (tid == 0) {
+      float mx = 0.f;
+      for (int w = 0; w < kRqThreads / 32; ++w) mx = fmaxf(mx, s_red[w]);
+      s_scale = fmaxf(__fdiv_rn(mx, 7.0f), 1e-6f);
+    }
+    __syncthreads();
+    const float sc = s_scale;
+    for (int gi = tid; gi < k / 64; gi += kRqThreads) scales[(size_t)row * (k / 64) + gi] = sc;
+    for (int i = tid; i < k; i += kRqThreads) {
+      const float q = fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), -8.f), 7.f);
       codes[(size_t)row * k + i] = (int8_t)(int)q;
     }
   } else {
@@ -245,6 +265,20 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
     __syncthreads();
     sc = fmaxf(s_scale, 1e-8f);
     lo_clamp = -128.f; hi_clamp = 127.f;
+  } else if (group == 0) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (lane == 0) s_red[tid >> 5] = amax;
+    __syncthreads();
+    if (tid == 0) {
+      float mx = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, s_red[w]);
+      s_scale = fmaxf(__fdiv_rn(mx, 7.0f), 1e-6f);
+    }
+    __syncthreads();
+    sc = s_scale;
+    if (active && (tid & 3) == 0) scales[(size_t)row * (k / 64) + tid / 4] = sc;     // one 64-K slot per four threads
+    lo_clamp = -8.f; hi_clamp = 7.f;
   } else {
     // group of `group` elements = group/16 adjacent lanes (group is 16, 32, 64, ... <= 512)
     for (int off = 1; off < group / 16; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
@@ -282,9 +316,9 @@ int rotate_quant_launch(const void* x, const float* column_scale, void* codes, f
     while (v % base == 0) v /= base;
     XQT_REQUIRE(v == 1);
   }
-  if (mode == 4) XQT_REQUIRE(group > 0 && k % group == 0);
+  if (mode == 4) XQT_REQUIRE(group == 0 ? k % 64 == 0 : (group > 0 && k % group == 0));
   XQT_REQUIRE(act_dtype == XQT_B200_BF16 || act_dtype == XQT_B200_FP16);
-  const bool group_ok = mode == 8 || (group >= 16 && group <= 512 && (group & (group - 1)) == 0);
+  const bool group_ok = mode == 8 || group == 0 || (group >= 16 && group <= 512 && (group & (group - 1)) == 0);
   const bool block_ok = rot_kind == 0 || (rot_block >= 16 && ((uintptr_t)column_scale & 15) == 0);   // vector loads of the column factors
   if (k % 16 == 0 && k <= 16384 && group_ok && block_ok && ((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 15) == 0 &&
       (x_rot == nullptr || ((uintptr_t)x_rot & 15) == 0)) {

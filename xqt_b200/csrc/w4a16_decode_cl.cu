@@ -71,6 +71,7 @@ struct DecodeClParams {
   void* out;
   unsigned int* status; // may be null
   int m, n, k, out_f32;
+  int round_first;      // 1: round the projection to T before the residual is added (unfused `residual + proj` numerics)
   int kblocks, pieces, kw;
   int per, rem;         // kblocks = pieces * per + rem: piece i starts at i * per + min(i, rem)
   int xrow_bytes;       // shared-memory row stride of x
@@ -465,7 +466,10 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
       if (chn < p.n) {
         if (p.bias != nullptr) sum += p.bias[chn];
         const size_t o = (size_t)token * p.n + chn;
-        if (p.residual != nullptr) sum += to_float<T>(reinterpret_cast<const T*>(p.residual)[o]);
+        if (p.residual != nullptr) {
+          if (p.round_first) sum = to_float<T>(from_float<T>(sum));
+          sum += to_float<T>(reinterpret_cast<const T*>(p.residual)[o]);     // may alias out: read before the store below
+        }
         if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = sum;
         else reinterpret_cast<T*>(p.out)[o] = from_float<T>(sum);
       }
@@ -603,7 +607,7 @@ static int dcl_dispatch(const DecodeClParams& p, int group_size, int nt, int gri
 
 int w4a16_decode_cl_launch(const void* x, const void* wt, const void* scl, const void* zer, const float* bias, const void* residual,
                            void* out, int m, int n, int k, int group_size, int nibble_signed, int act_dtype,
-                           int param_dtype, int out_f32, unsigned int* status, cudaStream_t stream) {
+                           int param_dtype, int out_f32, int epilogue_flags, unsigned int* status, cudaStream_t stream) {
   using namespace dcl;
   XQT_REQUIRE(w4a16_decode_cl_supported(m, n, k, group_size));
   XQT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)wt & 31) == 0 && ((uintptr_t)scl & 15) == 0 && ((uintptr_t)zer & 15) == 0);
@@ -615,6 +619,8 @@ int w4a16_decode_cl_launch(const void* x, const void* wt, const void* scl, const
   p.wt = (const uint8_t*)wt; p.scl = (const uint8_t*)scl; p.zer = (const uint8_t*)zer; p.x = x; p.bias = bias; p.residual = residual; p.out = out;
   p.status = status;
   p.m = m; p.n = n; p.k = k; p.out_f32 = out_f32;
+  p.round_first = (epilogue_flags & 1) != 0;
+  XQT_REQUIRE(!(p.round_first && out_f32));
   p.kblocks = kblocks; p.kw = plan.kw; p.pieces = plan.kw * plan.s;
   XQT_REQUIRE(p.pieces >= 1 && p.pieces <= kblocks);
   const int slice_max = (kblocks * plan.kw + p.pieces - 1) / p.pieces + 1;   // upper bound of any CTA's slice

@@ -161,8 +161,9 @@ def b200_w8a8_executor(activation, weight, *, spec, weight_scales=None, activati
         raise XQTBackendError("B200 W8A8 executor serves int8 weights with int8 activations")
     if quant.output_dtype not in _TORCH:
         raise XQTBackendError("B200 W8A8 output dtype must be fp16 or bf16")
-    if quant.weight_granularity != "per_channel" or quant.activation_granularity != "per_token":
-        raise XQTBackendError("B200 W8A8 supports per-channel weight scales with per-token activation scales")
+    if quant.weight_granularity != "per_channel" or quant.activation_granularity not in ("per_token", "per_tensor"):
+        raise XQTBackendError("B200 W8A8 supports per-channel weight scales with per-token or per-tensor activation scales")
+    per_tensor = quant.activation_granularity == "per_tensor"
     if weight_zero_points is not None or activation_zero_points is not None or quant.activation_zero_point:
         raise XQTBackendError("B200 W8A8 is symmetric: zero points are not supported")
     if residual is not None or spec.epilogue.has_residual or spec.epilogue.activation != "none":
@@ -183,14 +184,22 @@ def b200_w8a8_executor(activation, weight, *, spec, weight_scales=None, activati
         raise XQTBackendError("B200 W8A8 needs K % 16 == 0 and N % 8 == 0")
     device, dtype = activation.device, _TORCH[quant.output_dtype]
     if activation.dtype == torch.int8:
-        if activation_scales is None or activation_scales.numel() != problem.m:
-            raise XQTBackendError("int8 activations need per-token activation_scales with M entries")
+        want = 1 if per_tensor else problem.m
+        if activation_scales is None or activation_scales.numel() != want:
+            raise XQTBackendError(f"int8 activations need activation_scales with {want} entries")
         codes = activation.contiguous()
-        a_scale = activation_scales.reshape(-1).to(device=device, dtype=torch.float32).contiguous()
+        a_scale = activation_scales.reshape(-1).to(device=device, dtype=torch.float32)
+        a_scale = (a_scale.expand(problem.m) if per_tensor else a_scale).contiguous()
     elif activation.dtype in (torch.float16, torch.bfloat16):
         if activation_scales is not None:
             raise XQTBackendError("floating activations are quantised dynamically: do not pass activation_scales")
-        codes, a_scale = rotate_quantize(activation.contiguous(), None, bits=8)
+        if per_tensor:
+            # Int8MmaLinear semantics (xqt/contracts/int8_mma.py:135-149,317-319): one scale, clamp +-127
+            from .ops.activation import quantize_int8_per_tensor
+
+            codes, a_scale, _ = quantize_int8_per_tensor(activation.contiguous())
+        else:
+            codes, a_scale = rotate_quantize(activation.contiguous(), None, bits=8)
     else:
         raise XQTBackendError("B200 W8A8 activation must be int8, fp16 or bf16")
     packed = PackedConvRotW8A8Linear(

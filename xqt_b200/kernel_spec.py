@@ -197,21 +197,14 @@ B200_KERNELS = (
                "SVDQuant W4A4 linear with rank-r branch"),
     KernelSpec("quantization.convrot_w4a4_rowwise_linear", KernelBackend.CUSTOM_CUDA,
                "xqt_b200.ops.w4a4:convrot_w4a4_linear", SM100, "ConvRot W4A4 linear (no low-rank branch)"),
+    KernelSpec("quantization.gemm_int4_dequant", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.pattern:gemm_int4_dequant", SM100,
+               "operator-stage W4 pattern: signed nibbles, w = scale * code - zero (zero in real units)"),
+    KernelSpec("quantization.int8_mma_linear", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.w8a8:int8_mma_linear", SM100,
+               "per-tensor dynamic W8A8 (Int8MmaLinear semantics) on tcgen05 kind::i8"),
     KernelSpec("quantization.swiglu", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.mlp:swiglu", SM100, "fused SwiGLU gating"),
 )
 for _spec in B200_KERNELS:
     register_kernel(_spec)
 
-ENGINE = {
-    # the fields of xqt's EngineRegistration (xqt/kernels/engine_resolve.py:48-82) for this backend
-    "name": "b200_cuda",
-    "provides": frozenset({"int8_mma", "true_int8_mma", "int4_mma", "dequant_gemm_epilogue", "hadamard_groupwise",
-                           "w4_storage_int8_mma", "gemm_int4_dequant"}),
-    "min_capability": 100,
-    "materializer": None,
-    "operator_visible": True,
-    "requires_cuda": True,
-}
-
-__all__ = ["B200_KERNELS", "CapabilityRequirement", "DeviceType", "ENGINE", "KernelBackend", "KernelRegistry",
+__all__ = ["B200_KERNELS", "CapabilityRequirement", "DeviceType", "KernelBackend", "KernelRegistry",
            "KernelSpec", "PlatformInfo", "SM100", "get_kernel", "register_kernel", "registry", "select_kernel"]

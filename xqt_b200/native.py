@@ -47,11 +47,12 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_decode_lanes_supported": (_I, [_I] * 4),
     "xqt_b200_w4a16_decode_lanes_plan": (_I, [_I] * 4 + [ctypes.POINTER(_I), ctypes.POINTER(_I)]),
     "xqt_b200_w4a16_decode_lanes_set_plan": (_I, [_I, _I]),
-    "xqt_b200_w4a16_decode_lanes": (_I, [_P] * 7 + [_I] * 8 + [_P, _P]),
+    "xqt_b200_w4a16_decode_lanes": (_I, [_P] * 7 + [_I] * 9 + [_P, _P]),
     "xqt_b200_w4a16_decode_tiled_static": (_I, [_P] * 6 + [_I] * 8 + [_P]),
     "xqt_b200_w4a16_decode_static_scratch_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_static_max_n": (_I, []),
     "xqt_b200_rotate_quantize": (_I, [_P] * 5 + [_I] * 7 + [_P]),
+    "xqt_b200_quantize_per_tensor": (_I, [_P] * 4 + [_I] * 3 + [ctypes.c_float, _P]),
     "xqt_b200_w8a8_gemm": (_I, [_P] * 6 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_lowrank_down": (_I, [_P] * 3 + [_I] * 3 + [_P]),
     "xqt_b200_w4a4_aux_tile_bytes": (_Z, [_I]),

@@ -37,16 +37,18 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
     device = x.device
     if rotation is not None and k % rotation.block:
         raise XQTBackendError("the rotated dimension must be a multiple of the rotation block")
-    if bits == 4 and k % group_size:
+    per_token4 = bits == 4 and int(group_size) == 0      # one int4 scale per token, replicated per 64-K slot
+    if bits == 4 and (k % 64 if per_token4 else k % group_size):
         raise XQTBackendError("K must be a multiple of the activation group size")
+    scale_groups = k // 64 if per_token4 else (k // group_size if bits == 4 else 0)
     if out is None:
         codes = torch.empty((m, k), device=device, dtype=torch.int8)
-        scales = torch.empty((m,) if bits == 8 else (m, k // group_size), device=device, dtype=torch.float32)
+        scales = torch.empty((m,) if bits == 8 else (m, scale_groups), device=device, dtype=torch.float32)
         rotated = torch.empty_like(x) if return_rotated else None
     else:
         codes, scales = out[0][:m], out[1][:m]
         rotated = out[2][:m] if return_rotated else None
-        want_scales = (m,) if bits == 8 else (m, k // group_size)
+        want_scales = (m,) if bits == 8 else (m, scale_groups)
         if codes.dtype != torch.int8 or tuple(codes.shape) != (m, k) or not codes.is_contiguous() \
                 or scales.dtype != torch.float32 or tuple(scales.shape) != want_scales or not scales.is_contiguous() \
                 or (rotated is not None and (rotated.dtype != x.dtype or tuple(rotated.shape) != (m, k) or not rotated.is_contiguous())):
@@ -62,4 +64,31 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
     return (codes, scales, rotated) if return_rotated else (codes, scales)
 
 
-__all__ = ["rotate_quantize"]
+def quantize_int8_per_tensor(x: torch.Tensor, *, eps: float = 1e-6, out: tuple | None = None):
+    """Per-tensor dynamic int8 codes, the activation side of xqt's ``Int8MmaLinear``
+    (xqt/contracts/int8_mma.py:135-149,308-319): ``scale = max(absmax, eps)/127``, codes clamped to
+    [-127, 127].  -> (codes int8 ``[M,K]``, row_scales fp32 ``[M]`` (the scale, once per row), scale fp32 ``[1]``)."""
+
+    if x.ndim != 2 or x.dtype not in (torch.float16, torch.bfloat16) or not x.is_cuda:
+        raise XQTBackendError("quantize_int8_per_tensor expects a CUDA rank-2 fp16/bf16 activation")
+    x = x.contiguous()
+    m, k = int(x.shape[0]), int(x.shape[1])
+    if k % 8:
+        raise XQTBackendError("per-tensor int8 quantisation needs K % 8 == 0")
+    device = x.device
+    if out is None:
+        codes = torch.empty((m, k), device=device, dtype=torch.int8)
+        rows = torch.empty((m,), device=device, dtype=torch.float32)
+        stats = torch.empty((2,), device=device, dtype=torch.float32)
+    else:
+        codes, rows, stats = out[0][:m], out[1][:m], out[2]
+    if m:
+        with torch.cuda.device(device):
+            code = native.library().xqt_b200_quantize_per_tensor(
+                x.data_ptr(), codes.data_ptr(), rows.data_ptr(), stats.data_ptr(), m, k, native.DTYPE_CODE[x.dtype],
+                float(eps), native.stream_handle(device))
+        native.check(code, "xqt_b200_quantize_per_tensor")
+    return codes, rows, stats[1:2]
+
+
+__all__ = ["quantize_int8_per_tensor", "rotate_quantize"]

@@ -200,7 +200,7 @@ def bind_awq_w4a16_decode(qweight: torch.Tensor, scales: torch.Tensor, scaled_ze
     status = native.status_word(device)
     args_head = (qweight.data_ptr(), scales.data_ptr(), native.ptr(scaled_zeros), native.ptr(bias32), 0)
     args_tail = (rows, output_features, input_features, group, 0, native.DTYPE_CODE[dtype], native.DTYPE_CODE[scales.dtype],
-                 native.DTYPE_CODE[dtype], status.data_ptr())
+                 native.DTYPE_CODE[dtype], 0, status.data_ptr())
 
     def bound(inputs: torch.Tensor) -> torch.Tensor:
         output = torch.empty((rows, output_features), dtype=dtype, device=device)

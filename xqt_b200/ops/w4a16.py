@@ -282,7 +282,7 @@ def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tens
     head = (tiled.weights.data_ptr(), tiled.params[0].data_ptr(),
             tiled.params[1].data_ptr() if tiled.has_zero_point else 0, native.ptr(bias32))
     tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), native.DTYPE_CODE[dtype],
-            native.DTYPE_CODE[tiled.params.dtype], native.DTYPE_CODE[odt])
+            native.DTYPE_CODE[tiled.params.dtype], native.DTYPE_CODE[odt], 0)
     index = device.index if device.index is not None else torch.cuda.current_device()
     status = native.status_word(device)
     status_ptr = status.data_ptr()

@@ -49,6 +49,7 @@ class PackedSVDQW4A4Linear:
     rank: int
     dtype: torch.dtype
     rotation: Rotation | None = None
+    act_granularity: str = "group"     # "group": one scale per (token, 64 K); "token": one per token (ConvRot artifact form)
 
     @property
     def padded_rank(self) -> int:
@@ -68,12 +69,15 @@ def pack_svdq_w4a4_linear(
     dtype: torch.dtype = torch.bfloat16,
     rotation: Rotation | None = None,
     device: torch.device | None = None,
+    act_granularity: str = "group",
 ) -> PackedSVDQW4A4Linear:
     """Build the B200 layout.  Pass the artifact's ``packed_residual`` / ``residual_scale``
     (group 64) to keep its integer codes bit for bit; otherwise ``residual_weight`` ``[N,K]`` is
     quantised with the artifact's own rule (scale = absmax/7, xqt/compression/quant/quantizers/svd.py:92-128).
     ``down_weight`` is ``[r,K]``, ``up_weight`` ``[N,r]`` (None for a layer without low-rank branch)."""
 
+    if act_granularity not in ("group", "token"):
+        raise XQTBackendError("act_granularity must be 'group' (per token and 64 K) or 'token'")
     if smooth is not None or norm_weight is not None:
         # xqt's sm_89 kernel can divide the activation by a per-channel smoothing vector and fuse an
         # RMSNorm weight into its quantise prologue (svdq_w4a4_sm89.py:471-557); neither is served here
@@ -115,7 +119,8 @@ def pack_svdq_w4a4_linear(
         qweight=packed_residual.to(device).contiguous(), aux=aux, weight_scales=scale.contiguous(),
         up=up[:n].contiguous() if rank else None, down=down,
         bias=None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous(),
-        input_features=k, output_features=n, padded_input_features=k, rank=rank, dtype=dtype, rotation=rotation)
+        input_features=k, output_features=n, padded_input_features=k, rank=rank, dtype=dtype, rotation=rotation,
+        act_granularity=act_granularity)
 
 
 @dataclass
@@ -208,7 +213,8 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
                 or workspace.rotated_activation is None or (packed.rank and workspace.lora_activation is None):
             raise ValueError("workspace extent does not match inputs / packed weights")
         buffers = (workspace.quantized_activation, workspace.activation_scales, workspace.rotated_activation)
-    codes, scales, rotated = rotate_quantize(x, packed.rotation, bits=4, group_size=GROUP, return_rotated=True, out=buffers)
+    codes, scales, rotated = rotate_quantize(x, packed.rotation, bits=4, group_size=GROUP if packed.act_granularity == "group" else 0,
+                                             return_rotated=True, out=buffers)
     if workspace is not None and workspace.lora_activation is not None:
         la = workspace.lora_activation          # rows past M stay zero: the kernels only write rows < M
     else:
@@ -250,7 +256,9 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
 def convrot_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, rot_size: int | None = None,
                         workspace: W4A4Workspace | None = None) -> torch.Tensor:
     """ConvRot W4A4 (no low-rank branch): same kernels with an empty rank-R term
-    (cf. svdq_w4a4_sm89.py:1082-1100)."""
+    (cf. svdq_w4a4_sm89.py:1082-1100).  A layer packed with ``act_granularity="token"`` reproduces the
+    artifact's own per-token activation scale (``ConvRotMixedPrecisionLinear``, convrot_4bit.py:669-679,
+    what its row-wise native kernel computes)."""
 
     if rot_size is not None and packed.rotation is not None and int(rot_size) != packed.rotation.block:
         raise XQTBackendError("rot_size disagrees with the rotation the layer was packed with")

@@ -79,6 +79,23 @@ def w8a8_gemm(codes: torch.Tensor, act_scale: torch.Tensor, packed: PackedConvRo
     return out
 
 
+def int8_mma_linear(inputs: torch.Tensor, packed: PackedConvRotW8A8Linear, *, eps: float = 1e-6) -> torch.Tensor:
+    """xqt's reference W8A8 linear ``Int8MmaLinear`` on the tensor cores (xqt/contracts/int8_mma.py:308-334):
+    one dynamic activation scale for the whole tensor, ``scale = max(absmax, eps)/127``, codes clamped to
+    [-127, 127], no rotation; ``out = int32(q_a q_w^T) * (a_scale * w_scale[n]) + bias``.  ``packed`` comes from
+    :func:`pack_convrot_w8a8_linear` (the module's ``qweight_t`` / ``weight_scale`` buffers)."""
+
+    from .activation import quantize_int8_per_tensor
+
+    if inputs.dtype != packed.dtype or not inputs.is_cuda or inputs.device != packed.qweight.device:
+        raise XQTBackendError("Int8MmaLinear inputs must match the packed layer's dtype and device")
+    if inputs.shape[-1] != packed.input_features or packed.padded_input_features != packed.input_features:
+        raise XQTBackendError("Int8MmaLinear input trailing dimension does not match input_features")
+    x = inputs.reshape(-1, packed.input_features)
+    codes, row_scales, _ = quantize_int8_per_tensor(x, eps=eps)
+    return w8a8_gemm(codes, row_scales, packed).reshape(*inputs.shape[:-1], packed.output_features)
+
+
 _REGULAR_SIZES = (1, 4, 16, 64, 256, 1024)
 
 
@@ -209,5 +226,5 @@ def bind_convrot_w8a8_linear(packed: PackedConvRotW8A8Linear, workspace: ConvRot
 
 
 __all__ = ["ConvRotW8A8Workspace", "PackedConvRotW8A8Linear", "allocate_convrot_w8a8_workspace", "bind_convrot_w8a8_linear",
-           "convrot_w8a8_linear", "native_convrot_w8a8_available", "native_convrot_w8a8_shape_supported",
+           "convrot_w8a8_linear", "int8_mma_linear", "native_convrot_w8a8_available", "native_convrot_w8a8_shape_supported",
            "native_convrot_w8a8_version", "native_prerotated_w8a8_shape_supported", "pack_convrot_w8a8_linear", "w8a8_gemm"]

@@ -187,7 +187,7 @@ def b200_rows() -> tuple[GemmKernelRegistration, ...]:
             name=B200_W8A8, backend="custom_cuda", maturity="metadata_only",
             capability=GemmCapability(
                 architectures=("sm_100",), weight_dtypes=("int8",), activation_dtypes=("int8",),
-                scale_modes=("w:per_channel/a:per_token",), epilogues=("none",), min_sm=100),
+                scale_modes=("w:per_channel/a:per_token", "w:per_channel/a:per_tensor"), epilogues=("none",), min_sm=100),
             kernel_family="w8a8_int8_b200", layout="xqt_int8_nk_v1", tile_shape=(128, 256, 128), warp_count=6,
             stage_count=4, priority=60, implementation="cuda_sm100a_w8a8",
             selection_reason="per-token int8 quantisation prologue + tcgen05 kind::i8 GEMM, fp32 dequant epilogue",
