@@ -473,95 +473,241 @@ def _time_us(fn, barrier, reps: int, warm: int = 3) -> float:
     return e0.elapsed_time(e1) * 1e3 / reps
 
 
-def measure_other_configs(device, world, rank, barrier) -> dict:
-    """The other benchmark configurations, timed with CUDA events (kernels only, inputs resident):
-    the SwiGLU MLP block at every world size (gate/up column-parallel, down row-parallel + all-reduce),
-    and on one GPU the W8A8 and W4A4 linears.  Tensor-pipe fractions use the bf16 peak of
-    MEASURED_PEAKS.json and, for int8, a cuBLAS int8 GEMM (torch._int_mm 8192^3) timed in this run."""
+def _timed_with_clocks(fn, barrier, index: int, reps: int, world: int, device) -> tuple[float, dict]:
+    """Device time per call (CUDA events, max over ranks) and the SM clocks sampled while the same
+    load runs (the load is kept up for about 0.15 s so the sampler sees it)."""
 
     import torch.distributed as dist
 
-    from xqt_b200 import quantize
-    from xqt_b200.ops.mlp import W4A16SwiGLUMLP
-
-    out: dict = {}
-    try:
-        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
-        bf16_peak = float(peaks.get("bf16_tflops_sustained", 1339.5))
-    except Exception:  # noqa: BLE001
-        bf16_peak = 1400.0
-    hidden, inter = 4096, 14336
-    mk = lambda n, k, s: quantize.quantize_w4_asymmetric(  # noqa: E731
-        (torch.randn((n, k), generator=torch.Generator().manual_seed(s)) * 0.02).to(device), group_size=GROUP)
-    block = W4A16SwiGLUMLP(mk(inter, hidden, 20), mk(inter, hidden, 21), mk(hidden, inter, 22), device=device,
-                           rank=rank, world=world)
-    mlp = []
-    for m in (1, 16, 512, 4096):
-        x = torch.randn((m, hidden), device=device, dtype=torch.bfloat16)
-        us = _time_us(lambda: block(x), barrier, reps=20 if m <= 512 else 5)
-        _log(f"mlp m={m}: {us:.1f} us")
+    sampler = ClockSampler(index)
+    with sampler:
+        us = _time_us(fn, barrier, reps)
         if world > 1:
             t = torch.tensor([us], device=device, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             us = float(t.item())
-        row = {"m": m, "us": round(us, 2)}
-        if m <= 16:
-            row["weight_gbs"] = round(3 * weight_aux_bytes(hidden, inter) / us / 1e3, 1)
-        else:
-            tf = 2.0 * m * 3 * inter * hidden / us / 1e6
-            row["tflops"] = round(tf, 1)
-            row["frac_of_bf16_sustained_peak_per_gpu"] = round(tf / world / bf16_peak, 4)
-        mlp.append(row)
-    out["w4a16_swiglu_mlp_4096x14336"] = {"world": world, "rows": mlp,
-                                          "note": "L2-resident weights (93.6 MB per copy, one copy)"}
-    del block
-    if world > 1:
-        return out
-    # int8 library peak measured here
-    a = torch.randint(-128, 127, (8192, 8192), device=device, dtype=torch.int8)
-    i8_peak = None
+        extra = min(2000, int(150e3 / max(us, 1.0)) + 1)      # the same count on every rank
+        for _ in range(extra):
+            fn()
+        barrier()
+    return us, sampler.summary()
+
+
+def _e2e_us(host_x: torch.Tensor, call, barrier, reps: int, device) -> tuple[float, int, int]:
+    """The public call with HOST buffers: pinned input -> device, the op, result -> pinned host, sync."""
+
+    y = call(host_x.to(device, non_blocking=True))
+    host_y = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+
+    def once():
+        host_y.copy_(call(host_x.to(device, non_blocking=True)), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    us = _time_us(once, barrier, reps, warm=2)
+    return us, host_x.numel() * host_x.element_size(), host_y.numel() * host_y.element_size()
+
+
+def _cpu_seconds(fn, budget_s: float = 8.0) -> tuple[float, int]:
+    """Mean wall-clock seconds of ``fn`` on the host cores: one warm-up, then up to three runs inside the budget."""
+
+    fn()
+    times = []
+    while len(times) < 3 and (not times or sum(times) + times[-1] <= budget_s):
+        start = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - start)
+    return sum(times) / len(times), len(times)
+
+
+def _record(name: str, config: dict, *, metric: str, unit: str, work: float, us: float, bound: str, peak: float,
+            peak_source: str, kernel: str, algorithmic: str, clocks: dict, e2e=None, cpu=None, extra=None) -> dict:
+    """One measured configuration in the shape of the headline line.  ``work`` is bytes (hbm) or
+    operations (tensor) of one call; value = work / time in GB/s or Tera-op/s."""
+
+    scale = 1e3 if bound == "hbm" else 1e6
+    value = work / us / scale
+    rec = {
+        "name": name, "config": config, "metric": metric, "unit": unit, "value": round(value, 2), "us_per_call": round(us, 2),
+        "roofline": {"bound": bound, "achieved": round(value, 2), "peak": round(peak, 1), "unit": unit, "frac": round(value / peak, 4),
+                     "peak_source": peak_source, "kernel": kernel, "algorithmic": algorithmic, "traffic": None},
+        "clocks": clocks,
+    }
+    if e2e is not None:
+        e_us, h2d, d2h = e2e
+        rec["e2e"] = {"value": round(work / e_us / scale, 2), "unit": unit, "us_per_call": round(e_us, 2),
+                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    if cpu is not None:
+        seconds, runs, cores, what = cpu
+        rec["cpu_baseline"] = {"value": round(work / (seconds * 1e6) / scale, 4), "unit": unit, "cores": cores, "kind": "port",
+                               "seconds_per_call": round(seconds, 4), "sample": f"{what}; 1 warm-up + {runs} run(s) at the full size"}
+    if extra:
+        rec.update(extra)
+    return rec
+
+
+def measure_other_configs(device, world, rank, barrier) -> list:
+    """The other benchmark configurations as measured records (same keys as the headline line): the
+    SwiGLU MLP block at every world size (gate/up column-parallel, down row-parallel + reduction), and on
+    one GPU the ConvRot W8A8 and SVDQuant W4A4 linears.  Device times are CUDA events with the inputs
+    resident; ``e2e`` goes through the same public call with pinned host buffers; ``cpu_baseline`` times
+    the CPU restatement of the reference at the full size (one rank, world 1 only).  Tensor-bound rows
+    use the sustained bf16 peak of MEASURED_PEAKS.json or, for int8, a cuBLAS int8 GEMM
+    (torch._int_mm 8192^3) timed in this run."""
+
+    from xqt_b200 import quantize
+    from xqt_b200.ops.mlp import W4A16SwiGLUMLP
+
+    records: list = []
+    index = device.index or 0
+    cores = os.cpu_count() or 1
+    hbm_peak, hbm_kind = measured_peak()
     try:
-        us = _time_us(lambda: torch._int_mm(a, a.t()), barrier, reps=10)
-        i8_peak = 2.0 * 8192 ** 3 / us / 1e6
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        bf16_peak, bf16_kind = float(peaks.get("bf16_tflops_sustained", 1339.5)), "of measured (sustained bf16)"
     except Exception:  # noqa: BLE001
-        pass
+        bf16_peak, bf16_kind = 1400.0, "of fallback (sustained bf16)"
+    with_cpu = world == 1 and rank == 0
+    if with_cpu:
+        torch.set_num_threads(cores)
+
+    # ---------------------------------------------------------------- W4A16 SwiGLU MLP block, hidden 4096 <-> 14336
+    hidden, inter = 4096, 14336
+    cpu_w = [quantize.quantize_w4_asymmetric(torch.randn((n, k), generator=torch.Generator().manual_seed(s)) * 0.02, group_size=GROUP)
+             for n, k, s in ((inter, hidden, 20), (inter, hidden, 21), (hidden, inter, 22))]
+    to_dev = lambda pw: type(pw)(qweight=pw.qweight.to(device), scales=pw.scales.to(device),  # noqa: E731
+                                 zero_points=pw.zero_points.to(device), metadata=pw.metadata)
+    copies = 3          # 3 x 93.6 MB (/ world) rotated: every call streams its weights from HBM
+    blocks = [W4A16SwiGLUMLP(*(to_dev(pw) for pw in cpu_w), device=device, rank=rank, world=world) for _ in range(copies)]
+    weights = 3 * weight_aux_bytes(hidden, inter)
+    reduction = "none" if world == 1 else None
+    for m in (1, 16, 512, 4096):
+        x_host = torch.randn((m, hidden), generator=torch.Generator().manual_seed(30 + m)).to(torch.bfloat16).pin_memory()
+        x = x_host.to(device)
+        activations = 2 * m * (2 * hidden + 6 * inter)      # x, gate|up out + in, gated out + in, y
+        cfg = {"workload": f"w4a16_swiglu_mlp_{hidden}x{inter}_M{m}", "group_size": GROUP, "world": world,
+               "parallelism": "single" if world == 1 else f"gate/up column-parallel, down row-parallel x{world}"}
+        if world > 1:
+            cfg["collective"] = ("peer_allreduce_kernel over NVLink peer memory: fp32 partials, %d bytes per rank per call" % (4 * m * hidden)
+                                 if m <= 16 else "ncclAllReduce(sum) of the fp32 down-projection partials, %d bytes per call" % (4 * m * hidden))
+        state = {"i": 0}
+
+        def cold(xx=x):
+            state["i"] += 1
+            return blocks[state["i"] % copies](xx)
+
+        cpu = None
+        if with_cpu:
+            from oracle import mlp as oracle_mlp  # the timed CPU baseline
+
+            xc = x_host.clone()
+            sec, runs = _cpu_seconds(lambda: oracle_mlp.forward(xc, *((pw.qweight, pw.scales, pw.zero_points) for pw in cpu_w),
+                                                                group_size=GROUP), budget_s=8.0 if m <= 512 else 12.0)
+            cpu = (sec, runs, cores, "oracle.mlp.forward (fp32 dequant + fp32 matmul per linear)")
+        if m <= 16:
+            us_cold, clocks = _timed_with_clocks(cold, barrier, index, 30, world, device)
+            us_warm, _ = _timed_with_clocks(lambda: blocks[0](x), barrier, index, 30, world, device)
+            work = weights / world + activations
+            e2e = _e2e_us(x_host, cold, barrier, 20, device) if world == 1 else None
+            records.append(_record(
+                f"cfg5_mlp_M{m}", cfg, metric="w4a16_mlp_weight_bandwidth", unit="GB/s", work=work, us=us_cold, bound="hbm",
+                peak=hbm_peak, peak_source=f"of {hbm_kind}", kernel="w4a16_decode_cl_kernel",
+                algorithmic="per rank: packed weights + scales + zero points of the three projections + activations in and out",
+                clocks=clocks, e2e=e2e, cpu=cpu,
+                extra={"l2": f"cold: {copies} weight copies rotated ({copies * weights / world / 1e6:.0f} MB per rank > 126 MB L2)",
+                       "warm": {"us_per_call": round(us_warm, 2), "frac": round(work / us_warm / 1e3 / hbm_peak, 4),
+                                "l2": "one copy, weights L2-resident between calls: not an HBM figure"}}))
+            _log(f"mlp m={m}: cold {us_cold:.1f} us, warm {us_warm:.1f} us")
+        else:
+            us, clocks = _timed_with_clocks(lambda: blocks[0](x), barrier, index, 20 if m <= 512 else 5, world, device)
+            work = 2.0 * m * 3 * inter * hidden / world
+            e2e = _e2e_us(x_host, blocks[0], barrier, 5, device) if world == 1 else None
+            records.append(_record(
+                f"cfg5_mlp_M{m}", cfg, metric="w4a16_mlp_throughput", unit="TFLOP/s", work=work, us=us, bound="tensor",
+                peak=bf16_peak, peak_source=bf16_kind, kernel="gemm_f16_kernel (after dequant_w4_f16_kernel)",
+                algorithmic="per rank: 2*M*3*inter*hidden / world", clocks=clocks, e2e=e2e, cpu=cpu))
+            _log(f"mlp m={m}: {us:.1f} us")
+    del blocks
+    torch.cuda.empty_cache()
+    if world > 1:
+        return records
+
+    # ---------------------------------------------------------------- the int8 tensor peak, measured here
+    a = torch.randint(-128, 127, (8192, 8192), device=device, dtype=torch.int8)
+    try:
+        i8_peak = 2.0 * 8192 ** 3 / _time_us(lambda: torch._int_mm(a, a.t()), barrier, reps=10) / 1e6
+        i8_kind = "in-run cuBLAS int8 GEMM (torch._int_mm 8192^3)"
+    except Exception:  # noqa: BLE001
+        i8_peak, i8_kind = 2884.7, "cuBLAS int8 GEMM measured on an earlier run (torch._int_mm failed here)"
     del a
-    out["i8_library_gemm_tops"] = None if i8_peak is None else round(i8_peak, 1)
-    from xqt_b200.ops.w8a8 import convrot_w8a8_linear, pack_convrot_w8a8_linear, w8a8_gemm
+
+    # ---------------------------------------------------------------- ConvRot W8A8, M=2048, K=N=4096
     from xqt_b200.ops.activation import rotate_quantize
+    from xqt_b200.ops.w8a8 import convrot_w8a8_linear, pack_convrot_w8a8_linear, w8a8_gemm
 
     m, n, k = 2048, 4096, 4096
     rot = quantize.regular_rotation(256)
     w = torch.randn((n, k), generator=torch.Generator().manual_seed(6)) * 0.02
     q, sc = quantize.quantize_w8_per_channel(rot.apply(w))
     packed = pack_convrot_w8a8_linear(q.t().contiguous().to(device), sc.to(device), None, dtype=torch.bfloat16)
-    x = torch.randn((m, k), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(device)
+    x_host = torch.randn((m, k), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).pin_memory()
+    x = x_host.to(device)
     codes, scales = rotate_quantize(x, rot, bits=8)
     y = torch.empty((m, n), device=device, dtype=torch.bfloat16)
+    full = lambda xx: convrot_w8a8_linear(xx, packed, rot_size=256)  # noqa: E731
     t_gemm = _time_us(lambda: w8a8_gemm(codes, scales, packed, y), barrier, reps=30)
-    t_full = _time_us(lambda: convrot_w8a8_linear(x, packed, rot_size=256), barrier, reps=30)
-    tops = 2.0 * m * n * k / t_gemm / 1e6
-    out["w8a8_convrot_2048x4096x4096"] = {
-        "gemm_us": round(t_gemm, 2), "gemm_tops": round(tops, 1), "full_forward_us": round(t_full, 2),
-        "gemm_frac_of_i8_library_peak": None if i8_peak is None else round(tops / i8_peak, 4)}
+    t_full, clocks = _timed_with_clocks(lambda: full(x), barrier, index, 30, 1, device)
+    cpu = None
+    if with_cpu:
+        from oracle import w8a8 as oracle_w8a8  # the timed CPU baseline
+
+        xc = x_host.clone()
+        sec, runs = _cpu_seconds(lambda: oracle_w8a8.linear(xc, q, sc, rot_block=256))
+        cpu = (sec, runs, cores, "oracle.w8a8.linear (Hadamard-256 rotation, per-token int8, exact integer GEMM)")
+    records.append(_record(
+        "cfg4_w8a8_convrot", {"workload": "w8a8_convrot_linear_M2048_K4096_N4096", "rotation": "regular Hadamard 256", "world": 1},
+        metric="w8a8_linear_throughput", unit="TOP/s", work=2.0 * m * n * k, us=t_full, bound="tensor", peak=i8_peak, peak_source=i8_kind,
+        kernel="gemm_i8_kernel (after rotate_quant_fast_kernel)", algorithmic="2*M*N*K over the full forward (rotate + quantise + GEMM)",
+        clocks=clocks, e2e=_e2e_us(x_host, full, barrier, 20, device), cpu=cpu,
+        extra={"gemm_only": {"us_per_call": round(t_gemm, 2), "frac": round(2.0 * m * n * k / t_gemm / 1e6 / i8_peak, 4)}}))
+    _log(f"w8a8: full {t_full:.1f} us, gemm {t_gemm:.1f} us")
+
+    # ---------------------------------------------------------------- SVDQuant W4A4, M=4096, K=3072, N=12288, rank 32
     from xqt_b200.ops.w4a4 import pack_svdq_w4a4_linear, svdq_w4a4_linear
 
     m, n, k, r = 4096, 12288, 3072, 32
     rot4 = quantize.randomized_rotation(128, seed=3)
-    layer = pack_svdq_w4a4_linear(torch.randn((n, k), device=device) * 0.02, torch.randn((r, k), device=device) * 0.05,
-                                  torch.randn((n, r), device=device) * 0.05, None, rotation=rot4)
-    x4 = torch.randn((m, k), device=device, dtype=torch.bfloat16)
-    t4 = _time_us(lambda: svdq_w4a4_linear(x4, layer, form="integer"), barrier, reps=5)
-    t4d = _time_us(lambda: svdq_w4a4_linear(x4, layer, form="dense"), barrier, reps=5)
+    gen = torch.Generator().manual_seed(3)
+    x32 = torch.randn((m, k), generator=gen)
+    x32[:, torch.randperm(k, generator=gen)[: k // 100]] *= 20.0          # 1 % outlier channels, x20
+    x_host = x32.to(torch.bfloat16).pin_memory()
+    x4 = x_host.to(device)
+    w_rot = rot4.apply(torch.randn((n, k), generator=torch.Generator().manual_seed(4)) * 0.02)
+    down32, up32, residual = quantize.svd_split(w_rot.to(device), r)     # rank-32 factors of a truncated SVD of W
+    down, up = down32.to(torch.bfloat16), up32.to(torch.bfloat16)
+    packed4, scale4, _ = quantize.quantize_residual_int4(residual, group_size=64)
+    layer = pack_svdq_w4a4_linear(None, down, up, None, packed_residual=packed4, residual_scale=scale4, rotation=rot4)
     ops4 = 2.0 * m * n * k
-    out["w4a4_svdquant_4096x12288x3072_r32"] = {
-        "integer_form": {"full_forward_us": round(t4, 2), "tops": round(ops4 / t4 / 1e6, 1),
-                         "frac_of_i8_library_peak": None if i8_peak is None else round(ops4 / t4 / 1e6 / i8_peak, 4),
-                         "note": "default: tcgen05 kind::i8, per-group fp32 scaling; meets the 1e-3 parity bar"},
-        "dense_form": {"full_forward_us": round(t4d, 2), "tflops": round(ops4 / t4d / 1e6, 1),
-                       "frac_of_bf16_sustained_peak": round(ops4 / t4d / 1e6 / bf16_peak, 4),
-                       "note": "opt-in: operands expanded to fp16, dense tcgen05 kind::f16; rel-L2 1.2e-3 at this K"}}
-    return out
+    cpu = None
+    if with_cpu:
+        from oracle import w4a4 as oracle_w4a4  # the timed CPU baseline
+
+        xc, pc, sc4, dc, uc = x_host.clone(), packed4.cpu(), scale4.cpu(), down.cpu(), up.cpu()
+        sec, runs = _cpu_seconds(lambda: oracle_w4a4.w4a4_forward(xc, pc, sc4, dc, uc, group_size=64, rot_kind=rot4.kind, rot_block=128,
+                                                                  signs=rot4.signs), budget_s=12.0)
+        cpu = (sec, runs, cores, "oracle.w4a4.w4a4_forward (rotation, group-64 int4 activations, per-slab integer GEMM, low rank)")
+    for form, kernel, note in (("integer", "gemm_w4a4_kernel", "default form: tcgen05 kind::i8, per-group fp32 scaling; meets the 1e-3 parity bar"),
+                               ("dense", "gemm_f16_kernel", "opt-in form: operands expanded to fp16; rel-L2 1.2e-3 at this K, above the 1e-3 bar")):
+        call = lambda xx, f=form: svdq_w4a4_linear(xx, layer, form=f)  # noqa: E731
+        t4, clocks = _timed_with_clocks(lambda: call(x4), barrier, index, 5, 1, device)
+        records.append(_record(
+            f"cfg3_w4a4_svdquant_{form}", {"workload": "w4a4_svdquant_linear_M4096_K3072_N12288_r32", "form": form, "world": 1,
+                                          "inputs": "1 % outlier channels x20; rank-32 factors from a truncated SVD of the rotated weight"},
+            metric="w4a4_linear_throughput", unit="TOP/s", work=ops4, us=t4, bound="tensor", peak=i8_peak, peak_source=i8_kind, kernel=kernel,
+            algorithmic="2*M*N*K over the full forward (rotate + quantise + low-rank down + GEMM with low-rank up)", clocks=clocks,
+            e2e=_e2e_us(x_host, call, barrier, 3, device), cpu=cpu if form == "integer" else None, extra={"note": note}))
+        _log(f"w4a4 {form}: {t4:.1f} us")
+    records.append({"name": "i8_library_gemm_peak", "value": round(i8_peak, 1), "unit": "TOP/s", "source": i8_kind})
+    return records
 
 
 def run_single_case(args) -> None:
