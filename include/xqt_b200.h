@@ -225,8 +225,10 @@ int xqt_b200_w4a16_decode_static_status(unsigned int* host_status, xqt_b200_stre
  *                 4: per (token, group_size) scale max(amax/7,1e-6), codes in [-8,7], scales [M, K/group_size];
  *                    group_size 0: one scale per token (ConvRotMixedPrecisionLinear's own activation form,
  *                    convrot_4bit.py:669-679), replicated into scales [M, K/64]
- *   codes         int8 [M, K] in both modes;  rotated: [M, K] act_dtype or NULL (the rotated, rounded
- *                 activation, input of the W4A4 low-rank branch)
+ *                 5: the scales and codes of 4, every code written as the byte sign << 7 | magnitude (read as
+ *                    FP8 E4M3 that is code * 2^-9 exactly): the operand form xqt_b200_w4a4_gemm consumes
+ *   codes         one byte per element [M, K] in every mode (int8 for 8 and 4);  rotated: [M, K] act_dtype or
+ *                 NULL (the rotated, rounded activation, input of the W4A4 low-rank branch)
  */
 int xqt_b200_rotate_quantize(const void* activation, const float* column_scale, void* codes,
                              float* scales, void* rotated, int m, int k, int rot_kind, int rot_block,
@@ -251,19 +253,29 @@ int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const fl
                        xqt_b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
- * W4A4 SVDQuant / ConvRot linear: after xqt_b200_rotate_quantize(quant_bits = 4, group 64)
+ * W4A4 SVDQuant / ConvRot linear: after xqt_b200_rotate_quantize(quant_bits = 5, group 64)
  *   la     = rotated [M,K] * down[32,K]^T                              (xqt_b200_lowrank_down)
  *   output = sum_g a_s[m,g] w_s[n,g] int32(sum_{k in g} a_q w_q) + la * up^T + bias   (xqt_b200_w4a4_gemm)
  * Replaces xqt_svdq_w4a4_sm89_quantize_act_fuse_lora / _gemm_lora (svdq_w4a4_sm89_kernel.cu:330-572,
  * Nunchaku main loop gemm_w4a4.cuh:833-1101, low-rank branch lora.cuh:110-243); accumulation across
  * groups is fp32 here (half precision there).
- *   act_codes   int8 [M,K] in [-8,7];  act_scales fp32 [M, K/64]
+ *   act_codes   [M,K] int4 codes in [-8,7] as sign-magnitude bytes (quant_bits 5 above): the tensor core takes
+ *               them, and the weight nibbles widened the same way, as FP8 E4M3 values code * 2^-9, whose 64-K
+ *               sums are exact in its fp32 accumulators;  act_scales fp32 [M, K/64]
  *   qweight     canonical signed-nibble storage uint8 [N, K/2] (the composite artifact's packed_residual)
- *   aux         per 128-channel tile t, xqt_b200_w4a4_aux_tile_bytes(K) bytes: fp32 [K/64][128] = w_scale/16
- *               (transposed), then fp32 [128][32] = up factors (rank padded with zeros to 32)
+ *   aux         per 128-channel tile t, xqt_b200_w4a4_aux_tile_bytes(K) bytes: fp32 [K/64][128] = w_scale * 2^18
+ *               (transposed), then the tile's up factors as a 16 KiB tensor-core operand image: row n holds
+ *               bf16 [hi(32) | lo(32)] with hi = bf16(up), lo = bf16(up - hi) (rank padded with zeros to 32), its
+ *               eight 16-byte chunks stored at chunk index c ^ (n & 7) (the 128-byte swizzle).  The rank-R branch
+ *               is la * up^T on the tensor core from such hi/lo pairs (fp32 sums, the lo x lo term dropped).
  *   down        act_dtype [32, K] (rows past the rank are zero);  la fp32 [ceil(M/128)*128, 32]
- *   K a multiple of 128, N a multiple of 8, rank <= 32.  workspace >= 256 bytes (status word).
+ *   K a multiple of 128, N a multiple of 8, rank <= 32.
+ *   workspace   xqt_b200_w4a4_workspace_bytes(M, N, K) bytes, 256-byte aligned: the status word (zero before first
+ *               use), then scratch the call fills itself: the la operand images and the weights widened to one
+ *               sign-magnitude byte each ([N, K], converted once per call by a streaming pre-pass so that the GEMM
+ *               takes both operands by TMA; the packed 4-bit storage stays the only persistent copy).
  */
+size_t xqt_b200_w4a4_workspace_bytes(int m, int n, int k);
 int xqt_b200_lowrank_down(const void* rotated, const void* down, float* la, int m, int k, int act_dtype,
                           xqt_b200_stream_t stream);
 size_t xqt_b200_w4a4_aux_tile_bytes(int k);

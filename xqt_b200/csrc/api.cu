@@ -32,8 +32,9 @@ size_t w4a16_gemm_tc_workspace_bytes(int m, int n, int k);
 bool w4a16_gemm_tc_any_zero_point(int m);
 bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size);
 int lowrank_down_launch(const void*, const void*, float*, int, int, int, cudaStream_t);
+size_t w4a4_workspace_bytes(int m, int n, int k);
 int w4a4_gemm_launch(const void*, const float*, const void*, const void*, const float*, const float*, void*, int, int, int,
-                     int, unsigned int*, cudaStream_t);
+                     int, void*, cudaStream_t);
 size_t w4a4_aux_tile_bytes(int k);
 bool w4a4_gemm_supported(int m, int n, int k);
 int rotate_quant_launch(const void*, const float*, void*, float*, void*, int, int, int, int, int, int, int, cudaStream_t);
@@ -276,9 +277,13 @@ int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const voi
                        const float* la, const float* bias, void* output, int m, int n, int k, int out_dtype,
                        void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
   if (m == 0) return 0;
-  XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
-  return w4a4_gemm_launch(act_codes, act_scales, qweight, aux, la, bias, output, m, n, k, out_dtype,
-                          reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
+  XQT_REQUIRE(m > 0 && workspace != nullptr && workspace_bytes >= w4a4_workspace_bytes(m, n, k) && ((uintptr_t)workspace & 255) == 0);
+  return w4a4_gemm_launch(act_codes, act_scales, qweight, aux, la, bias, output, m, n, k, out_dtype, workspace,
+                          (cudaStream_t)stream);
+}
+
+size_t xqt_b200_w4a4_workspace_bytes(int m, int n, int k) {
+  return m > 0 && n > 0 && k > 0 ? w4a4_workspace_bytes(m, n, k) : 256;
 }
 
 size_t xqt_b200_w4a4_dense_workspace_bytes(int m, int n, int k) {

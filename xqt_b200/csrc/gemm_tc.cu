@@ -288,6 +288,21 @@ int make_tile_map_ld(CUtensorMap* map, const void* base, CUtensorMapDataType dty
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// unswizzled byte tile: `box_rows` rows of `box_bytes` bytes out of a [rows][row_bytes] byte matrix
+int make_byte_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  if (((uintptr_t)base & 15) != 0 || row_bytes % 16 != 0 || box_bytes % 16 != 0) return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 int make_tile_map(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int esize, long long rows,
                   long long cols, int box_rows) {
   return make_tile_map_ld(map, base, dtype, esize, rows, cols, cols, box_rows);

@@ -2,21 +2,39 @@
 //   Y[m,n] = sum_g a_s[m,g] w_s[n,g] * ( sum_{k in g} a_q[m,k] w_q[n,k] )  +  sum_r la[m,r] up[n,r]  + bias[n]
 // with 64-K groups g, int4 codes on both sides, fp32 scales and an fp32 accumulation across groups.
 //
-// Blackwell has no int4 MMA: the activation codes arrive as int8 (written by the rotate+quantise
-// prologue) and the weight nibbles are widened to int8 on the fly, as 16*w (a nibble moved to the
-// high half of a byte IS the signed value times 16, no sign extension needed; the factor is folded
-// into the weight scale).  Each 64-K slab is two tcgen05.mma kind::i8 steps into its own int32
-// tensor-memory buffer (a ring of four); the epilogue warps drain every slab, convert exactly
-// (|sum| <= 2^16) and fold it into fp32 register accumulators with a_s*w_s -- the per-slab scaling
-// the reference does in half precision (jit/include/nunchaku/gemm_base.cuh:367-446,
-// gemm_w4a4.cuh:833-930), here in fp32.  The rank-R branch and the bias are added at the end of
-// the tile (reference: lora.cuh:110-243 "LoRA up").  That per-slab drain is CUDA-core work of
-// M*N*K/64 scaled adds and bounds the kernel well below the int8 tensor peak; it is what exact
-// per-group scales cost.
+// Operands.  Blackwell has no int4 MMA.  Both operands go to the tensor core as FP8 E4M3 bytes of the form
+// sign << 7 | magnitude: for magnitudes 0..15 that byte IS the E4M3 number magnitude * 2^-9 (subnormals and
+// the first binade are linear), so an int4 code becomes an exact FP8 value without a table.  The activation
+// codes arrive in that form from the rotate+quantise prologue.  The packed two's-complement weight nibbles
+// are widened to the same bytes by a streaming pre-pass (w44_expand_kernel, N*K bytes of scratch that stay
+// in L2) -- each weight is converted once per call, not once per 128-row tile of activations, and both
+// operands of the GEMM then come in by TMA.  Every product is an integer times 2^-18, a 64-K slab sums to
+// at most 2^12 of them, so the fp32 accumulation of tcgen05.mma kind::f8f6f4 is exact and equals the
+// reference's int32 group sum (jit/include/nunchaku/gemm_base.cuh:367-446); 2^18 is folded into the weight
+// scale on the host.
 //
-// Warp roles (448 threads): warp 0 TMA producer (activation codes, per-tile scales / low-rank
-// factors), warp 1 MMA issuer, warps 2-9 epilogue (quarter = warp % 4, column half = (warp-2)/4),
-// warps 10-13 weight unpack (one thread per weight row, bytes prefetched one stage ahead).
+// Per-group scales.  A 128-K stage is two slabs; each slab is two MMAs (K = 32) into its own 128 columns of
+// tensor memory, and a stage's two slabs are handed to the drain warps together (two 256-column buffers:
+// a barrier test costs about 200 cycles, so there is one hand-over per stage and warp, not per slab).
+// Sixteen drain warps fold the slabs into fp32 register accumulators with a_s*w_s -- the per-slab scaling
+// the reference does in half precision (gemm_w4a4.cuh:833-930), here in fp32: one multiply and one fused
+// multiply-add per element (the packed f32x2 forms measured no faster).  That drain is CUDA-core work,
+// M*N*K/64 scaled adds (two fp32 pipe operations each): 256 cycles per 128x128 slab at 128 lanes per SM
+// and clock, against about 210 for the slab's MMAs; exact per-group scales bound the kernel near 0.8 of
+// the tensor rate.
+//
+// Rank-R branch (reference: lora.cuh:110-243 "LoRA up").  la * up^T is one more slab per tile, computed by
+// the tensor core from bf16 hi/lo splits of both factors (hi x hi + lo x hi + hi x lo, fp32 sums; the
+// dropped lo x lo term is 2^-18 relative): six K = 16 steps over two 128-row operand images.
+//
+// Warp roles (576 threads): warp 0 TMA producer (both operand tiles per stage, weight scales per tile, the
+// two rank-R operand images per tile), warp 1 MMA issuer, warps 2-17 drain (tensor-memory lane quarter =
+// warp % 4, 32-column quarter = (warp - 2) / 4).  A drain warp reads a slab in the accumulator-fragment
+// distribution (tcgen05.ld shape 16x256b): lane t holds rows t/4 + {0, 8, 16, 24} and, of each 8-column
+// group, columns 2*(t%4), 2*(t%4)+1.  A thread then needs 4 activation scales and 8 weight scales per slab;
+// in the one-row-per-thread shape it would need 32 weight scales, every lane the same ones, and those
+// broadcast loads alone (128 bytes of register write-back per lane and slab) take more shared-memory pipe
+// time than the slab's MMAs.
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -28,104 +46,284 @@ int make_tile_map(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
                   long long cols, int box_rows);
 
 namespace w4a4 {
-constexpr int kBM = 128, kBN = 128, kStageK = 128, kGroup = 64, kRank = 32;
-constexpr int kThreads = 448;
-constexpr int kMaxStages = 6;
-constexpr int kSlabBufs = 4;
+constexpr int kBM = 128, kBN = 128, kStageK = 128, kRank = 32;
+constexpr int kDrainWarps = 16, kFirstDrainWarp = 2;
+constexpr int kThreads = (kFirstDrainWarp + kDrainWarps) * 32;      // 576
+constexpr int kMaxStages = 5;
+constexpr int kPairBufs = 2;                                        // tensor-memory buffers of two slabs (256 columns)
 constexpr int kABytes = kBM * 128, kBBytes = kBN * 128, kStageBytes = kABytes + kBBytes;
-constexpr int kLaBytes = kBM * kRank * 4, kUpBytes = kBN * kRank * 4;
-constexpr int kSmemBudget = 220 * 1024;
+constexpr int kUpBytes = kBN * kRank * 4, kLaBytes = kBM * kRank * 4;
+constexpr int kSmemBudget = 226 * 1024;
 enum Status : unsigned int { kTimeout = 64 };
+// barrier slots
+constexpr int kBarFull = 0, kBarEmpty = kBarFull + kMaxStages;
+constexpr int kBarPairFull = kBarEmpty + kMaxStages, kBarPairEmpty = kBarPairFull + kPairBufs;
+constexpr int kBarScaleFull = kBarPairEmpty + kPairBufs, kBarScaleEmpty = kBarScaleFull + 2;
+constexpr int kBarEpiFull = kBarScaleEmpty + 2, kBarEpiEmpty = kBarEpiFull + 1, kBarCount = kBarEpiEmpty + 1;
 }  // namespace w4a4
 
 struct W4A4Params {
   int m, n, k, groups;
-  int mtiles, ntiles, kstages, stages, aux_bufs;
+  int mtiles, ntiles, kstages, stages, scale_bufs;
   int aux_tile_bytes;          // groups * 512 + kUpBytes
-  const uint8_t* qweight;      // canonical signed nibbles [N, K/2]
-  const float* a_scale;        // [M, groups]
-  const uint8_t* aux;          // per n-tile: w_scale/16 as [groups][128] fp32, then up factors [128][32] fp32
-  const float* la;             // [mtiles*128, 32] fp32 (zeros when there is no low-rank branch)
+  const float* a_scale_t;      // [groups, mtiles*128]: the activation scales transposed (rows past M are zero)
+  const uint8_t* aux;          // per n-tile: w_scale * 2^18 as [groups][128] fp32, then the up factors as a 128-row operand image
+  const uint8_t* la_tiles;     // per m-tile: the low-rank activations as a 128-row operand image (see w44_la_image_kernel)
   const float* bias;
   void* out;
   unsigned int* status;
 };
 
-template <typename OutT>
-__device__ __forceinline__ void w44_store8(OutT* dst, const float (&v)[8]);
-template <>
-__device__ __forceinline__ void w44_store8<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[8]) {
-  uint4 o;
-  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-  __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
-  o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
-  o.z = *reinterpret_cast<uint32_t*>(&c); o.w = *reinterpret_cast<uint32_t*>(&d);
-  *reinterpret_cast<uint4*>(dst) = o;
+__device__ __forceinline__ uint32_t w44_pack2(__nv_bfloat16*, float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
-template <>
-__device__ __forceinline__ void w44_store8<__half>(__half* dst, const float (&v)[8]) {
-  uint4 o;
-  __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
-  __half2 c = __floats2half2_rn(v[4], v[5]), d = __floats2half2_rn(v[6], v[7]);
-  o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
-  o.z = *reinterpret_cast<uint32_t*>(&c); o.w = *reinterpret_cast<uint32_t*>(&d);
-  *reinterpret_cast<uint4*>(dst) = o;
+__device__ __forceinline__ uint32_t w44_pack2(__half*, float a, float b) {
+  const __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ unsigned long long w44_lds64(uint32_t addr) {
+  unsigned long long v;
+  asm volatile("ld.shared.b64 %0, [%1];\n" : "=l"(v) : "r"(addr));
+  return v;
 }
 
-// two packed words (16 nibbles, k0..k15) -> 16 int8 values 16*w in K order
-__device__ __forceinline__ uint4 widen16(uint32_t w0, uint32_t w1) {
-  const uint32_t e0 = (w0 << 4) & 0xF0F0F0F0u, o0 = w0 & 0xF0F0F0F0u;
-  const uint32_t e1 = (w1 << 4) & 0xF0F0F0F0u, o1 = w1 & 0xF0F0F0F0u;
-  uint4 r;
-  r.x = __byte_perm(e0, o0, 0x5140);
-  r.y = __byte_perm(e0, o0, 0x7362);
-  r.z = __byte_perm(e1, o1, 0x5140);
-  r.w = __byte_perm(e1, o1, 0x7362);
-  return r;
+// one packed word (8 two's-complement nibbles, k0..k7) -> 8 bytes sign << 7 | |w| in K order.
+// Per nibble: mask = 0xF where negative; (w ^ mask) + 1 negates it (no carry leaves a nibble: the
+// complemented value of a negative nibble is at most 7).
+__device__ __forceinline__ uint2 signmag8(uint32_t w) {
+  const uint32_t s = w & 0x88888888u, t = s >> 3;
+  const uint32_t mag = (w ^ (s | (s - t))) + t;
+  const uint32_t e = (mag & 0x0F0F0F0Fu) | ((s << 4) & 0x80808080u);
+  const uint32_t o = ((mag >> 4) & 0x0F0F0F0Fu) | (s & 0x80808080u);
+  return make_uint2(__byte_perm(e, o, 0x5140), __byte_perm(e, o, 0x7362));
+}
+
+// packed nibbles [N, K/2] -> sign-magnitude bytes [N, K]; a thread converts 16 packed bytes (32 weights)
+__global__ void __launch_bounds__(256) w44_expand_kernel(const uint4* __restrict__ packed, uint4* __restrict__ bytes, size_t chunks) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 v = __ldg(packed + i);
+    const uint2 a = signmag8(v.x), b = signmag8(v.y), c = signmag8(v.z), d = signmag8(v.w);
+    bytes[2 * i] = make_uint4(a.x, a.y, b.x, b.y);
+    bytes[2 * i + 1] = make_uint4(c.x, c.y, d.x, d.y);
+  }
+}
+
+// The drain role as a function of its own (not inlined): its register allocation then holds nothing of the
+// other roles' state.
+template <typename OutT>
+__device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, uint32_t bar0, uint32_t scale_addr,
+                                       volatile unsigned int* s_abort) {
+  using namespace w4a4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nsb = p.scale_bufs;
+  const int scale_bytes = p.groups * 512;
+  const int total_tiles = p.mtiles * p.ntiles;
+  auto bar = [&](int slot) { return bar0 + 8u * (uint32_t)slot; };
+  auto guarded_wait = [&](uint32_t b, uint32_t parity) {
+    if (*s_abort == 0u && !mbar_wait(b, parity)) {
+      *s_abort = 1u;
+      atomicExch(p.status, (unsigned int)kTimeout);
+    }
+  };
+  const int quarter = warp & 3, colq = (warp - kFirstDrainWarp) >> 2;
+  const int rq = lane >> 2, c2 = lane & 3;
+  const uint32_t tlane = tmem_base + colq * 32 + ((uint32_t)(quarter * 32) << 16);
+  uint32_t local = 0, pair = 0;                       // pair: hand-overs so far (one per stage, one per rank-R slab)
+  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+    const int mt = tile % p.mtiles, nt = tile / p.mtiles;
+    const int ab = local % nsb;
+    // activation scales: the scalars of the next slab are requested while this one is folded
+    const int row0 = mt * kBM + quarter * 32 + rq;       // the thread's rows are row0 + 8 i
+    const int mpad = p.mtiles * kBM;
+    const float* sp = p.a_scale_t + row0;                // one slab's scales of the four rows: sp[8 i]; next slab: + mpad
+    float sn[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sn[i] = __ldg(sp + 8 * i);
+    // Two 16-register buffers: rows 0-15 and rows 16-31 of the warp's 32 x 32 part of a slab (one tcgen05.ld each).
+    // While one is folded the other is in flight: a tensor-memory load takes about 150 cycles, and one warp's
+    // share of the arithmetic between two waits has to cover it.
+    uint32_t ra[16], rb[16];
+    guarded_wait(bar(kBarPairFull + pair % kPairBufs), (pair / kPairBufs) & 1);
+    tc_fence_after();
+    tmem_ld_16x256b_x4(tlane + (pair % kPairBufs) * (2 * kBN), ra);
+    guarded_wait(bar(kBarScaleFull + ab), (local / nsb) & 1);
+    const uint32_t sw = scale_addr + (uint32_t)ab * (uint32_t)scale_bytes + (colq * 32 + 2 * c2) * 4;     // [groups][128] fp32
+    float acc[32];                                    // [row i][column group j][x]: acc[8 i + 2 j + x]
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    // 16 rows (i0, i0 + 1) x 32 columns: acc += r * (a_s[row] * w_s[column])
+    auto fold = [&](const uint32_t (&r)[16], const float2 (&ws)[4], const float (&sa)[4], int i0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int ii = 0; ii < 2; ++ii) {
+          const int i = i0 + ii;
+          acc[8 * i + 2 * j] = fmaf(__uint_as_float(r[4 * j + 2 * ii]), __fmul_rn(sa[i], ws[j].x), acc[8 * i + 2 * j]);
+          acc[8 * i + 2 * j + 1] = fmaf(__uint_as_float(r[4 * j + 2 * ii + 1]), __fmul_rn(sa[i], ws[j].y), acc[8 * i + 2 * j + 1]);
+        }
+      }
+    };
+    const int kstages = p.kstages;
+    for (int ks = 0; ks < kstages; ++ks, ++pair) {
+      const int pb = pair % kPairBufs;
+      const uint32_t npair = pair + 1;
+      // A barrier test answers after about 200 cycles even when the phase is complete: ask for the next
+      // hand-over now and read the answer after this stage's arithmetic.
+      const bool next_full = mbar_try_wait(bar(kBarPairFull + npair % kPairBufs), (npair / kPairBufs) & 1);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t swg = sw + (uint32_t)(2 * ks + h) * (kBN * 4);
+        const uint32_t tslab = tlane + pb * (2 * kBN) + h * kBN;
+        float2 ws[4];
+        float sa[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {                  // columns 8 j + 2 c2, + 1
+          const unsigned long long w = w44_lds64(swg + j * 32);
+          f32x2_unpack(w, ws[j].x, ws[j].y);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sa[i] = sn[i];
+        if (h == 0 || ks + 1 < kstages) {
+          sp += mpad;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sn[i] = __ldg(sp + 8 * i);                // the next slab's, a slab ahead
+        }
+        tmem_wait_ld_dep(ra);                          // rows 0-15 of the slab
+        tmem_ld_16x256b_x4(tslab + (16u << 16), rb);
+        fold(ra, ws, sa, 0);
+        tmem_wait_ld_dep(rb);                          // rows 16-31
+        if (h == 0) {
+          tmem_ld_16x256b_x4(tslab + kBN, ra);         // the stage's second slab
+        } else {
+          tc_fence_before();                           // both slabs are in registers: hand the buffer back
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarPairEmpty + pb));
+          // the next hand-over: the following stage, or the tile's rank-R slab
+          if (!next_full) guarded_wait(bar(kBarPairFull + npair % kPairBufs), (npair / kPairBufs) & 1);
+          tc_fence_after();
+          tmem_ld_16x256b_x4(tlane + (npair % kPairBufs) * (2 * kBN), ra);
+        }
+        fold(rb, ws, sa, 2);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(kBarScaleEmpty + ab));       // the tile's weight scales are consumed
+    // rank-R branch: one more slab (la * up^T from the tensor core), added as it is; its first half is in flight
+    {
+      const int pb = pair % kPairBufs;
+      const uint32_t tslab = tlane + pb * (2 * kBN);
+      tmem_wait_ld_dep(ra);
+      tmem_ld_16x256b_x4(tslab + (16u << 16), rb);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int ii = 0; ii < 2; ++ii) {
+          acc[8 * ii + 2 * j] += __uint_as_float(ra[4 * j + 2 * ii]);
+          acc[8 * ii + 2 * j + 1] += __uint_as_float(ra[4 * j + 2 * ii + 1]);
+        }
+      }
+      tmem_wait_ld_dep(rb);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarPairEmpty + pb));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int ii = 0; ii < 2; ++ii) {
+          acc[8 * (2 + ii) + 2 * j] += __uint_as_float(rb[4 * j + 2 * ii]);
+          acc[8 * (2 + ii) + 2 * j + 1] += __uint_as_float(rb[4 * j + 2 * ii + 1]);
+        }
+      }
+      ++pair;
+    }
+    // bias and store.  The four lanes of a row group exchange their column pairs so that each stores eight
+    // adjacent columns (16 bytes) of one row: lane c2 ends up with column group j = c2 of rows row0 + 8 i.
+    OutT* out = reinterpret_cast<OutT*>(p.out);
+    const int col = nt * kBN + colq * 32 + 8 * c2;
+    float b8[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) b8[e] = (p.bias != nullptr && col < p.n) ? __ldg(p.bias + col + e) : 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // before: v[j] holds columns 8 j + 2 c2 (+1); after: columns 8 c2 + 2 j (+1).
+      unsigned long long v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = f32x2_pack(acc[8 * i + 2 * j], acc[8 * i + 2 * j + 1]);
+      // 4 x 4 transpose over the lanes c2 = 0..3 in two exchange steps
+#pragma unroll
+      for (int step = 1; step <= 2; step <<= 1) {
+        const bool upper = (c2 & step) != 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if ((j & step) == 0) {
+            // lanes without the bit keep [j] and give [j + step]; lanes with it keep [j + step] and give [j]
+            const unsigned long long give = upper ? v[j] : v[j + step];
+            const unsigned long long got = __shfl_xor_sync(0xffffffffu, give, step);
+            if (upper) v[j] = got; else v[j + step] = got;
+          }
+        }
+      }
+      const int row = row0 + 8 * i;
+      if (row < p.m && col < p.n) {            // N is a multiple of 8: the eight columns are inside together
+        float f[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) f32x2_unpack(v[q], f[2 * q], f[2 * q + 1]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += b8[e];
+        OutT* dst = out + (size_t)row * p.n + col;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w44_pack2(dst, f[0], f[1]), w44_pack2(dst, f[2], f[3]), w44_pack2(dst, f[4], f[5]),
+                                                    w44_pack2(dst, f[6], f[7]));
+      }
+    }
+  }
 }
 
 template <typename OutT>
 __global__ void __launch_bounds__(w4a4::kThreads, 1)
-gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const W4A4Params p) {
+gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ W4A4Params p) {
   using namespace w4a4;
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) unsigned long long bars[3 * kMaxStages + 2 * kSlabBufs + 4];
+  __shared__ __align__(8) unsigned long long bars[kBarCount];
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile unsigned int s_abort;
 
-  constexpr uint32_t kTmemCols = kSlabBufs * kBN;   // 512
-  constexpr uint32_t kIdesc = umma_idesc(kAccS32, kFmtS8, kFmtS8, kBM, kBN);
+  constexpr uint32_t kTmemCols = kPairBufs * 2 * kBN;   // 512
+  constexpr uint32_t kIdesc = umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, kBM, kBN);
+  constexpr uint32_t kIdescLora = umma_idesc(kAccF32, kFmtBF16, kFmtBF16, kBM, kBN);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
   const int ns = p.stages;
+  // dynamic shared memory: operand stages | weight scales (x scale_bufs) | up-factor image | low-rank activation image
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
-  const int aux_bytes = p.aux_tile_bytes + kLaBytes;            // one buffer: w scales, up factors, la tile
-  unsigned char* aux_base = tiles + (size_t)ns * kStageBytes;
-  auto full_bar = [&](int s) { return smem_addr(&bars[s]); };
-  auto bready_bar = [&](int s) { return smem_addr(&bars[kMaxStages + s]); };
-  auto empty_bar = [&](int s) { return smem_addr(&bars[2 * kMaxStages + s]); };
-  auto sfull_bar = [&](int b) { return smem_addr(&bars[3 * kMaxStages + b]); };
-  auto sempty_bar = [&](int b) { return smem_addr(&bars[3 * kMaxStages + kSlabBufs + b]); };
-  auto afull_bar = [&](int b) { return smem_addr(&bars[3 * kMaxStages + 2 * kSlabBufs + b]); };
-  auto aempty_bar = [&](int b) { return smem_addr(&bars[3 * kMaxStages + 2 * kSlabBufs + 2 + b]); };
+  const int scale_bytes = p.groups * 512;
+  unsigned char* scale_base = tiles + (size_t)ns * kStageBytes;
+  const int nsb = p.scale_bufs;
+  unsigned char* up_base = scale_base + (size_t)nsb * scale_bytes;
+  unsigned char* la_base = up_base + kUpBytes;
+  const uint32_t bar0 = smem_addr(&bars[0]);
+  auto bar = [&](int slot) { return bar0 + 8u * (uint32_t)slot; };
 
   if (threadIdx.x == 0) {
     s_abort = 0u;
     for (int s = 0; s < ns; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(bready_bar(s), 4);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(bar(kBarFull + s), 1);
+      mbar_init(bar(kBarEmpty + s), 1);
     }
-    for (int b = 0; b < kSlabBufs; ++b) {
-      mbar_init(sfull_bar(b), 1);
-      mbar_init(sempty_bar(b), 8);
+    for (int b = 0; b < kPairBufs; ++b) {
+      mbar_init(bar(kBarPairFull + b), 1);
+      mbar_init(bar(kBarPairEmpty + b), kDrainWarps);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(afull_bar(b), 1);
-      mbar_init(aempty_bar(b), 8);
+      mbar_init(bar(kBarScaleFull + b), 1);
+      mbar_init(bar(kBarScaleEmpty + b), kDrainWarps);
     }
+    mbar_init(bar(kBarEpiFull), 1);
+    mbar_init(bar(kBarEpiEmpty), 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
   }
   if (warp == 1) {
     tmem_alloc(smem_addr(&s_tmem_base), kTmemCols);
@@ -136,10 +334,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const W4A4Params p) {
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   const int total_tiles = p.mtiles * p.ntiles;
-  const int nab = p.aux_bufs;
 
-  auto guarded_wait = [&](uint32_t bar, uint32_t parity) {
-    if (s_abort == 0u && !mbar_wait(bar, parity)) {
+  // Every wait is bounded: when one runs out the CTA stops waiting anywhere, reports and drains out.
+  auto guarded_wait = [&](uint32_t b, uint32_t parity) {
+    if (s_abort == 0u && !mbar_wait(b, parity)) {
+      s_abort = 1u;
+      atomicExch(p.status, (unsigned int)kTimeout);
+    }
+  };
+  // two independent barrier tests in flight at once (each takes about 200 cycles to answer)
+  auto guarded_wait2 = [&](uint32_t b0, uint32_t parity0, uint32_t b1, uint32_t parity1) {
+    if (s_abort == 0u && !mbar_wait2(b0, parity0, b1, parity1)) {
       s_abort = 1u;
       atomicExch(p.status, (unsigned int)kTimeout);
     }
@@ -151,223 +356,205 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const W4A4Params p) {
       uint32_t it = 0, local = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
         const int mt = tile % p.mtiles, nt = tile / p.mtiles;
-        const int ab = local % nab;
-        guarded_wait(aempty_bar(ab), ((local / nab) & 1) ^ 1);
-        unsigned char* ax = aux_base + (size_t)ab * aux_bytes;
-        mbar_expect_tx(afull_bar(ab), aux_bytes);
-        bulk_g2s(smem_addr(ax), p.aux + (size_t)nt * p.aux_tile_bytes, p.aux_tile_bytes, afull_bar(ab));
-        bulk_g2s(smem_addr(ax + p.aux_tile_bytes), p.la + (size_t)mt * kBM * kRank, kLaBytes, afull_bar(ab));
+        const int ab = local % nsb;
+        guarded_wait(bar(kBarScaleEmpty + ab), ((local / nsb) & 1) ^ 1);
+        mbar_expect_tx(bar(kBarScaleFull + ab), scale_bytes);
+        bulk_g2s(smem_addr(scale_base + (size_t)ab * scale_bytes), p.aux + (size_t)nt * p.aux_tile_bytes, scale_bytes,
+                 bar(kBarScaleFull + ab));
         for (int ks = 0; ks < p.kstages; ++ks, ++it) {
           const int s = it % ns;
-          guarded_wait(empty_bar(s), ((it / ns) & 1) ^ 1);
-          mbar_expect_tx(full_bar(s), kABytes);
-          tma_load_2d(smem_addr(tiles + (size_t)s * kStageBytes), &tm_a, ks * kStageK, mt * kBM, full_bar(s));
+          guarded_wait(bar(kBarEmpty + s), ((it / ns) & 1) ^ 1);
+          unsigned char* st = tiles + (size_t)s * kStageBytes;
+          mbar_expect_tx(bar(kBarFull + s), kStageBytes);
+          tma_load_2d(smem_addr(st), &tm_a, ks * kStageK, mt * kBM, bar(kBarFull + s));
+          tma_load_2d(smem_addr(st + kABytes), &tm_b, ks * kStageK, nt * kBN, bar(kBarFull + s));
         }
+        // the tile's rank-R operand images; the MMAs of the previous tile's rank-R slab have released the buffers
+        guarded_wait(bar(kBarEpiEmpty), (local & 1) ^ 1);
+        mbar_expect_tx(bar(kBarEpiFull), kUpBytes + kLaBytes);
+        bulk_g2s(smem_addr(up_base), p.aux + (size_t)nt * p.aux_tile_bytes + scale_bytes, kUpBytes, bar(kBarEpiFull));
+        bulk_g2s(smem_addr(la_base), p.la_tiles + (size_t)mt * kLaBytes, kLaBytes, bar(kBarEpiFull));
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      uint32_t it = 0, slab = 0;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-          const int s = it % ns;
-          guarded_wait(bready_bar(s), (it / ns) & 1);
+      uint32_t it = 0, pair = 0, local = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+        for (int ks = 0; ks < p.kstages; ++ks, ++it, ++pair) {
+          const int s = it % ns, pb = pair % kPairBufs;
+          guarded_wait2(bar(kBarFull + s), (it / ns) & 1, bar(kBarPairEmpty + pb), ((pair / kPairBufs) & 1) ^ 1);
           tc_fence_after();
           const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
           const uint64_t adesc = umma_desc_sw128(a_addr), bdesc = umma_desc_sw128(a_addr + kABytes);
 #pragma unroll
-          for (int h = 0; h < 2; ++h, ++slab) {          // two 64-K slabs per stage
-            const int sb = slab % kSlabBufs;
-            guarded_wait(sempty_bar(sb), ((slab / kSlabBufs) & 1) ^ 1);
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + sb * kBN;
-            umma_ss<true>(d_tmem, adesc + h * 4, bdesc + h * 4, kIdesc, 0u);
-            umma_ss<true>(d_tmem, adesc + h * 4 + 2, bdesc + h * 4 + 2, kIdesc, 1u);
-            umma_commit(sfull_bar(sb));
+          for (int h = 0; h < 2; ++h) {                  // two 64-K slabs per stage, 128 columns each
+            const uint32_t d_tmem = tmem_base + pb * (2 * kBN) + h * kBN;
+            umma_ss_f8(d_tmem, adesc + h * 4, bdesc + h * 4, kIdesc, 0u);
+            umma_ss_f8(d_tmem, adesc + h * 4 + 2, bdesc + h * 4 + 2, kIdesc, 1u);
           }
-          umma_commit(empty_bar(s));
+          umma_commit(bar(kBarPairFull + pb));
+          umma_commit(bar(kBarEmpty + s));
+        }
+        // the rank-R branch as one more slab: [la_hi | la_lo] x [up_hi | up_lo]^T without the lo x lo term, bf16
+        // operands (kind::f16), six K = 16 steps over the two 128-byte-row images the producer has brought in
+        {
+          const int pb = pair % kPairBufs;
+          guarded_wait2(bar(kBarEpiFull), local & 1, bar(kBarPairEmpty + pb), ((pair / kPairBufs) & 1) ^ 1);
+          tc_fence_after();
+          const uint64_t ladesc = umma_desc_sw128(smem_addr(la_base)), updesc = umma_desc_sw128(smem_addr(up_base));
+          const uint32_t d_tmem = tmem_base + pb * (2 * kBN);
+          umma_ss<false>(d_tmem, ladesc + 0, updesc + 0, kIdescLora, 0u);     // hi x hi
+          umma_ss<false>(d_tmem, ladesc + 2, updesc + 2, kIdescLora, 1u);
+          umma_ss<false>(d_tmem, ladesc + 4, updesc + 0, kIdescLora, 1u);     // lo x hi
+          umma_ss<false>(d_tmem, ladesc + 6, updesc + 2, kIdescLora, 1u);
+          umma_ss<false>(d_tmem, ladesc + 0, updesc + 4, kIdescLora, 1u);     // hi x lo
+          umma_ss<false>(d_tmem, ladesc + 2, updesc + 6, kIdescLora, 1u);
+          umma_commit(bar(kBarPairFull + pb));
+          umma_commit(bar(kBarEpiEmpty));                                      // the two images may be overwritten
+          ++pair;
         }
       }
-    }
-  } else if (warp < 10) {
-    // ---------------------------------------------------------------- epilogue warps
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
-    OutT* out = reinterpret_cast<OutT*>(p.out);
-    uint32_t local = 0, slab = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
-      const int mt = tile % p.mtiles, nt = tile / p.mtiles;
-      const int ab = local % nab;
-      const int row_in_tile = quarter * 32 + lane;
-      const int row = mt * kBM + row_in_tile;
-      const float* sa = p.a_scale + (size_t)(row < p.m ? row : p.m - 1) * p.groups;
-      guarded_wait(afull_bar(ab), (local / nab) & 1);
-      const unsigned char* ax = aux_base + (size_t)ab * aux_bytes;
-      const float* sw = reinterpret_cast<const float*>(ax) + half * 64;            // [groups][128]
-      float acc[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-      float sa_next = __ldg(sa);
-      for (int g = 0; g < p.groups; ++g, ++slab) {
-        const int sb = slab % kSlabBufs;
-        const float sa_g = sa_next;
-        if (g + 1 < p.groups) sa_next = __ldg(sa + g + 1);
-        guarded_wait(sfull_bar(sb), (slab / kSlabBufs) & 1);
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + sb * kBN + half * 64 + ((uint32_t)(quarter * 32) << 16);
-        const float* swg = sw + (size_t)g * kBN;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_wait_ld();
-          if (c == 1) {          // both halves are in registers: hand the buffer back to the MMA issuer
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sempty_bar(sb));
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 w4 = *reinterpret_cast<const float4*>(swg + c * 32 + j * 4);
-            const float ws[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              // exact int -> float for |v| < 2^22: bias the exponent, subtract the bias
-              const float f = __int_as_float((int)r[j * 4 + e] + 0x4B400000) - 12582912.f;
-              acc[c * 32 + j * 4 + e] = fmaf(f, sa_g * ws[e], acc[c * 32 + j * 4 + e]);
-            }
-          }
-        }
-      }
-      // rank-R branch, bias, store
-      const float* la = reinterpret_cast<const float*>(ax + p.aux_tile_bytes) + row_in_tile * kRank;
-      const float* up = reinterpret_cast<const float*>(ax + (size_t)p.groups * 512) + (size_t)half * 64 * kRank;
-      float lar[kRank];
-#pragma unroll
-      for (int r4 = 0; r4 < kRank / 4; ++r4) {
-        const float4 v = *reinterpret_cast<const float4*>(la + r4 * 4);
-        lar[r4 * 4] = v.x; lar[r4 * 4 + 1] = v.y; lar[r4 * 4 + 2] = v.z; lar[r4 * 4 + 3] = v.w;
-      }
-      const int col0 = nt * kBN + half * 64;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {   // fully unrolled: acc[] must stay in registers
-        float v[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float* u = up + (size_t)(j * 8 + e) * kRank;
-          float s = 0.f;
-#pragma unroll
-          for (int r4 = 0; r4 < kRank / 4; ++r4) {
-            const float4 uu = *reinterpret_cast<const float4*>(u + r4 * 4);
-            s = fmaf(lar[r4 * 4], uu.x, s); s = fmaf(lar[r4 * 4 + 1], uu.y, s);
-            s = fmaf(lar[r4 * 4 + 2], uu.z, s); s = fmaf(lar[r4 * 4 + 3], uu.w, s);
-          }
-          v[e] = acc[j * 8 + e] + s;
-        }
-        const int col = col0 + j * 8;
-        if (row < p.m && col < p.n) {
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] += __ldg(p.bias + col + e);
-          }
-          w44_store8<OutT>(out + (size_t)row * p.n + col, v);
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(aempty_bar(ab));
     }
   } else {
-    // ---------------------------------------------------------------- weight unpack warps (one thread per row)
-    const int row_in_tile = threadIdx.x - 10 * 32;   // 0..127
-    uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int nt = tile / p.mtiles;
-      int row = nt * kBN + row_in_tile;
-      row = row < p.n ? row : p.n - 1;
-      const uint4* wrow = reinterpret_cast<const uint4*>(p.qweight + (size_t)row * (p.k / 2));
-      uint4 nxt[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) nxt[c] = __ldg(wrow + c);
-      for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-        const int s = it % ns;
-        uint4 cur[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) cur[c] = nxt[c];
-        if (ks + 1 < p.kstages) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) nxt[c] = __ldg(wrow + (size_t)(ks + 1) * 4 + c);
-        }
-        guarded_wait(full_bar(s), (it / ns) & 1);
-        unsigned char* brow = tiles + (size_t)s * kStageBytes + kABytes + row_in_tile * 128;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {          // 16 raw bytes = 32 K = two 16-byte chunks of the swizzled row
-          const int j0 = c * 2;
-          *reinterpret_cast<uint4*>(brow + (((j0) ^ (row_in_tile & 7)) << 4)) = widen16(cur[c].x, cur[c].y);
-          *reinterpret_cast<uint4*>(brow + (((j0 + 1) ^ (row_in_tile & 7)) << 4)) = widen16(cur[c].z, cur[c].w);
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bready_bar(s));
-      }
-    }
+    // ---------------------------------------------------------------- drain warps
+    w44_drain<OutT>(p, tmem_base, bar0, smem_addr(scale_base), &s_abort);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-// ----------------------------------------------------------------------------------------- host
+// Operand image of the low-rank activations for one 128-row tile: row r holds [hi(32) | lo(32)] bf16 with
+// hi = bf16(v), lo = bf16(v - hi) -- 128 bytes, stored in the 128-byte-swizzled order the MMA descriptors read
+// (16-byte chunk c of row r at chunk c ^ (r & 7)).  The up factors get the same image on the host, once.
+__global__ void __launch_bounds__(128) w44_la_image_kernel(const float* __restrict__ la, uint8_t* __restrict__ tiles) {
+  const int r = threadIdx.x;
+  const float4* src = reinterpret_cast<const float4*>(la + ((size_t)blockIdx.x * 128 + r) * w4a4::kRank);
+  uint8_t* dst = tiles + (size_t)blockIdx.x * w4a4::kLaBytes + (size_t)r * 128;
+  uint32_t hi[16], lo[16];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float4 v = __ldg(src + q);
+    const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const __nv_bfloat16 h0 = __float2bfloat16_rn(f[2 * e]), h1 = __float2bfloat16_rn(f[2 * e + 1]);
+      const __nv_bfloat16 l0 = __float2bfloat16_rn(f[2 * e] - __bfloat162float(h0)), l1 = __float2bfloat16_rn(f[2 * e + 1] - __bfloat162float(h1));
+      hi[2 * q + e] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+      lo[2 * q + e] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+    *reinterpret_cast<uint4*>(dst + (((c + 4) ^ (r & 7)) << 4)) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+  }
+}
 
-bool w4a4_gemm_supported(int m, int n, int k) { return m >= 1 && n % 8 == 0 && k % 128 == 0 && k / 64 <= 160; }
+// activation scales [M, G] -> [G, Mpad] (rows past M zero): a drain thread then walks one pointer per slab
+__global__ void __launch_bounds__(256) w44_scale_transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int m, int groups,
+                                                                  int mpad) {
+  __shared__ float tile[32][33];
+  const int r0 = blockIdx.x * 32, g0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 x 8
+  for (int y = ty; y < 32; y += 8) {
+    const int r = r0 + y, g = g0 + tx;
+    tile[y][tx] = (r < m && g < groups) ? __ldg(src + (size_t)r * groups + g) : 0.f;
+  }
+  __syncthreads();
+  for (int y = ty; y < 32; y += 8) {
+    const int g = g0 + y, r = r0 + tx;
+    if (g < groups && r < mpad) dst[(size_t)g * mpad + r] = tile[tx][y];
+  }
+}
+
+// ----------------------------------------------------------------------------------------- host
 
 size_t w4a4_aux_tile_bytes(int k) { return (size_t)(k / 64) * 512 + w4a4::kUpBytes; }
 
-template <typename OutT>
-static int launch_w4a4(const void* a_codes, W4A4Params p, cudaStream_t stream) {
+// shared-memory plan: operand stages and weight-scale buffers (the two rank-R images are fixed)
+static bool w4a4_plan(int k, int* stages, int* scale_bufs) {
   using namespace w4a4;
-  CUtensorMap tm_a;
-  XQT_CUDA((cudaError_t)make_tile_map(&tm_a, a_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.m, p.k, kBM));
-  const int aux_bytes = p.aux_tile_bytes + kLaBytes;
-  // two aux buffers when at least three stages still fit, else one
-  int nab = 2;
-  int stages = (kSmemBudget - 1024 - nab * aux_bytes) / kStageBytes;
-  if (stages < 3) {
-    nab = 1;
-    stages = (kSmemBudget - 1024 - aux_bytes) / kStageBytes;
+  const int scale_bytes = (k / 64) * 512;
+  for (int nsb = 2; nsb >= 1; --nsb) {
+    int ns = (kSmemBudget - 1024 - kUpBytes - kLaBytes - nsb * scale_bytes) / kStageBytes;
+    if (ns > kMaxStages) ns = kMaxStages;
+    if (ns >= (nsb == 2 ? 3 : 2)) {
+      *stages = ns; *scale_bufs = nsb;
+      return true;
+    }
   }
-  XQT_REQUIRE(stages >= 2);
-  p.stages = stages > kMaxStages ? kMaxStages : stages;
-  p.aux_bufs = nab;
+  return false;
+}
+
+bool w4a4_gemm_supported(int m, int n, int k) {
+  int a, b;
+  return m >= 1 && n % 8 == 0 && k % 128 == 0 && k > 0 && w4a4_plan(k, &a, &b);
+}
+
+template <typename OutT>
+static int launch_w4a4(const void* a_codes, const void* b_bytes, W4A4Params p, cudaStream_t stream) {
+  using namespace w4a4;
+  CUtensorMap tm_a, tm_b;
+  XQT_CUDA((cudaError_t)make_tile_map(&tm_a, a_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.m, p.k, kBM));
+  XQT_CUDA((cudaError_t)make_tile_map(&tm_b, b_bytes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.n, p.k, kBN));
+  XQT_REQUIRE(w4a4_plan(p.k, &p.stages, &p.scale_bufs));
   p.mtiles = ceil_div(p.m, kBM);
   p.ntiles = ceil_div(p.n, kBN);
   p.kstages = p.k / kStageK;
-  const size_t smem_bytes = (size_t)p.stages * kStageBytes + (size_t)nab * aux_bytes + 1024;
+  const size_t smem_bytes = (size_t)p.stages * kStageBytes + (size_t)p.scale_bufs * p.groups * 512 + kUpBytes + kLaBytes + 1024;
   auto kern = gemm_w4a4_kernel<OutT>;
   XQT_SMEM_OPT_IN(kern, kSmemBudget);
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int grid = sms > 0 ? sms : 148;
   if (grid > p.mtiles * p.ntiles) grid = p.mtiles * p.ntiles;
-  kern<<<grid, kThreads, smem_bytes, stream>>>(tm_a, p);
+  kern<<<grid, kThreads, smem_bytes, stream>>>(tm_a, tm_b, p);
   return launch_status();
 }
 
+// workspace: status word (256 bytes) | one low-rank activation image per 128-row tile | the activation scales
+// transposed [K/64, mtiles*128] | the weights as bytes [N, K]
+static size_t w4a4_images_bytes(int m) { return (size_t)ceil_div(m, w4a4::kBM) * w4a4::kLaBytes; }
+static size_t w4a4_scales_bytes(int m, int k) { return (size_t)ceil_div(m, w4a4::kBM) * w4a4::kBM * (k / 64) * sizeof(float); }
+size_t w4a4_workspace_bytes(int m, int n, int k) { return 256 + w4a4_images_bytes(m) + w4a4_scales_bytes(m, k) + (size_t)n * k; }
+
 int w4a4_gemm_launch(const void* a_codes, const float* a_scale, const void* qweight, const void* aux, const float* la,
-                     const float* bias, void* out, int m, int n, int k, int out_dtype, unsigned int* status,
+                     const float* bias, void* out, int m, int n, int k, int out_dtype, void* workspace,
                      cudaStream_t stream) {
+  unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
   XQT_REQUIRE(w4a4_gemm_supported(m, n, k));
   XQT_REQUIRE(a_codes != nullptr && a_scale != nullptr && qweight != nullptr && aux != nullptr && la != nullptr &&
               out != nullptr && status != nullptr);
   XQT_REQUIRE(((uintptr_t)qweight & 15) == 0 && ((uintptr_t)aux & 15) == 0 && ((uintptr_t)la & 15) == 0 &&
-              ((uintptr_t)out & 15) == 0);
+              ((uintptr_t)out & 15) == 0 && ((uintptr_t)a_codes & 15) == 0);
   W4A4Params p{};
   p.m = m; p.n = n; p.k = k; p.groups = k / 64;
   p.aux_tile_bytes = (int)w4a4_aux_tile_bytes(k);
-  p.qweight = (const uint8_t*)qweight; p.a_scale = a_scale; p.aux = (const uint8_t*)aux; p.la = la; p.bias = bias;
+  p.aux = (const uint8_t*)aux; p.bias = bias;
+  uint8_t* images = reinterpret_cast<uint8_t*>(workspace) + 256;
+  float* scales_t = reinterpret_cast<float*>(images + w4a4_images_bytes(m));
+  uint8_t* b_bytes = reinterpret_cast<uint8_t*>(scales_t) + w4a4_scales_bytes(m, k);
+  const int mpad = ceil_div(m, w4a4::kBM) * w4a4::kBM;
+  w44_scale_transpose_kernel<<<dim3(mpad / 32, ceil_div(p.groups, 32)), 256, 0, stream>>>(a_scale, scales_t, m, p.groups, mpad);
+  XQT_CUDA(cudaGetLastError());
+  p.a_scale_t = scales_t;
+  XQT_REQUIRE(((uintptr_t)images & 15) == 0);
+  w44_la_image_kernel<<<ceil_div(m, w4a4::kBM), 128, 0, stream>>>(la, images);
+  XQT_CUDA(cudaGetLastError());
+  const size_t chunks = (size_t)n * k / 32;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const size_t want = (chunks + 255) / 256;
+  w44_expand_kernel<<<(unsigned)(want < (size_t)sms * 8 ? want : (size_t)sms * 8), 256, 0, stream>>>(
+      reinterpret_cast<const uint4*>(qweight), reinterpret_cast<uint4*>(b_bytes), chunks);
+  XQT_CUDA(cudaGetLastError());
+  p.la_tiles = images;
   p.out = out; p.status = status;
-  if (out_dtype == XQT_B200_BF16) return launch_w4a4<__nv_bfloat16>(a_codes, p, stream);
+  if (out_dtype == XQT_B200_BF16) return launch_w4a4<__nv_bfloat16>(a_codes, b_bytes, p, stream);
   XQT_REQUIRE(out_dtype == XQT_B200_FP16);
-  return launch_w4a4<__half>(a_codes, p, stream);
+  return launch_w4a4<__half>(a_codes, b_bytes, p, stream);
 }
 
 }  // namespace xqt_b200

@@ -19,19 +19,26 @@
 //           group == 0 selects the artifact's own per-token form (one scale per token,
 //           convrot_4bit.py:669-679), written to every 64-K slot of the scale row so that the
 //           group-64 GEMM consumes it unchanged
-// Codes are written as int8 in both modes (the int4 GEMM consumes int8 operands: Blackwell has no
-// int4 MMA).
+//   mode 5: the codes and scales of mode 4, each code written as the byte sign << 7 | magnitude.  Read as
+//           FP8 E4M3 that byte is the subnormal/first-binade value code * 2^-9 exactly (magnitudes 0..15
+//           are linear there), the operand form of the W4A4 GEMM's tcgen05 kind::f8f6f4 MMA.
+// Codes are written as one byte each in every mode (Blackwell has no int4 MMA).
 #include "common.cuh"
 
 namespace xqt_b200 {
 
 constexpr int kRqThreads = 256;
 
+__device__ __forceinline__ int8_t rq_encode(float q, int signmag) {
+  const int c = (int)q;
+  return (int8_t)(signmag ? ((c < 0 ? 0x80 : 0) | (c < 0 ? -c : c)) : c);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kRqThreads)
 rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_scale, int8_t* __restrict__ codes,
                     float* __restrict__ scales, T* __restrict__ x_rot, int k, int rot_kind, int rot_block, int mode,
-                    int group) {
+                    int group, int signmag) {
   extern __shared__ float v[];  // [k]
   __shared__ float s_red[kRqThreads / 32];
   __shared__ float s_scale;
@@ -107,7 +114,7 @@ rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_sc
     for (int gi = tid; gi < k / 64; gi += kRqThreads) scales[(size_t)row * (k / 64) + gi] = sc;
     for (int i = tid; i < k; i += kRqThreads) {
       const float q = fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), -8.f), 7.f);
-      codes[(size_t)row * k + i] = (int8_t)(int)q;
+      codes[(size_t)row * k + i] = rq_encode(q, signmag);
     }
   } else {
     __syncthreads();
@@ -119,7 +126,7 @@ rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_sc
       scales[(size_t)row * groups + gi] = sc;
       for (int e = 0; e < group; ++e) {
         const float q = fminf(fmaxf(rintf(__fdiv_rn(v[gi * group + e], sc)), -8.f), 7.f);
-        codes[(size_t)row * k + gi * group + e] = (int8_t)(int)q;
+        codes[(size_t)row * k + gi * group + e] = rq_encode(q, signmag);
       }
     }
   }
@@ -135,7 +142,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ column_scale, int8_t* __restrict__ codes,
                          float* __restrict__ scales, T* __restrict__ x_rot, int k, int rot_kind, int rot_block, int mode,
-                         int group) {
+                         int group, int signmag) {
   __shared__ float s_red[32];
   __shared__ float s_scale;
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
@@ -299,7 +306,7 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
       const float dist = fabsf(fabsf(__fsub_rn(quot, nearest)) - 0.5f);   // distance from a half-integer
       float code = nearest;
       if (dist < 0x1p-10f && fabsf(quot) < 512.f) code = rintf(__fdiv_rn(v[i], sc));
-      q[i] = (int8_t)(int)fminf(fmaxf(code, lo_clamp), hi_clamp);
+      q[i] = rq_encode(fminf(fmaxf(code, lo_clamp), hi_clamp), signmag);
     }
     *reinterpret_cast<uint4*>(codes + (size_t)row * k + tid * 16) = *reinterpret_cast<const uint4*>(q);
   }
@@ -307,7 +314,9 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
 
 int rotate_quant_launch(const void* x, const float* column_scale, void* codes, float* scales, void* x_rot, int m, int k,
                         int rot_kind, int rot_block, int mode, int group, int act_dtype, cudaStream_t stream) {
-  XQT_REQUIRE(m > 0 && k > 0 && (mode == 8 || mode == 4));
+  XQT_REQUIRE(m > 0 && k > 0 && (mode == 8 || mode == 4 || mode == 5));
+  const int signmag = mode == 5 ? 1 : 0;      // mode 5: the int4 codes of mode 4, written as sign-magnitude bytes
+  if (mode == 5) mode = 4;
   XQT_REQUIRE(rot_kind >= 0 && rot_kind <= 2);
   if (rot_kind != 0) {
     XQT_REQUIRE(rot_block >= 1 && k % rot_block == 0 && column_scale != nullptr);
@@ -325,10 +334,10 @@ int rotate_quant_launch(const void* x, const float* column_scale, void* codes, f
     const int threads = ceil_div(k / 16, 32) * 32;
     if (act_dtype == XQT_B200_BF16)
       rotate_quant_fast_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>(
-          (const __nv_bfloat16*)x, column_scale, (int8_t*)codes, scales, (__nv_bfloat16*)x_rot, k, rot_kind, rot_block, mode, group);
+          (const __nv_bfloat16*)x, column_scale, (int8_t*)codes, scales, (__nv_bfloat16*)x_rot, k, rot_kind, rot_block, mode, group, signmag);
     else
       rotate_quant_fast_kernel<__half><<<m, threads, 0, stream>>>(
-          (const __half*)x, column_scale, (int8_t*)codes, scales, (__half*)x_rot, k, rot_kind, rot_block, mode, group);
+          (const __half*)x, column_scale, (int8_t*)codes, scales, (__half*)x_rot, k, rot_kind, rot_block, mode, group, signmag);
     return launch_status();
   }
   const size_t smem = (size_t)k * sizeof(float);
@@ -338,7 +347,7 @@ int rotate_quant_launch(const void* x, const float* column_scale, void* codes, f
     auto kern = rotate_quant_kernel<TT>;                                                                         \
     XQT_SMEM_OPT_IN(kern, 200 * 1024);                                                                           \
     kern<<<m, kRqThreads, smem, stream>>>((const TT*)x, column_scale, (int8_t*)codes, scales, (TT*)x_rot, k,     \
-                                          rot_kind, rot_block, mode, group);                                     \
+                                          rot_kind, rot_block, mode, group, signmag);                            \
   } while (0)
   if (act_dtype == XQT_B200_BF16) XQT_RQ(__nv_bfloat16);
   else XQT_RQ(__half);

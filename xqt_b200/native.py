@@ -57,6 +57,7 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_lowrank_down": (_I, [_P] * 3 + [_I] * 3 + [_P]),
     "xqt_b200_w4a4_aux_tile_bytes": (_Z, [_I]),
     "xqt_b200_w4a4_supported": (_I, [_I] * 3),
+    "xqt_b200_w4a4_workspace_bytes": (_Z, [_I] * 3),
     "xqt_b200_w4a4_gemm": (_I, [_P] * 7 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_w4a4_dense_workspace_bytes": (_Z, [_I] * 3),
     "xqt_b200_w4a4_dense_preferred": (_I, [_I] * 3),

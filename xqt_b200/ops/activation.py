@@ -22,8 +22,12 @@ def _column_scale(rotation: Rotation, device: torch.device) -> torch.Tensor:
 
 
 def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, group_size: int = 64,
-                    return_rotated: bool = False, out: tuple | None = None):
+                    return_rotated: bool = False, out: tuple | None = None, sign_magnitude: bool = False):
     """-> (codes int8 ``[M,K]``, scales fp32 ``[M]`` (bits=8) or ``[M, K/group]`` (bits=4)[, rotated x]).
+
+    ``sign_magnitude`` (bits=4 only) writes each int4 code as the byte ``sign << 7 | magnitude`` -- read as
+    FP8 E4M3 that is ``code * 2**-9`` exactly, the operand form of the W4A4 GEMM; :func:`decode_sign_magnitude`
+    turns such bytes back into two's-complement codes.
 
     ``out = (codes, scales[, rotated])`` supplies preallocated buffers whose leading ``M`` rows are
     written (a workspace sized for at least M rows): the call then allocates nothing."""
@@ -32,6 +36,8 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
         raise XQTBackendError("rotate_quantize expects a CUDA rank-2 fp16/bf16 activation")
     if bits not in (4, 8):
         raise XQTBackendError("rotate_quantize supports 8-bit per-token or 4-bit per-group codes")
+    if sign_magnitude and bits != 4:
+        raise XQTBackendError("sign-magnitude bytes are the form of 4-bit codes only")
     x = x.contiguous()
     m, k = int(x.shape[0]), int(x.shape[1])
     device = x.device
@@ -59,9 +65,17 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
             code = native.library().xqt_b200_rotate_quantize(
                 x.data_ptr(), native.ptr(cs), codes.data_ptr(), scales.data_ptr(), native.ptr(rotated), m, k,
                 _KIND[None if rotation is None else rotation.kind], 0 if rotation is None else rotation.block,
-                bits, int(group_size), native.DTYPE_CODE[x.dtype], native.stream_handle(device))
+                5 if sign_magnitude else bits, int(group_size), native.DTYPE_CODE[x.dtype], native.stream_handle(device))
         native.check(code, "xqt_b200_rotate_quantize")
     return (codes, scales, rotated) if return_rotated else (codes, scales)
+
+
+def decode_sign_magnitude(codes: torch.Tensor) -> torch.Tensor:
+    """Sign-magnitude code bytes (``sign << 7 | magnitude``) -> two's-complement int8 codes."""
+
+    raw = codes.view(torch.uint8).to(torch.int16)
+    magnitude = raw & 0x7F
+    return torch.where(raw >= 0x80, -magnitude, magnitude).to(torch.int8)
 
 
 def quantize_int8_per_tensor(x: torch.Tensor, *, eps: float = 1e-6, out: tuple | None = None):
@@ -91,4 +105,4 @@ def quantize_int8_per_tensor(x: torch.Tensor, *, eps: float = 1e-6, out: tuple |
     return codes, rows, stats[1:2]
 
 
-__all__ = ["quantize_int8_per_tensor", "rotate_quantize"]
+__all__ = ["decode_sign_magnitude", "quantize_int8_per_tensor", "rotate_quantize"]

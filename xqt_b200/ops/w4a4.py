@@ -56,6 +56,19 @@ class PackedSVDQW4A4Linear:
         return RANK_PAD
 
 
+def _operand_image(values: torch.Tensor) -> torch.Tensor:
+    """fp32 ``[rows (a multiple of 128), 32]`` -> fp32-typed view of the tensor-core operand image: per row bf16
+    ``[hi(32) | lo(32)]`` (``hi = bf16(v)``, ``lo = bf16(v - hi)``), its eight 16-byte chunks at index ``c ^ (row & 7)``."""
+
+    rows = int(values.shape[0])
+    hi = values.to(torch.bfloat16)
+    lo = (values - hi.to(torch.float32)).to(torch.bfloat16)
+    chunks = torch.cat((hi, lo), dim=1).reshape(rows, 8, 8)                     # 8 chunks of 8 bf16
+    index = torch.arange(8, device=values.device).reshape(1, 8) ^ (torch.arange(rows, device=values.device).reshape(rows, 1) & 7)
+    image = torch.gather(chunks, 1, index.reshape(rows, 8, 1).expand(rows, 8, 8))   # physical chunk c holds logical chunk c ^ (row & 7)
+    return image.contiguous().view(torch.float32).reshape(rows, RANK_PAD)
+
+
 def pack_svdq_w4a4_linear(
     residual_weight: torch.Tensor | None,
     down_weight: torch.Tensor | None,
@@ -105,7 +118,7 @@ def pack_svdq_w4a4_linear(
     tiles = -(-n // TILE)
     scale = residual_scale.to(device=device, dtype=torch.float32)
     sw = torch.zeros((tiles * TILE, groups), device=device, dtype=torch.float32)
-    sw[:n] = scale / 16.0                     # the kernel feeds 16*w to the tensor core
+    sw[:n] = scale * float(2 ** 18)           # both operands reach the tensor core as code * 2^-9 (FP8 E4M3 bytes)
     up = torch.zeros((tiles * TILE, RANK_PAD), device=device, dtype=torch.float32)
     down = torch.zeros((RANK_PAD, k), device=device, dtype=dtype)
     if rank:
@@ -114,7 +127,7 @@ def pack_svdq_w4a4_linear(
         up[:n, :rank] = up_weight.to(device=device, dtype=dtype).to(torch.float32)
         down[:rank] = down_weight.to(device=device, dtype=dtype)
     aux = torch.cat((sw.reshape(tiles, TILE, groups).transpose(1, 2).reshape(tiles, -1),
-                     up.reshape(tiles, -1)), dim=1).contiguous()
+                     _operand_image(up).reshape(tiles, -1)), dim=1).contiguous()
     return PackedSVDQW4A4Linear(
         qweight=packed_residual.to(device).contiguous(), aux=aux, weight_scales=scale.contiguous(),
         up=up[:n].contiguous() if rank else None, down=down,
@@ -213,8 +226,12 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
                 or workspace.rotated_activation is None or (packed.rank and workspace.lora_activation is None):
             raise ValueError("workspace extent does not match inputs / packed weights")
         buffers = (workspace.quantized_activation, workspace.activation_scales, workspace.rotated_activation)
+    dense = form == "dense"
+    if form not in ("auto", "dense", "integer"):
+        raise XQTBackendError("form must be auto, dense or integer")
+    # the integer form's GEMM takes the codes as sign-magnitude bytes (FP8 E4M3 operands), the dense form as int8
     codes, scales, rotated = rotate_quantize(x, packed.rotation, bits=4, group_size=GROUP if packed.act_granularity == "group" else 0,
-                                             return_rotated=True, out=buffers)
+                                             return_rotated=True, out=buffers, sign_magnitude=not dense)
     if workspace is not None and workspace.lora_activation is not None:
         la = workspace.lora_activation          # rows past M stay zero: the kernels only write rows < M
     else:
@@ -222,11 +239,9 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
     stream = native.stream_handle(device)
     # auto keeps the integer form: it is the one that meets the 1e-3 parity bar at every K (the dense
     # form is about 3.5x faster at M >= 256 and within 1.2e-3)
-    dense = form == "dense"
-    if form not in ("auto", "dense", "integer"):
-        raise XQTBackendError("form must be auto, dense or integer")
     with torch.cuda.device(device):
-        scratch = native.workspace(device, lib.xqt_b200_w4a4_dense_workspace_bytes(m, n, k) if dense else 256, "gemm")
+        scratch = native.workspace(device, lib.xqt_b200_w4a4_dense_workspace_bytes(m, n, k) if dense else
+                                   lib.xqt_b200_w4a4_workspace_bytes(m, n, k), "gemm")
         if packed.rank:
             if dense:
                 native.check(lib.xqt_b200_lowrank_down_tc(
@@ -249,7 +264,9 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
                 scratch.numel(), stream), "xqt_b200_w4a4_gemm")
     out = out.reshape(*inputs.shape[:-1], n)
     if return_parts:
-        return out, {"codes": codes, "scales": scales, "rotated": rotated, "la": la[:m]}
+        from .activation import decode_sign_magnitude
+
+        return out, {"codes": codes if dense else decode_sign_magnitude(codes), "scales": scales, "rotated": rotated, "la": la[:m]}
     return out
 
 
