@@ -97,6 +97,11 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
 int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_size,
                                   int epilogue_activation, int has_residual);
 
+/* 1 when the fused form (XQT_B200_VARIANT_TCGEN05_FUSED: packed weights dequantised in registers on their way to the
+ * tensor core, K split over CTAs when there are few channel tiles) measures faster than the two-pass form for this
+ * problem; it needs integer zero points (or none), which only the caller can know. */
+int xqt_b200_w4a16_fused_preferred(int m, int n, int k, int padded_k, int group_size);
+
 /* 1 when XQT_B200_VARIANT_TCGEN05 serves this M in two passes (weights dequantised once per call
  * into an fp16 scratch in fp32 arithmetic, then a dense tcgen05 GEMM): in that form any zero
  * point is accepted, integer or not, and xqt_b200_w4a16_workspace_bytes includes N*K*2 bytes for

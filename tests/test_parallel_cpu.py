@@ -17,7 +17,7 @@ from oracle import mlp as omlp
 from oracle import w4a16 as oracle
 from xqt_b200 import quantize
 from xqt_b200.errors import XQTBackendError
-from xqt_b200.parallel import (ColumnParallelLinear, RowParallelLinear, TensorParallelSwiGLUMLP,
+from xqt_b200.parallel import (ColumnParallelLinear, RowParallelLinear,
                                shard_packed_weight)
 
 
@@ -68,9 +68,11 @@ def _worker(rank, world, port, results, fail_rank):
         row = RowParallelLinear(shard_packed_weight(down, world=world, rank=rank, axis=1), local_linear=_oracle_linear)
         cols = 512 // world
         y_row = row(h[:, rank * cols:(rank + 1) * cols].contiguous())
-        mlp = TensorParallelSwiGLUMLP(
-            shard_packed_weight(gate, world=world, rank=rank, axis=0), shard_packed_weight(up, world=world, rank=rank, axis=0),
-            shard_packed_weight(down, world=world, rank=rank, axis=1), local_linear=_oracle_linear, swiglu=omlp.swiglu)
+        # the product's MLP block itself (it shards the canonical weights), its kernels replaced by the oracle
+        from xqt_b200.ops.mlp import W4A16SwiGLUMLP
+
+        mlp = W4A16SwiGLUMLP(gate, up, down, device=torch.device("cpu"), rank=rank, world=world, local_linear=_oracle_linear,
+                             swiglu_fn=lambda gu: omlp.swiglu(gu[:, : gu.shape[1] // 2], gu[:, gu.shape[1] // 2:]))
         if rank == fail_rank:
             raise XQTBackendError("injected backend failure on this rank")
         y_mlp = mlp(x)

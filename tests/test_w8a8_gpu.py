@@ -11,6 +11,7 @@ from oracle import rotation as orot
 from oracle import w4a16 as o16
 from oracle import w8a8 as oracle
 from xqt_b200 import native, quantize
+from xqt_b200.errors import XQTBackendError
 from xqt_b200.ops.activation import rotate_quantize
 from xqt_b200.ops.w8a8 import convrot_w8a8_linear, pack_convrot_w8a8_linear, w8a8_gemm
 
@@ -122,3 +123,37 @@ def test_registry_executor_through_dispatch(prequantized):
     torch.cuda.synchronize()
     assert result.report.selected_kernel == B200_W8A8 and result.report.native
     assert o16.rel_l2(result.output.cpu(), ref) <= 1e-3
+
+
+@pytest.mark.gpu
+def test_shared_and_fused_projection_groups():
+    """Gate/up style groups: one prologue for all projections; the fused group is one horizontal GEMM whose
+    column slices equal the separate projections bit for bit, and feeds the SwiGLU kernel."""
+
+    from oracle import mlp as omlp
+    from xqt_b200.ops.w8a8 import FusedConvRotW8A8LinearGroup, SharedConvRotW8A8Group
+
+    dev = torch.device("cuda", 0)
+    m, k, inter = 70, 512, 384
+    rot = quantize.regular_rotation(256)
+    x = torch.randn((m, k), generator=seeded(31)).to(torch.bfloat16)
+    packeds, refs = [], []
+    for i in range(2):
+        w = torch.randn((inter, k), generator=seeded(32 + i)) * 0.02
+        q, s = quantize.quantize_w8_per_channel(rot.apply(w))
+        bias = torch.randn((inter,), generator=seeded(34 + i)) if i == 0 else None
+        packeds.append(pack_convrot_w8a8_linear(q.t().contiguous().to(dev), s.to(dev), None if bias is None else bias.to(dev),
+                                                dtype=torch.bfloat16))
+        refs.append(oracle.linear(x, q, s, rot_block=256, bias=bias))
+    shared = SharedConvRotW8A8Group(packeds, rot_size=256)(x.to(dev))
+    fused_group = FusedConvRotW8A8LinearGroup(packeds, rot_size=256)
+    fused = fused_group(x.to(dev))
+    for got_s, got_f, ref in zip(shared, fused, refs):
+        assert o16.rel_l2(got_s.cpu(), ref) <= 1e-3
+        assert torch.equal(got_s, got_f)
+    gated = fused_group.forward_swiglu(x.to(dev))
+    assert torch.equal(gated.cpu(), omlp.swiglu(fused[0].cpu(), fused[1].cpu()))
+    x3 = x.reshape(2, 35, k).to(dev)
+    assert tuple(fused_group(x3)[1].shape) == (2, 35, inter)
+    with pytest.raises(XQTBackendError):
+        FusedConvRotW8A8LinearGroup(packeds + packeds[:1], rot_size=256).forward_swiglu(x.to(dev))

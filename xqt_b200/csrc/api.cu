@@ -31,6 +31,7 @@ int swiglu_launch(const void*, void*, int, int, int, cudaStream_t);
 size_t w4a16_gemm_tc_workspace_bytes(int m, int n, int k);
 bool w4a16_gemm_tc_any_zero_point(int m);
 bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size);
+bool w4a16_gemm_fused_preferred(int m, int n, int k, int padded_k, int group_size);
 int lowrank_down_launch(const void*, const void*, float*, int, int, int, cudaStream_t);
 size_t w4a4_workspace_bytes(int m, int n, int k);
 int w4a4_gemm_launch(const void*, const float*, const void*, const void*, const float*, const float*, void*, int, int, int,
@@ -85,6 +86,10 @@ int xqt_b200_w4a16_select_variant(int m, int n, int k, int padded_k, int group_s
 
 int xqt_b200_w4a16_two_pass(int m) { return w4a16_gemm_tc_any_zero_point(m) ? 1 : 0; }
 
+int xqt_b200_w4a16_fused_preferred(int m, int n, int k, int padded_k, int group_size) {
+  return w4a16_gemm_fused_preferred(m, n, k, padded_k, group_size) ? 1 : 0;
+}
+
 int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* scales, const void* zero_points,
                        const float* bias, const void* residual, void* output, int m, int n, int k, int padded_k,
                        int group_size, int nibble_signed, int act_dtype, int param_dtype, int out_dtype,
@@ -113,6 +118,10 @@ int xqt_b200_w4a16_run(const void* activation, const void* qweight, const void* 
     // (at large M the weights are dequantised in fp32 first, which serves any zero point)
     if (variant == XQT_B200_VARIANT_TCGEN05 && zero_points != nullptr && !w4a16_gemm_tc_any_zero_point(m))
       variant = XQT_B200_VARIANT_SIMT;
+    // the fused form where it measures faster; with zero points only a caller who knows they are integers asks for it
+    if (variant == XQT_B200_VARIANT_TCGEN05 && zero_points == nullptr && !out_f32 &&
+        w4a16_gemm_fused_preferred(m, n, k, padded_k, group_size))
+      variant = XQT_B200_VARIANT_TCGEN05_FUSED;
   }
   cudaStream_t s = (cudaStream_t)stream;
   switch (variant) {

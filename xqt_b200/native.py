@@ -37,6 +37,7 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_workspace_bytes": (_Z, [_I, _I, _I]),
     "xqt_b200_w4a16_select_variant": (_I, [_I] * 7),
     "xqt_b200_w4a16_two_pass": (_I, [_I]),
+    "xqt_b200_w4a16_fused_preferred": (_I, [_I] * 5),
     "xqt_b200_w4a16_run": (_I, [_P] * 7 + [_I] * 10 + [_P, _Z, _I, _P]),
     "xqt_b200_w4a16_decode_workspace_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_supported": (_I, [_I] * 4),

@@ -58,6 +58,9 @@ def _concat_rows(a: PackedWeight, b: PackedWeight) -> PackedWeight:
         metadata=PackedWeightMetadata(**values))
 
 
+CHUNKED_DECODE_MAX_ROWS = 48
+
+
 class _Linear:
     """One W4A16 layer on a device with both execution forms: decode layout and canonical bytes."""
 
@@ -80,37 +83,75 @@ class _Linear:
                 run = bind_w4a16_decode(self.tiled, rows=m, dtype=self.dtype, out_dtype=odt)
                 self._bound[(m, odt)] = run
             return run(x, out) if out is not None else run(x)
+        if m <= CHUNKED_DECODE_MAX_ROWS and self.tiled.layout == "lanes":
+            # a few decode passes over 16-row chunks: the packed weights of a layer (tens of MB) stay in the 126 MB
+            # L2 between passes, and each pass runs at the decode kernel's rate -- measured ahead of the GEMM forms
+            # up to three passes
+            if out is None:
+                out = torch.empty((m, self.n), device=x.device, dtype=odt)
+            for r0 in range(0, m, 16):
+                rows = min(16, m - r0)
+                run = self._bound.get((rows, odt))
+                if run is None:
+                    run = bind_w4a16_decode(self.tiled, rows=rows, dtype=self.dtype, out_dtype=odt)
+                    self._bound[(rows, odt)] = run
+                run(x[r0:r0 + rows], out[r0:r0 + rows])
+            return out
         return w4a16_linear(x, self.qweight, self.scales, self.zeros, group_size=self.group,
                             nibble_signed=self.signed, k=self.k, out_dtype=odt, out=out)
 
 
+class _InjectedLinear:
+    """One layer served by a caller-supplied ``local_linear(x, weight, out_dtype=...)`` (the gloo tests run the
+    block's sharding and reduction logic on the CPU with the oracle in this seat)."""
+
+    def __init__(self, weight: PackedWeight, local_linear) -> None:
+        self.weight, self.local_linear = weight, local_linear
+        self.n, self.k = weight.metadata.logical_shape
+        self.tiled = None
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        y = self.local_linear(x, self.weight) if out_dtype is None else self.local_linear(x, self.weight, out_dtype=out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+
 class W4A16SwiGLUMLP:
     """The MLP block of one rank.  ``gate`` / ``up`` are canonical ``[inter, hidden]`` weights,
-    ``down`` is ``[hidden, inter]``; they are sharded here for ``rank`` of ``world``."""
+    ``down`` is ``[hidden, inter]``; they are sharded here for ``rank`` of ``world``.  ``local_linear`` /
+    ``swiglu_fn`` replace the CUDA kernels (tests of the multi-rank logic on CPU ranks)."""
 
     def __init__(self, gate: PackedWeight, up: PackedWeight, down: PackedWeight, *, device: torch.device,
                  dtype: torch.dtype = torch.bfloat16, rank: int = 0, world: int = 1, group=None,
-                 peer_reduce: bool | None = None) -> None:
+                 peer_reduce: bool | None = None, local_linear=None, swiglu_fn=None) -> None:
         if world > 1:
             gate = shard_packed_weight(gate, world=world, rank=rank, axis=0)
             up = shard_packed_weight(up, world=world, rank=rank, axis=0)
             down = shard_packed_weight(down, world=world, rank=rank, axis=1)
         self.world, self.group, self.dtype = world, group, dtype
-        self.gate_up = _Linear(_concat_rows(gate, up), device, dtype)
-        self.down = _Linear(down, device, dtype)
+        self._swiglu = swiglu_fn or swiglu
+        if local_linear is not None:
+            self.gate_up = _InjectedLinear(_concat_rows(gate, up), local_linear)
+            self.down = _InjectedLinear(down, local_linear)
+            peer_reduce = False
+        else:
+            self.gate_up = _Linear(_concat_rows(gate, up), device, dtype)
+            self.down = _Linear(down, device, dtype)
         self.hidden, self.inter_local = self.down.n, self.down.k
         # decode sizes (M <= 16): the partial sums of down are added by our own kernel over NVLink peer
         # memory instead of an NCCL all-reduce (XQT_B200_PEER_REDUCE=0 or peer_reduce=False: NCCL)
         if peer_reduce is None:
             peer_reduce = os.environ.get("XQT_B200_PEER_REDUCE", "1") not in {"0", ""}
         self._peer = None
-        if world > 1 and peer_reduce and self.down.tiled.layout in ("rows128", "lanes"):
+        if world > 1 and peer_reduce and self.down.tiled is not None and self.down.tiled.layout in ("rows128", "lanes"):
             from ..parallel import PeerAllReduce
 
             self._peer = PeerAllReduce(device, 16 * self.hidden, group)
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        h = swiglu(self.gate_up(x))
+        h = self._swiglu(self.gate_up(x))
         if self.world == 1:
             return self.down(h)
         m = int(h.shape[0])
@@ -128,9 +169,10 @@ class W4A16SwiGLUMLP:
         return {
             "implementation": "b200_w4a16_swiglu_mlp", "world": self.world,
             "reduction": "none" if self.world == 1 else ("peer_allreduce_kernel (M <= 16) / NCCL all-reduce" if self._peer else "NCCL all-reduce"),
-            "decode_layout": self.gate_up.tiled.layout, "hidden": self.hidden, "inter_local": self.inter_local,
+            "decode_layout": None if self.gate_up.tiled is None else self.gate_up.tiled.layout, "hidden": self.hidden,
+            "inter_local": self.inter_local,
             "kernels": {"m<=16": {"lanes": "w4a16_decode_cl_kernel", "rows128": "w4a16_decode_tc_kernel"}.get(
-                            self.gate_up.tiled.layout, "w4a16_decode_kernel"),
+                            None if self.gate_up.tiled is None else self.gate_up.tiled.layout, "w4a16_decode_kernel"),
                         "m>16": "gemm_w4a16_kernel", "gating": "swiglu_kernel"},
         }
 

@@ -119,6 +119,10 @@ def w4a16_linear(
         variant = select_variant(m, n, k, padded_k, int(group_size), activation, residual is not None)
         if variant == "tcgen05" and not two_pass and not _integer_zero_points(zero_points):
             variant = "simt"
+        # the fused single-pass form where it measures faster (few channel tiles, M <= 128); integer zero points only
+        if variant == "tcgen05" and odt != torch.float32 and lib.xqt_b200_w4a16_fused_preferred(m, n, k, padded_k, int(group_size)) \
+                and _integer_zero_points(zero_points):
+            variant = "tcgen05_fused"
     if variant == "tcgen05_fused" and not _integer_zero_points(zero_points):
         raise XQTBackendError("the single-pass tcgen05 GEMM needs integer zero points")
     scratch = native.workspace(device, lib.xqt_b200_w4a16_workspace_bytes(m, n, k))

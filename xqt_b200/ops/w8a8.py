@@ -96,6 +96,86 @@ def int8_mma_linear(inputs: torch.Tensor, packed: PackedConvRotW8A8Linear, *, ep
     return w8a8_gemm(codes, row_scales, packed).reshape(*inputs.shape[:-1], packed.output_features)
 
 
+def _rms_norm(flat: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    x = flat.to(torch.float32)
+    return (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.to(torch.float32)).to(flat.dtype)
+
+
+class SharedConvRotW8A8Group:
+    """Projections that share one rotated, quantised activation (cf. convrot_w8a8_sm89.py:601-661): the
+    rotate + quantise prologue runs once, one GEMM per projection.  ``norm_weight`` (RMSNorm ahead of the
+    projections) is applied by an eager fp32 pass here, not inside the prologue kernel."""
+
+    def __init__(self, packeds: list, *, rot_size: int = 256, norm_weight: torch.Tensor | None = None, eps: float = 1e-6) -> None:
+        if not packeds:
+            raise ValueError("packeds must contain at least one projection")
+        first = packeds[0]
+        if any((p.input_features, p.padded_input_features, p.dtype, p.qweight.device) !=
+               (first.input_features, first.padded_input_features, first.dtype, first.qweight.device) for p in packeds):
+            raise XQTBackendError("grouped ConvRot W8A8 projections must share input size, dtype and device")
+        self.packeds, self.rot_size = list(packeds), int(rot_size)
+        self.input_features, self.padded_input_features = first.input_features, first.padded_input_features
+        self.dtype, self.device = first.dtype, first.qweight.device
+        self.norm_weight = None if norm_weight is None else norm_weight.to(device=self.device, dtype=self.dtype)
+        self.eps = float(eps)
+        self._rotation = None if self.rot_size == 1 else regular_rotation(self.rot_size)
+
+    def _quantise(self, inputs: torch.Tensor):
+        flat = inputs.reshape(-1, self.input_features)
+        if flat.dtype != self.dtype or flat.device != self.device:
+            raise XQTBackendError("grouped ConvRot W8A8 inputs must match the packed layers' dtype and device")
+        if self.norm_weight is not None:
+            flat = _rms_norm(flat, self.norm_weight, self.eps)
+        if self.padded_input_features != self.input_features:
+            flat = torch.nn.functional.pad(flat, (0, self.padded_input_features - self.input_features))
+        return rotate_quantize(flat.contiguous(), self._rotation, bits=8)
+
+    def __call__(self, inputs: torch.Tensor) -> list:
+        codes, scales = self._quantise(inputs)
+        return [w8a8_gemm(codes, scales, p).reshape(*inputs.shape[:-1], p.output_features) for p in self.packeds]
+
+
+class FusedConvRotW8A8LinearGroup(SharedConvRotW8A8Group):
+    """The same group as ONE horizontal GEMM over the concatenated output channels
+    (cf. convrot_w8a8_sm89.py:664-917): one prologue, one tcgen05 GEMM, the outputs are column slices of its
+    result.  ``forward_swiglu`` (two projections, gate then up) feeds the fused result to the SwiGLU kernel.
+    The reference's small-row fallbacks to a dense de-quantised GEMM are not needed: the int8 GEMM serves every M."""
+
+    def __init__(self, packeds: list, *, rot_size: int = 256, norm_weight: torch.Tensor | None = None, eps: float = 1e-6,
+                 min_int8_rows: int = 0) -> None:
+        super().__init__(packeds, rot_size=rot_size, norm_weight=norm_weight, eps=eps)
+        self.split_sizes = [p.output_features for p in self.packeds]
+        self.total_output_features = sum(self.split_sizes)
+        self.min_int8_rows = int(min_int8_rows)         # accepted for signature parity; unused
+        bias = None
+        if any(p.bias is not None for p in self.packeds):
+            bias = torch.cat([p.bias if p.bias is not None else torch.zeros(p.output_features, device=self.device) for p in self.packeds])
+        self.fused_packed = PackedConvRotW8A8Linear(
+            qweight=torch.cat([p.qweight for p in self.packeds], dim=0).contiguous(),
+            weight_scales=torch.cat([p.weight_scales for p in self.packeds]).contiguous(), bias=bias,
+            input_features=self.input_features, output_features=self.total_output_features,
+            padded_input_features=self.padded_input_features, dtype=self.dtype)
+
+    def _fused(self, inputs: torch.Tensor) -> torch.Tensor:
+        codes, scales = self._quantise(inputs)
+        return w8a8_gemm(codes, scales, self.fused_packed)
+
+    def __call__(self, inputs: torch.Tensor) -> list:
+        fused = self._fused(inputs)
+        return [part.reshape(*inputs.shape[:-1], part.shape[-1]) for part in torch.split(fused, self.split_sizes, dim=1)]
+
+    def forward_swiglu(self, inputs: torch.Tensor) -> torch.Tensor:
+        """``silu(gate(x)) * up(x)`` from the fused gate|up GEMM and the SwiGLU kernel."""
+
+        from .mlp import swiglu
+
+        if len(self.packeds) != 2 or self.split_sizes[0] != self.split_sizes[1]:
+            raise XQTBackendError("forward_swiglu requires exactly two packed projections (gate and up) of equal width")
+        out = swiglu(self._fused(inputs))
+        return out.reshape(*inputs.shape[:-1], self.split_sizes[0])
+
+
+
 _REGULAR_SIZES = (1, 4, 16, 64, 256, 1024)
 
 
@@ -225,6 +305,6 @@ def bind_convrot_w8a8_linear(packed: PackedConvRotW8A8Linear, workspace: ConvRot
     return run
 
 
-__all__ = ["ConvRotW8A8Workspace", "PackedConvRotW8A8Linear", "allocate_convrot_w8a8_workspace", "bind_convrot_w8a8_linear",
+__all__ = ["ConvRotW8A8Workspace", "FusedConvRotW8A8LinearGroup", "PackedConvRotW8A8Linear", "SharedConvRotW8A8Group", "allocate_convrot_w8a8_workspace", "bind_convrot_w8a8_linear",
            "convrot_w8a8_linear", "int8_mma_linear", "native_convrot_w8a8_available", "native_convrot_w8a8_shape_supported",
            "native_convrot_w8a8_version", "native_prerotated_w8a8_shape_supported", "pack_convrot_w8a8_linear", "w8a8_gemm"]

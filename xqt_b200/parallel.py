@@ -122,25 +122,6 @@ class RowParallelLinear:
         return partial.to(x.dtype)
 
 
-class TensorParallelSwiGLUMLP:
-    """``down(silu(gate x) * up x)`` with gate/up column-parallel (no gather: the gating is
-    element-wise on the local slice) and down row-parallel (one all-reduce per call).
-
-    ``gate``, ``up`` are shards over N of ``[inter, hidden]``; ``down`` is a shard over K of
-    ``[hidden, inter]``.  ``swiglu(g, u)`` defaults to the CUDA kernel.
-    """
-
-    def __init__(self, gate: PackedWeight, up: PackedWeight, down: PackedWeight, *, group=None,
-                 local_linear: LocalLinear | None = None, swiglu: Callable | None = None) -> None:
-        self.gate = ColumnParallelLinear(gate, group=group, gather_output=False, local_linear=local_linear)
-        self.up = ColumnParallelLinear(up, group=group, gather_output=False, local_linear=local_linear)
-        self.down = RowParallelLinear(down, group=group, local_linear=local_linear)
-        self.swiglu = swiglu or _default_swiglu
-
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down(self.swiglu(self.gate(x), self.up(x)))
-
-
 class PeerAllReduce:
     """Sum of the ranks' fp32 partials over NVLink peer memory, epilogue (bias, rounding) fused in.
 
@@ -226,10 +207,4 @@ class PeerAllReduce:
                                   "the affected outputs are not valid")
 
 
-def _default_swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-    from .ops.mlp import swiglu
-
-    return swiglu(torch.cat((gate, up), dim=1))
-
-
-__all__ = ["ColumnParallelLinear", "PeerAllReduce", "RowParallelLinear", "TensorParallelSwiGLUMLP", "shard_packed_weight"]
+__all__ = ["ColumnParallelLinear", "PeerAllReduce", "RowParallelLinear", "shard_packed_weight"]
