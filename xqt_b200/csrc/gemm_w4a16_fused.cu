@@ -180,7 +180,7 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
 
   // Every wait is bounded: when one runs out the CTA stops waiting anywhere, reports and drains out.
   auto guarded_wait = [&](uint32_t b, uint32_t parity) {
-    if (s_abort == 0u && !mbar_wait_short(b, parity)) {
+    if (s_abort == 0u && !mbar_wait(b, parity)) {
       s_abort = 1u;
       atomicExch(p.status, (unsigned int)kTimeout);
     }
@@ -233,7 +233,7 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           const int s = it % ns;
           if (!ready) guarded_wait(bar(kBarReady + s), (it / ns) & 1);   // weights dequantised (their writers saw the activations land)
           // a barrier test takes about 200 cycles to answer: the next stage's travels while this stage's MMAs are issued
-          ready = mbar_try_wait_short(bar(kBarReady + (it + 1) % ns), ((it + 1) / ns) & 1);
+          ready = mbar_try_wait(bar(kBarReady + (it + 1) % ns), ((it + 1) / ns) & 1);
           tc_fence_after();
           const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
           const uint64_t bdesc = umma_desc_sw128(a_addr + kABytes);
@@ -404,8 +404,8 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         if (!ahead_full) guarded_wait(bar(kBarFull + s), (it / ns) & 1);   // the stage is free again (and its activations have landed)
         // this group's next stage: its two barriers are tested while this stage is converted
         const uint32_t nx = it + kDqGroups;
-        ahead_raw = mbar_try_wait_short(bar(kBarRawFull + nx % nr), (nx / nr) & 1);
-        ahead_full = mbar_try_wait_short(bar(kBarFull + nx % ns), (nx / ns) & 1);
+        ahead_raw = mbar_try_wait(bar(kBarRawFull + nx % nr), (nx / nr) & 1);
+        ahead_full = mbar_try_wait(bar(kBarFull + nx % ns), (nx / ns) & 1);
         unsigned char* bt = tiles + (size_t)s * kStageBytes + kABytes;
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
