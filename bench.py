@@ -695,7 +695,7 @@ def measure_other_configs(device, world, rank, barrier) -> list:
         sec, runs = _cpu_seconds(lambda: oracle_w4a4.w4a4_forward(xc, pc, sc4, dc, uc, group_size=64, rot_kind=rot4.kind, rot_block=128,
                                                                   signs=rot4.signs), budget_s=12.0)
         cpu = (sec, runs, cores, "oracle.w4a4.w4a4_forward (rotation, group-64 int4 activations, per-slab integer GEMM, low rank)")
-    for form, kernel, note in (("integer", "gemm_w4a4_kernel", "default form: tcgen05 kind::i8, per-group fp32 scaling; meets the 1e-3 parity bar"),
+    for form, kernel, note in (("integer", "gemm_w4a4_kernel", "default form: exact FP8 operands on tcgen05 kind::f8f6f4, per-group fp32 scaling; meets the 1e-3 parity bar"),
                                ("dense", "gemm_f16_kernel", "opt-in form: operands expanded to fp16; rel-L2 1.2e-3 at this K, above the 1e-3 bar")):
         call = lambda xx, f=form: svdq_w4a4_linear(xx, layer, form=f)  # noqa: E731
         t4, clocks = _timed_with_clocks(lambda: call(x4), barrier, index, 5, 1, device)

@@ -63,7 +63,7 @@ block = W4A16SwiGLUMLP(gate, up, down, device=dev, rank=rank, world=world)      
 nccl_block = W4A16SwiGLUMLP(gate, up, down, device=dev, rank=rank, world=world, peer_reduce=False)
 assert block.execution_metadata()["reduction"].startswith("peer_allreduce_kernel")
 from xqt_b200 import native
-for m in (4, 64):
+for m in (4, 64, 300):
     x = torch.randn((m, 1024), generator=seeded(m)).to(torch.bfloat16).to(dev)
     y = block(x)
     torch.cuda.synchronize()
@@ -98,7 +98,7 @@ def test_mlp_two_ranks_nccl(tmp_path):
                    timeout=300)
     gate, up, down = _weights(1024, 2048, 20)
     w = lambda pw: (pw.qweight, pw.scales, pw.zero_points)
-    for m in (4, 64):
+    for m in (4, 64, 300):       # 300 rows: the reduction runs in column blocks overlapped with the down projection
         x = torch.randn((m, 1024), generator=seeded(m)).to(torch.bfloat16)
         ref = omlp.forward(x, w(gate), w(up), w(down), group_size=128)
         y = torch.load(tmp_path / f"y{m}.pt", weights_only=True)

@@ -133,13 +133,9 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
   for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
     const int mt = tile % p.mtiles, nt = tile / p.mtiles;
     const int ab = local % nsb;
-    // activation scales: the scalars of the next slab are requested while this one is folded
     const int row0 = mt * kBM + quarter * 32 + rq;       // the thread's rows are row0 + 8 i
     const int mpad = p.mtiles * kBM;
     const float* sp = p.a_scale_t + row0;                // one slab's scales of the four rows: sp[8 i]; next slab: + mpad
-    float sn[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) sn[i] = __ldg(sp + 8 * i);
     // Two 16-register buffers: rows 0-15 and rows 16-31 of the warp's 32 x 32 part of a slab (one tcgen05.ld each).
     // While one is folded the other is in flight: a tensor-memory load takes about 150 cycles, and one warp's
     // share of the arithmetic between two waits has to cover it.
@@ -183,12 +179,8 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
           f32x2_unpack(w, ws[j].x, ws[j].y);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sa[i] = sn[i];
-        if (h == 0 || ks + 1 < kstages) {
-          sp += mpad;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) sn[i] = __ldg(sp + 8 * i);                // the next slab's, a slab ahead
-        }
+        for (int i = 0; i < 4; ++i) sa[i] = __ldg(sp + 8 * i);     // requested here, used after the tensor-memory wait below; a
+        sp += mpad;                                               // prefetch a slab ahead costs four registers the role does not have
         tmem_wait_ld_dep(ra);                          // rows 0-15 of the slab
         tmem_ld_16x256b_x4(tslab + (16u << 16), rb);
         fold(ra, ws, sa, 0);

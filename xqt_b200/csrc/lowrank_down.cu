@@ -3,7 +3,7 @@
 // It is the "LoRA down" step the reference fuses into its activation-quantisation kernel
 // (jit/include/nunchaku/lora.cuh:110-243, gemm_w4a4.cuh:1149-1188): the rank-R branch is taken from
 // the rotated, un-quantised activation.  R <= 32 makes this a skinny GEMM (1.3 % of the layer's
-// flops); one warp computes a 16-row x 32-column strip with mma.m16n8k16, both operands read
+// flops); a warp computes a 16-row x 32-column strip over its share of K with mma.m16n8k16, both operands read
 // straight from global memory with 16-byte loads.  K order inside an MMA is free as long as both
 // operands agree, so lane t simply takes 8 consecutive K of its row for two consecutive MMA steps.
 #include "common.cuh"
@@ -32,14 +32,16 @@ __device__ __forceinline__ void lr_mma<__nv_bfloat16>(float (&c)[4], uint32_t a0
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// down: [32, K] (rows >= rank are zero), out: [M, 32] fp32
+// down: [32, K] (rows >= rank are zero), out: [M, 32] fp32.  A CTA owns 16 rows; its four warps take every fourth
+// 32-K chunk each and add their partial strips through shared memory in warp order (M / 16 CTAs: 256 at M = 4096,
+// enough to keep every SM streaming).
 template <typename T>
 __global__ void __launch_bounds__(kLrWarps * 32)
 lowrank_down_kernel(const T* __restrict__ x, const T* __restrict__ down, float* __restrict__ out, int m, int k) {
+  __shared__ float part[kLrWarps][16][33];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int row0 = (blockIdx.x * kLrWarps + warp) * 16;
-  if (row0 >= m) return;
+  const int row0 = blockIdx.x * 16;
   const int ra = min(row0 + g, m - 1), rb = min(row0 + g + 8, m - 1);
   const uint4* xa = reinterpret_cast<const uint4*>(x + (size_t)ra * k) + t;
   const uint4* xb = reinterpret_cast<const uint4*>(x + (size_t)rb * k) + t;
@@ -51,7 +53,7 @@ lowrank_down_kernel(const T* __restrict__ x, const T* __restrict__ down, float* 
   for (int j = 0; j < 4; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   const int chunks = k / 32;   // 32 K per iteration: 4 lanes x 8 K
 #pragma unroll 4
-  for (int c = 0; c < chunks; ++c) {
+  for (int c = warp; c < chunks; c += kLrWarps) {
     const uint4 a = __ldg(xa + c * 4), b = __ldg(xb + c * 4);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -63,15 +65,27 @@ lowrank_down_kernel(const T* __restrict__ x, const T* __restrict__ down, float* 
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int col = 8 * j + 2 * t;
-    if (row0 + g < m) *reinterpret_cast<float2*>(out + (size_t)(row0 + g) * 32 + col) = make_float2(acc[j][0], acc[j][1]);
-    if (row0 + g + 8 < m) *reinterpret_cast<float2*>(out + (size_t)(row0 + g + 8) * 32 + col) = make_float2(acc[j][2], acc[j][3]);
+    part[warp][g][col] = acc[j][0];
+    part[warp][g][col + 1] = acc[j][1];
+    part[warp][g + 8][col] = acc[j][2];
+    part[warp][g + 8][col + 1] = acc[j][3];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 16 * 32; i += kLrWarps * 32) {
+    const int r = i >> 5, c = i & 31;
+    if (row0 + r < m) {
+      float s = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < kLrWarps; ++wv) s += part[wv][r][c];
+      out[(size_t)(row0 + r) * 32 + c] = s;
+    }
   }
 }
 
 int lowrank_down_launch(const void* x, const void* down, float* out, int m, int k, int act_dtype, cudaStream_t stream) {
   XQT_REQUIRE(m > 0 && k > 0 && k % 32 == 0);
   XQT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)down & 15) == 0 && ((uintptr_t)out & 7) == 0);
-  const int grid = ceil_div(m, kLrWarps * 16);
+  const int grid = ceil_div(m, 16);
   if (act_dtype == XQT_B200_BF16)
     lowrank_down_kernel<__nv_bfloat16><<<grid, kLrWarps * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)down, out, m, k);
   else

@@ -100,6 +100,13 @@ class _Linear:
         return w4a16_linear(x, self.qweight, self.scales, self.zeros, group_size=self.group,
                             nibble_signed=self.signed, k=self.k, out_dtype=odt, out=out)
 
+    def rows(self, x: torch.Tensor, n0: int, n1: int, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """The output channels [n0, n1) only: ``x @ W[n0:n1]^T`` (a row block of the canonical weight is contiguous)."""
+
+        return w4a16_linear(x, self.qweight[n0:n1], self.scales[n0:n1], None if self.zeros is None else self.zeros[n0:n1],
+                            group_size=self.group, nibble_signed=self.signed, k=self.k,
+                            out_dtype=self.dtype if out_dtype is None else out_dtype)
+
 
 class _InjectedLinear:
     """One layer served by a caller-supplied ``local_linear(x, weight, out_dtype=...)`` (the gloo tests run the
@@ -158,9 +165,35 @@ class W4A16SwiGLUMLP:
         if self._peer is not None and m <= 16:
             self.down(h, out_dtype=torch.float32, out=self._peer.partial(m, self.hidden))
             return self._peer.reduce(m, self.hidden, dtype=self.dtype)
-        partial = self.down(h, out_dtype=torch.float32)
-        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
-        return partial.to(self.dtype)
+        blocks = self._reduce_blocks(m)
+        if blocks == 1 or not isinstance(self.down, _Linear):
+            partial = self.down(h, out_dtype=torch.float32)
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+            return partial.to(self.dtype)
+        # The down projection in column blocks of the output: block j's fp32 partial sums are all-reduced (NCCL, its
+        # own stream) while block j + 1 is computed, so only the last block's reduction is exposed.  Blocks cut the
+        # weight's rows, every packed weight is still dequantised once.
+        width = self.hidden // blocks
+        parts, works = [], []
+        for j in range(blocks):
+            part = self.down.rows(h, j * width, (j + 1) * width, out_dtype=torch.float32)
+            works.append(dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            parts.append(part)
+        out = torch.empty((m, self.hidden), device=h.device, dtype=self.dtype)
+        for j, (part, work) in enumerate(zip(parts, works)):
+            work.wait()
+            out[:, j * width:(j + 1) * width].copy_(part)       # the cast to the activation dtype
+        return out
+
+    def _reduce_blocks(self, m: int) -> int:
+        """Column blocks of the row-parallel reduction: enough rows for the per-block GEMM to fill the GPU."""
+
+        forced = os.environ.get("XQT_B200_REDUCE_BLOCKS")
+        if forced:
+            return max(1, int(forced))
+        if m < 256 or self.hidden % 1024:
+            return 1
+        return 4 if m >= 1024 else 2
 
     def execution_metadata(self) -> dict:
         """Which kernels serve this block (the report xqt's runtime modules expose,
@@ -168,7 +201,8 @@ class W4A16SwiGLUMLP:
 
         return {
             "implementation": "b200_w4a16_swiglu_mlp", "world": self.world,
-            "reduction": "none" if self.world == 1 else ("peer_allreduce_kernel (M <= 16) / NCCL all-reduce" if self._peer else "NCCL all-reduce"),
+            "reduction": "none" if self.world == 1 else ("peer_allreduce_kernel (M <= 16) / " if self._peer else "") +
+                         "NCCL all-reduce of fp32 partial sums, in column blocks overlapped with the down projection from M = 256",
             "decode_layout": None if self.gate_up.tiled is None else self.gate_up.tiled.layout, "hidden": self.hidden,
             "inter_local": self.inter_local,
             "kernels": {"m<=16": {"lanes": "w4a16_decode_cl_kernel", "rows128": "w4a16_decode_tc_kernel"}.get(
