@@ -159,3 +159,36 @@ def test_svdq_w4a4_workspace_bind_and_registry_executor():
     dual = o44.composite_forward(rot.apply(x.float()), packed_r, scale_r, down, up, group_size=64, bias=bias)
     assert o16.rel_l2(result.output.float().cpu(), dual) < 0.25
     assert native.workspace_status(DEV) == 0
+
+
+@pytest.mark.parametrize("symmetric,scalar_scale", [(True, True), (False, False)])
+def test_awq_w4a8_decode(symmetric, scalar_scale):
+    """int8 activation codes with one scale against the W4 execution layout: exact integer group sums, fp32
+    scaling -- checked against the integer arithmetic of the reference's DP4A kernel restated on the CPU."""
+
+    from xqt_b200.layout import unpack_int4
+    from xqt_b200.ops import awq
+
+    n, k, m, group = 264, 1024, 3, 128
+    w = torch.randn((n, k), generator=seeded(40)) * 0.02
+    pw = quantize.quantize_w4_symmetric(w, group_size=group) if symmetric else quantize.quantize_w4_asymmetric(w, group_size=group)
+    codes = torch.randint(-127, 128, (m, k), generator=seeded(41), dtype=torch.int8)
+    scale_a = 0.0173
+    q = unpack_int4(pw.qweight, logical_k=k, signed=symmetric).to(torch.float64)
+    if not symmetric:
+        q = q - pw.zero_points.to(torch.float64).repeat_interleave(group, dim=1)
+    sums = torch.einsum("mgk,ngk->mng", codes.to(torch.float64).reshape(m, k // group, group), q.reshape(n, k // group, group))
+    ref = ((sums * pw.scales.to(torch.float64).unsqueeze(0)).sum(dim=2) * scale_a).to(torch.float32).to(torch.bfloat16)
+    execution = awq.prepack_b200_awq_w4a16_decode(_on_device(pw))
+    qweight, scales, zeros = awq.prepare_b200_awq_w4a16_decode_parameters(execution, dtype=torch.bfloat16)
+    out = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
+    sa = scale_a if scalar_scale else torch.tensor(scale_a, device=DEV)
+    got = awq.awq_w4a8_decode(codes.to(DEV), qweight, scales, sa, scaled_zeros=zeros, dtype=torch.bfloat16, output=out)
+    assert got is out and o16.rel_l2(out.cpu(), ref) <= 1e-3
+    run = awq.bind_awq_w4a8_decode(qweight, scales, zeros, rows=m, input_features=k, output_features=n, dtype=torch.bfloat16,
+                                   device=DEV, residual=True)
+    res = torch.randn((m, n), generator=seeded(42)).to(torch.bfloat16)
+    assert torch.equal(run(codes.to(DEV), sa, res.to(DEV)).cpu(), out.cpu() + res)
+    with pytest.raises(XQTBackendError):
+        awq.awq_w4a8_decode(codes.to(DEV).to(torch.bfloat16), qweight, scales, sa)
+    assert native.workspace_status(DEV) == 0

@@ -187,6 +187,8 @@ SM100 = frozenset({CapabilityRequirement.cuda(min_sm=(10, 0), max_sm=(10, 0))})
 B200_KERNELS = (
     KernelSpec("quantization.awq_w4a16_decode", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.awq:awq_w4a16_decode", SM100,
                "AWQ W4A16 decode (M<=16), xqt's signature: cluster split-K kernel on the lane-ordered layout"),
+    KernelSpec("quantization.awq_w4a8_decode", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.awq:awq_w4a8_decode", SM100,
+               "AWQ W4A8 decode (M<=16): int8 activation codes as exact integers through the cluster decode kernel"),
     KernelSpec("quantization.w4a16_decode_tiled", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.w4a16:w4a16_decode_tiled", SM100,
                "W4A16 decode (M<=16) on a TiledW4 execution layout (lanes / rows128 / tile128)"),
     KernelSpec("quantization.w4a16_linear", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.w4a16:w4a16_linear", SM100,

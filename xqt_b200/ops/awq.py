@@ -244,6 +244,77 @@ def awq_w4a16_decode_bias(inputs: torch.Tensor, qweight: torch.Tensor, scales: t
     return output
 
 
+def bind_awq_w4a8_decode(qweight: torch.Tensor, scales: torch.Tensor, scaled_zeros: torch.Tensor | None, *, rows: int,
+                         input_features: int, output_features: int, dtype: torch.dtype, device: torch.device,
+                         residual: bool = False) -> Callable:
+    """W4A8 decode: int8 activation codes with ONE activation scale against the same W4 execution layout,
+    ``y = s_a * sum_g s_w[n,g] * sum_{k in g} a_q[m,k] (code[n,k] - zero[n,g])`` (cf. ``bind_awq_w4a8_decode`` and the
+    DP4A kernel it binds, awq_w4a16_sm89.py:386-430, awq_w4a16_sm89_kernel.cu:595-724).  On B200 the integer codes go
+    through the cluster decode kernel as exact bf16/fp16 integers (|a_q| <= 127 is exact in either format, a group's
+    integer sum stays below 2^24), fp32 sums out, and the activation scale and rounding are one elementwise pass.
+    ``dtype`` is the output dtype (the reference takes it from ``scales``).  Returns ``run(codes, scale_a[, residual])``;
+    with ``residual=True`` the residual row is added in the output dtype, as the reference's ``_bias`` form does."""
+
+    rows, input_features, output_features = int(rows), int(input_features), int(output_features)
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    if not 1 <= rows <= 16 or dtype not in _SUPPORTED_DTYPES or device.type != "cuda":
+        raise XQTBackendError("bound AWQ W4A8 decode requires 1 <= rows <= 16, an FP16/BF16 output dtype and a CUDA device")
+    group = _check_static(qweight, scales, scaled_zeros, input_features=input_features, output_features=output_features,
+                          device=device)
+    lib = native.library()
+    if not lib.xqt_b200_w4a16_decode_lanes_supported(rows, output_features, input_features, group):
+        raise XQTBackendError("bound AWQ W4A8 decode: shape outside the B200 kernel's envelope")
+    fn = lib.xqt_b200_w4a16_decode_lanes
+    status = native.status_word(device)
+    head = (qweight.data_ptr(), scales.data_ptr(), native.ptr(scaled_zeros), 0, 0)
+    tail = (rows, output_features, input_features, group, 0, native.DTYPE_CODE[dtype], native.DTYPE_CODE[scales.dtype],
+            native.DTYPE_CODE[torch.float32], 0, status.data_ptr())
+    sums = torch.empty((rows, output_features), dtype=torch.float32, device=device)
+
+    def bound(codes: torch.Tensor, scale_a, residual_row: torch.Tensor | None = None) -> torch.Tensor:
+        if codes.dtype != torch.int8 or tuple(codes.shape) != (rows, input_features) or codes.device != device:
+            raise XQTBackendError("AWQ W4A8 inputs must be INT8 [rows, input_features] on the bound device")
+        exact = codes.to(dtype)                                       # integers up to 127: exact in fp16 and bf16
+        code = fn(exact.data_ptr(), *head, sums.data_ptr(), *tail, torch.cuda.current_stream(device).cuda_stream)
+        if code != 0:
+            native.check(code, "xqt_b200_w4a16_decode_lanes")
+        scale = scale_a.to(device=device, dtype=torch.float32).reshape(()) if isinstance(scale_a, torch.Tensor) else float(scale_a)
+        out = (sums * scale).to(dtype)
+        if residual:
+            if residual_row is None or residual_row.dtype != dtype or tuple(residual_row.shape) != (rows, output_features):
+                raise XQTBackendError("AWQ W4A8 residual must be [rows, output_features] in the output dtype")
+            out = out + residual_row
+        return out
+
+    bound.keep = (qweight, scales, scaled_zeros, status, sums)
+    return bound
+
+
+def awq_w4a8_decode(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, scale_a, *,
+                    scaled_zeros: torch.Tensor | None = None, dtype: torch.dtype | None = None,
+                    output: torch.Tensor | None = None) -> torch.Tensor:
+    """One W4A8 decode projection (cf. awq_w4a16_sm89.py:305-341): ``inputs`` int8 ``[M <= 16, K]``, ``scale_a`` a
+    tensor or a float.  ``scaled_zeros`` is the zero-point plane of the execution layout (None: symmetric, stored as
+    ``code ^ 8``); the output dtype is ``dtype``, by default the dtype of ``scales`` when that is fp16 / bf16, else bf16."""
+
+    if inputs.ndim != 2 or inputs.dtype != torch.int8:
+        raise XQTBackendError("AWQ W4A8 inputs must be INT8 rank-2")
+    if not inputs.is_cuda:
+        raise XQTBackendError("AWQ W4A8 inputs must be CUDA")
+    odt = dtype if dtype is not None else (scales.dtype if scales.dtype in _SUPPORTED_DTYPES else torch.bfloat16)
+    rows, k = int(inputs.shape[0]), int(inputs.shape[1])
+    n = int(qweight.shape[0]) * 128 if output is None else int(output.shape[1])
+    run = bind_awq_w4a8_decode(qweight, scales, scaled_zeros, rows=rows, input_features=k, output_features=n, dtype=odt,
+                               device=inputs.device)
+    result = run(inputs.contiguous(), scale_a)
+    if output is None:
+        return result
+    output.copy_(result)
+    return output
+
+
 def b200_awq_w4a16_decode_executor(activation, weight, *, spec, weight_scales=None, activation_scales=None,
                                    weight_zero_points=None, activation_zero_points=None, bias=None, residual=None,
                                    **_unused) -> torch.Tensor:
@@ -266,7 +337,7 @@ def b200_awq_w4a16_decode_executor(activation, weight, *, spec, weight_scales=No
 
 
 __all__ = [
-    "LANES_LAYOUT", "awq_w4a16_decode", "awq_w4a16_decode_bias", "b200_awq_w4a16_decode_executor", "bind_awq_w4a16_decode",
+    "LANES_LAYOUT", "awq_w4a8_decode", "bind_awq_w4a8_decode", "awq_w4a16_decode", "awq_w4a16_decode_bias", "b200_awq_w4a16_decode_executor", "bind_awq_w4a16_decode",
     "native_awq_w4a16_available", "native_awq_w4a16_shape_supported", "native_awq_w4a16_version",
     "prepack_b200_awq_w4a16_decode", "prepare_b200_awq_w4a16_decode_parameters",
 ]
