@@ -92,7 +92,7 @@ def test_mlp_two_ranks_nccl(tmp_path):
         port = s.getsockname()[1]
     script = tmp_path / "rank.py"
     script.write_text(_RANK_SCRIPT)
-    env = dict(os.environ, XQT_ROOT=str(ROOT), XQT_OUT=str(tmp_path), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, XQT_ROOT=str(ROOT), XQT_OUT=str(tmp_path), NCCL_NVLS_ENABLE="0", XQT_B200_REDUCE_BLOCKS="2")
     subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                     "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)], env=env, check=True,
                    timeout=300)

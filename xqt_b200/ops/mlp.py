@@ -186,14 +186,15 @@ class W4A16SwiGLUMLP:
         return out
 
     def _reduce_blocks(self, m: int) -> int:
-        """Column blocks of the row-parallel reduction: enough rows for the per-block GEMM to fill the GPU."""
+        """Column blocks of the row-parallel reduction.  One block (the whole partial in one all-reduce) unless
+        ``XQT_B200_REDUCE_BLOCKS`` asks for more: measured on two GPUs the blocked form is slower at every M (M = 4096:
+        850 / 867 / 950 us with 1 / 2 / 4 blocks; M = 512: 242 / 293 / 460 us) -- the narrower GEMMs lose more than the
+        overlapped part of a two-rank all-reduce gains.  More ranks shift that balance; it is a knob, not a default."""
 
         forced = os.environ.get("XQT_B200_REDUCE_BLOCKS")
-        if forced:
+        if forced and m >= 256 and self.hidden % (1024 * max(1, int(forced))) == 0:
             return max(1, int(forced))
-        if m < 256 or self.hidden % 1024:
-            return 1
-        return 4 if m >= 1024 else 2
+        return 1
 
     def execution_metadata(self) -> dict:
         """Which kernels serve this block (the report xqt's runtime modules expose,
@@ -202,7 +203,7 @@ class W4A16SwiGLUMLP:
         return {
             "implementation": "b200_w4a16_swiglu_mlp", "world": self.world,
             "reduction": "none" if self.world == 1 else ("peer_allreduce_kernel (M <= 16) / " if self._peer else "") +
-                         "NCCL all-reduce of fp32 partial sums, in column blocks overlapped with the down projection from M = 256",
+                         "NCCL all-reduce of fp32 partial sums (XQT_B200_REDUCE_BLOCKS: in column blocks overlapped with the down projection)",
             "decode_layout": None if self.gate_up.tiled is None else self.gate_up.tiled.layout, "hidden": self.hidden,
             "inter_local": self.inter_local,
             "kernels": {"m<=16": {"lanes": "w4a16_decode_cl_kernel", "rows128": "w4a16_decode_tc_kernel"}.get(
