@@ -192,7 +192,7 @@ class W4A16SwiGLUMLP:
         overlapped part of a two-rank all-reduce gains.  More ranks shift that balance; it is a knob, not a default."""
 
         forced = os.environ.get("XQT_B200_REDUCE_BLOCKS")
-        if forced and m >= 256 and self.hidden % (1024 * max(1, int(forced))) == 0:
+        if forced and m >= 256 and self.hidden % (128 * max(1, int(forced))) == 0:
             return max(1, int(forced))
         return 1
 
