@@ -167,3 +167,20 @@ def test_static_decode_status_is_readable():
     with torch.cuda.device(0):
         code = native.library().xqt_b200_w4a16_decode_static_status(ctypes.byref(value), native.stream_handle(torch.device("cuda", 0)))
     assert code == 0 and value.value == 0
+
+
+def test_mlp_block_as_cuda_graph_matches_eager_calls():
+    """`capture(rows)` replays the block from one CUDA graph: same bits as the eager call, for new inputs too."""
+
+    from xqt_b200 import native
+    from xqt_b200.ops.mlp import W4A16SwiGLUMLP
+    dev = torch.device("cuda", 0)
+    gate, up, down = _weights(1024, 2048, 20)
+    block = W4A16SwiGLUMLP(gate, up, down, device=dev)
+    replay = block.capture(4)
+    for seed in (1, 2):
+        x = torch.randn((4, 1024), generator=seeded(seed)).to(torch.bfloat16).to(dev)
+        replay.input.copy_(x)
+        got = replay().clone()
+        assert torch.equal(got, block(x))
+    assert native.workspace_status(dev) == 0

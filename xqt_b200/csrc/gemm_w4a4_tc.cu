@@ -27,11 +27,13 @@
 // the tensor core from bf16 hi/lo splits of both factors (hi x hi + lo x hi + hi x lo, fp32 sums; the
 // dropped lo x lo term is 2^-18 relative): six K = 16 steps over two 128-row operand images.
 //
-// Warp roles (576 threads): warp 0 TMA producer (both operand tiles per stage, weight scales per tile, the
-// two rank-R operand images per tile), warp 1 MMA issuer, warps 2-17 drain (tensor-memory lane quarter =
+// Warp roles (576 threads): warp 0 TMA producer (both operand tiles and the two scale rows of both sides per
+// stage, the two rank-R operand images per tile), warp 1 MMA issuer, warps 2-17 drain (tensor-memory lane quarter =
 // warp % 4, 32-column quarter = (warp - 2) / 4).  A drain warp reads a slab in the accumulator-fragment
 // distribution (tcgen05.ld shape 16x256b): lane t holds rows t/4 + {0, 8, 16, 24} and, of each 8-column
-// group, columns 2*(t%4), 2*(t%4)+1.  A thread then needs 4 activation scales and 8 weight scales per slab;
+// group, columns 2*(t%4), 2*(t%4)+1.  A thread then needs 4 activation scales and 8 weight scales per slab,
+// all from shared memory (activation scales read from global memory came back from L2 once per slab and
+// were the longest stall of the drain: 539 -> 485 us for the forward of the 4096 x 12288 x 3072 layer);
 // in the one-row-per-thread shape it would need 32 weight scales, every lane the same ones, and those
 // broadcast loads alone (128 bytes of register write-back per lane and slab) take more shared-memory pipe
 // time than the slab's MMAs.
@@ -58,15 +60,20 @@ enum Status : unsigned int { kTimeout = 64 };
 // barrier slots
 constexpr int kBarFull = 0, kBarEmpty = kBarFull + kMaxStages;
 constexpr int kBarPairFull = kBarEmpty + kMaxStages, kBarPairEmpty = kBarPairFull + kPairBufs;
-constexpr int kBarScaleFull = kBarPairEmpty + kPairBufs, kBarScaleEmpty = kBarScaleFull + 2;
-constexpr int kBarEpiFull = kBarScaleEmpty + 2, kBarEpiEmpty = kBarEpiFull + 1, kBarCount = kBarEpiEmpty + 1;
+constexpr int kBarEpiFull = kBarPairEmpty + kPairBufs, kBarEpiEmpty = kBarEpiFull + 1, kBarCount = kBarEpiEmpty + 1;
+// Scales travel with their stage: a ring of (stages + 2) slots of [w_scale: 2 groups x 128 | a_scale: 2 groups x 128]
+// fp32, filled by two bulk copies on the stage's full barrier.  A slot is rewritten for stage i only after the MMAs of
+// stage i - stages have completed; those were issued after the drain warps had released the pair buffer of two
+// hand-overs earlier, i.e. after they had read the scales of stage i - stages - 2: no barrier of its own.
+constexpr int kScaleSlotBytes = 2 * 2 * 128 * 4;                    // 2048
+constexpr int kScaleSlotsExtra = 2;
 }  // namespace w4a4
 
 struct W4A4Params {
   int m, n, k, groups;
-  int mtiles, ntiles, kstages, stages, scale_bufs;
+  int mtiles, ntiles, kstages, stages;
   int aux_tile_bytes;          // groups * 512 + kUpBytes
-  const float* a_scale_t;      // [groups, mtiles*128]: the activation scales transposed (rows past M are zero)
+  const float* a_scale_t;      // [mtiles][groups][128]: the activation scales, tile-major (rows past M are zero)
   const uint8_t* aux;          // per n-tile: w_scale * 2^18 as [groups][128] fp32, then the up factors as a 128-row operand image
   const uint8_t* la_tiles;     // per m-tile: the low-rank activations as a 128-row operand image (see w44_la_image_kernel)
   const float* bias;
@@ -81,6 +88,11 @@ __device__ __forceinline__ uint32_t w44_pack2(__nv_bfloat16*, float a, float b) 
 __device__ __forceinline__ uint32_t w44_pack2(__half*, float a, float b) {
   const __half2 v = __floats2half2_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float w44_lds32f(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ unsigned long long w44_lds64(uint32_t addr) {
   unsigned long long v;
@@ -116,8 +128,8 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
                                        volatile unsigned int* s_abort) {
   using namespace w4a4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nsb = p.scale_bufs;
-  const int scale_bytes = p.groups * 512;
+  const uint32_t nslots = (uint32_t)p.stages + kScaleSlotsExtra;
+  uint32_t slot = 0;                                  // ring slot of the stage being drained
   const int total_tiles = p.mtiles * p.ntiles;
   auto bar = [&](int slot) { return bar0 + 8u * (uint32_t)slot; };
   auto guarded_wait = [&](uint32_t b, uint32_t parity) {
@@ -132,10 +144,7 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
   uint32_t local = 0, pair = 0;                       // pair: hand-overs so far (one per stage, one per rank-R slab)
   for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
     const int mt = tile % p.mtiles, nt = tile / p.mtiles;
-    const int ab = local % nsb;
     const int row0 = mt * kBM + quarter * 32 + rq;       // the thread's rows are row0 + 8 i
-    const int mpad = p.mtiles * kBM;
-    const float* sp = p.a_scale_t + row0;                // one slab's scales of the four rows: sp[8 i]; next slab: + mpad
     // Two 16-register buffers: rows 0-15 and rows 16-31 of the warp's 32 x 32 part of a slab (one tcgen05.ld each).
     // While one is folded the other is in flight: a tensor-memory load takes about 150 cycles, and one warp's
     // share of the arithmetic between two waits has to cover it.
@@ -143,8 +152,8 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
     guarded_wait(bar(kBarPairFull + pair % kPairBufs), (pair / kPairBufs) & 1);
     tc_fence_after();
     tmem_ld_16x256b_x4(tlane + (pair % kPairBufs) * (2 * kBN), ra);
-    guarded_wait(bar(kBarScaleFull + ab), (local / nsb) & 1);
-    const uint32_t sw = scale_addr + (uint32_t)ab * (uint32_t)scale_bytes + (colq * 32 + 2 * c2) * 4;     // [groups][128] fp32
+    const uint32_t sw = scale_addr + (colq * 32 + 2 * c2) * 4;                  // this thread's first column pair of a w_scale row
+    const uint32_t sr = scale_addr + 1024 + (quarter * 32 + rq) * 4;            // its first row of an a_scale row
     float acc[32];                                    // [row i][column group j][x]: acc[8 i + 2 j + x]
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
@@ -169,7 +178,8 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
       const bool next_full = mbar_try_wait(bar(kBarPairFull + npair % kPairBufs), (npair / kPairBufs) & 1);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const uint32_t swg = sw + (uint32_t)(2 * ks + h) * (kBN * 4);
+        const uint32_t swg = sw + slot * kScaleSlotBytes + h * (kBN * 4);
+        const uint32_t srg = sr + slot * kScaleSlotBytes + h * (kBM * 4);
         const uint32_t tslab = tlane + pb * (2 * kBN) + h * kBN;
         float2 ws[4];
         float sa[4];
@@ -179,8 +189,7 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
           f32x2_unpack(w, ws[j].x, ws[j].y);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sa[i] = __ldg(sp + 8 * i);     // requested here, used after the tensor-memory wait below; a
-        sp += mpad;                                               // prefetch a slab ahead costs four registers the role does not have
+        for (int i = 0; i < 4; ++i) sa[i] = w44_lds32f(srg + 32 * i);   // rows row0 + 8 i
         tmem_wait_ld_dep(ra);                          // rows 0-15 of the slab
         tmem_ld_16x256b_x4(tslab + (16u << 16), rb);
         fold(ra, ws, sa, 0);
@@ -198,9 +207,8 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
         }
         fold(rb, ws, sa, 2);
       }
+      if (++slot == nslots) slot = 0;
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar(kBarScaleEmpty + ab));       // the tile's weight scales are consumed
     // rank-R branch: one more slab (la * up^T from the tensor core), added as it is; its first half is in flight
     {
       const int pb = pair % kPairBufs;
@@ -287,12 +295,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int ns = p.stages;
-  // dynamic shared memory: operand stages | weight scales (x scale_bufs) | up-factor image | low-rank activation image
+  // dynamic shared memory: operand stages | scale ring | up-factor image | low-rank activation image
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
-  const int scale_bytes = p.groups * 512;
+  const int scale_bytes = p.groups * 512;            // one tile's w_scale rows in `aux` (the up image follows them)
   unsigned char* scale_base = tiles + (size_t)ns * kStageBytes;
-  const int nsb = p.scale_bufs;
-  unsigned char* up_base = scale_base + (size_t)nsb * scale_bytes;
+  const uint32_t nslots = (uint32_t)ns + kScaleSlotsExtra;
+  unsigned char* up_base = scale_base + (size_t)nslots * kScaleSlotBytes;
   unsigned char* la_base = up_base + kUpBytes;
   const uint32_t bar0 = smem_addr(&bars[0]);
   auto bar = [&](int slot) { return bar0 + 8u * (uint32_t)slot; };
@@ -306,10 +314,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     for (int b = 0; b < kPairBufs; ++b) {
       mbar_init(bar(kBarPairFull + b), 1);
       mbar_init(bar(kBarPairEmpty + b), kDrainWarps);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(kBarScaleFull + b), 1);
-      mbar_init(bar(kBarScaleEmpty + b), kDrainWarps);
     }
     mbar_init(bar(kBarEpiFull), 1);
     mbar_init(bar(kBarEpiEmpty), 1);
@@ -345,21 +349,22 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (elect_one()) {
-      uint32_t it = 0, local = 0;
+      uint32_t it = 0, local = 0, slot = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
         const int mt = tile % p.mtiles, nt = tile / p.mtiles;
-        const int ab = local % nsb;
-        guarded_wait(bar(kBarScaleEmpty + ab), ((local / nsb) & 1) ^ 1);
-        mbar_expect_tx(bar(kBarScaleFull + ab), scale_bytes);
-        bulk_g2s(smem_addr(scale_base + (size_t)ab * scale_bytes), p.aux + (size_t)nt * p.aux_tile_bytes, scale_bytes,
-                 bar(kBarScaleFull + ab));
+        const uint8_t* wsrc = p.aux + (size_t)nt * p.aux_tile_bytes;
+        const uint8_t* asrc = reinterpret_cast<const uint8_t*>(p.a_scale_t) + (size_t)mt * scale_bytes;
         for (int ks = 0; ks < p.kstages; ++ks, ++it) {
           const int s = it % ns;
           guarded_wait(bar(kBarEmpty + s), ((it / ns) & 1) ^ 1);
           unsigned char* st = tiles + (size_t)s * kStageBytes;
-          mbar_expect_tx(bar(kBarFull + s), kStageBytes);
+          const uint32_t sc = smem_addr(scale_base + (size_t)slot * kScaleSlotBytes);
+          mbar_expect_tx(bar(kBarFull + s), kStageBytes + kScaleSlotBytes);
           tma_load_2d(smem_addr(st), &tm_a, ks * kStageK, mt * kBM, bar(kBarFull + s));
           tma_load_2d(smem_addr(st + kABytes), &tm_b, ks * kStageK, nt * kBN, bar(kBarFull + s));
+          bulk_g2s(sc, wsrc + (size_t)ks * 1024, 1024, bar(kBarFull + s));             // groups 2 ks, 2 ks + 1
+          bulk_g2s(sc + 1024, asrc + (size_t)ks * 1024, 1024, bar(kBarFull + s));
+          if (++slot == nslots) slot = 0;
         }
         // the tile's rank-R operand images; the MMAs of the previous tile's rank-R slab have released the buffers
         guarded_wait(bar(kBarEpiEmpty), (local & 1) ^ 1);
@@ -444,7 +449,7 @@ __global__ void __launch_bounds__(128) w44_la_image_kernel(const float* __restri
   }
 }
 
-// activation scales [M, G] -> [G, Mpad] (rows past M zero): a drain thread then walks one pointer per slab
+// activation scales [M, G] -> [Mpad/128][G][128] (rows past M zero): one stage's two groups of a 128-row tile are 1 KiB
 __global__ void __launch_bounds__(256) w44_scale_transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int m, int groups,
                                                                   int mpad) {
   __shared__ float tile[32][33];
@@ -457,7 +462,7 @@ __global__ void __launch_bounds__(256) w44_scale_transpose_kernel(const float* _
   __syncthreads();
   for (int y = ty; y < 32; y += 8) {
     const int g = g0 + y, r = r0 + tx;
-    if (g < groups && r < mpad) dst[(size_t)g * mpad + r] = tile[tx][y];
+    if (g < groups && r < mpad) dst[((size_t)(r >> 7) * groups + g) * 128 + (r & 127)] = tile[tx][y];
   }
 }
 
@@ -465,24 +470,19 @@ __global__ void __launch_bounds__(256) w44_scale_transpose_kernel(const float* _
 
 size_t w4a4_aux_tile_bytes(int k) { return (size_t)(k / 64) * 512 + w4a4::kUpBytes; }
 
-// shared-memory plan: operand stages and weight-scale buffers (the two rank-R images are fixed)
-static bool w4a4_plan(int k, int* stages, int* scale_bufs) {
+// shared-memory plan: operand stages, the scale ring that follows them, the two rank-R images
+static size_t w4a4_smem_bytes(int stages) {
   using namespace w4a4;
-  const int scale_bytes = (k / 64) * 512;
-  for (int nsb = 2; nsb >= 1; --nsb) {
-    int ns = (kSmemBudget - 1024 - kUpBytes - kLaBytes - nsb * scale_bytes) / kStageBytes;
-    if (ns > kMaxStages) ns = kMaxStages;
-    if (ns >= (nsb == 2 ? 3 : 2)) {
-      *stages = ns; *scale_bufs = nsb;
-      return true;
-    }
-  }
-  return false;
+  return (size_t)stages * kStageBytes + (size_t)(stages + kScaleSlotsExtra) * kScaleSlotBytes + kUpBytes + kLaBytes + 1024;
+}
+static int w4a4_stages() {
+  int ns = w4a4::kMaxStages;
+  while (ns > 2 && w4a4_smem_bytes(ns) > (size_t)w4a4::kSmemBudget) --ns;
+  return ns;
 }
 
 bool w4a4_gemm_supported(int m, int n, int k) {
-  int a, b;
-  return m >= 1 && n % 8 == 0 && k % 128 == 0 && k > 0 && w4a4_plan(k, &a, &b);
+  return m >= 1 && n % 8 == 0 && k % 128 == 0 && k > 0;
 }
 
 template <typename OutT>
@@ -491,11 +491,11 @@ static int launch_w4a4(const void* a_codes, const void* b_bytes, W4A4Params p, c
   CUtensorMap tm_a, tm_b;
   XQT_CUDA((cudaError_t)make_tile_map(&tm_a, a_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.m, p.k, kBM));
   XQT_CUDA((cudaError_t)make_tile_map(&tm_b, b_bytes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.n, p.k, kBN));
-  XQT_REQUIRE(w4a4_plan(p.k, &p.stages, &p.scale_bufs));
+  p.stages = w4a4_stages();
   p.mtiles = ceil_div(p.m, kBM);
   p.ntiles = ceil_div(p.n, kBN);
   p.kstages = p.k / kStageK;
-  const size_t smem_bytes = (size_t)p.stages * kStageBytes + (size_t)p.scale_bufs * p.groups * 512 + kUpBytes + kLaBytes + 1024;
+  const size_t smem_bytes = w4a4_smem_bytes(p.stages);
   auto kern = gemm_w4a4_kernel<OutT>;
   XQT_SMEM_OPT_IN(kern, kSmemBudget);
   int dev = 0, sms = 148;

@@ -58,25 +58,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
-// The same wait as a plain poll (mbarrier.test_wait never suspends the thread): for waits inside a
-// tight producer/consumer ring, where the wake-up of a suspended thread would cost more than the poll
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (kSpinLimit << 4); ++i)
-    if (mbar_test_wait(bar, parity)) return true;
-  return false;
-}
-
 // Two barriers at once.  A try_wait takes about 150 cycles to return its predicate even when the
 // phase has already completed, but independent ones pipeline: polling both in one go costs one
 // round trip instead of two.
@@ -226,17 +207,9 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "r"(taddr)
       : "memory");
 }
-// 16 lanes x 16 columns in the accumulator-fragment distribution (shape 16x256b, twice along the columns):
-// lane t of the warp holds rows t/4 and t/4 + 8 (relative to the lane in taddr) and, of every 8-column
-// group, the columns 2*(t%4) and 2*(t%4)+1: r[4j+0..1] = row t/4, r[4j+2..3] = row t/4 + 8 of group j.
-__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-}
-// the same shape four times along the columns: 16 lanes x 32 columns, r[4j+0..1] = row t/4, r[4j+2..3] = row t/4 + 8
-// of 8-column group j
+// 16 lanes x 32 columns in the accumulator-fragment distribution (shape 16x256b, four times along the columns):
+// lane t of the warp holds rows t/4 and t/4 + 8 (relative to the lane in taddr) and, of every 8-column group j, the
+// columns 2*(t%4) and 2*(t%4)+1: r[4j+0..1] = row t/4, r[4j+2..3] = row t/4 + 8
 __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
@@ -244,23 +217,6 @@ __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
-}
-__device__ __forceinline__ unsigned long long f32x2_add(unsigned long long a, unsigned long long b) {
-  unsigned long long d;
-  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld_dep8(uint32_t (&r)[8]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
-               :
-               : "memory");
 }
 // 32 registers -> this warp's 32 lanes x 32 columns
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -328,7 +284,7 @@ __device__ __forceinline__ void umma_ss_f8(uint32_t d_tmem, uint64_t adesc, uint
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// packed fp32 pairs: one issue slot for two multiplies / fused multiply-adds
+// a pair of fp32 values in one 64-bit register (shuffled as one value in the W4A4 store epilogue)
 __device__ __forceinline__ unsigned long long f32x2_pack(float lo, float hi) {
   unsigned long long v;
   asm("mov.b64 %0, {%1, %2};\n" : "=l"(v) : "f"(lo), "f"(hi));
@@ -336,16 +292,6 @@ __device__ __forceinline__ unsigned long long f32x2_pack(float lo, float hi) {
 }
 __device__ __forceinline__ void f32x2_unpack(unsigned long long v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long f32x2_mul(unsigned long long a, unsigned long long b) {
-  unsigned long long d;
-  asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ unsigned long long f32x2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
-  unsigned long long d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
 }
 // One K block of four SS MMA steps (descriptors a0..a3 / b0..b3), its commit to `done_bar`, and --
 // issued first, consumed last -- one poll of `next_bar`: the 150-cycle round trip of the poll runs

@@ -185,6 +185,36 @@ class W4A16SwiGLUMLP:
             out[:, j * width:(j + 1) * width].copy_(part)       # the cast to the activation dtype
         return out
 
+    def capture(self, rows: int):
+        """The block for a fixed row count as one CUDA graph (single-GPU blocks; the decode kernels chain through
+        programmatic dependent launch inside the graph, so the three launches run without host gaps -- what xqt's
+        graph decode runtime does around its modules, xqt/runtime/graph_decode.py).  Returns ``replay`` with
+        ``replay.input`` (``[rows, hidden]``, written by the caller, e.g. the target of its host-to-device copy) and
+        ``replay.output``; ``replay()`` launches the graph on the current stream and returns ``replay.output``."""
+
+        if self.world != 1:
+            raise XQTBackendError("capture: the peer-memory reduction takes its call number from the host and cannot be captured")
+        rows = int(rows)
+        device = self.gate_up.qweight.device
+        static_in = torch.zeros((rows, self.hidden), device=device, dtype=self.dtype)
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(2):                      # bind the callables and load the kernels outside the capture
+                self(static_in)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                static_out = self(static_in)
+        torch.cuda.current_stream(device).wait_stream(side)
+
+        def replay() -> torch.Tensor:
+            graph.replay()
+            return static_out
+
+        replay.input, replay.output, replay.graph = static_in, static_out, graph
+        return replay
+
     def _reduce_blocks(self, m: int) -> int:
         """Column blocks of the row-parallel reduction.  One block (the whole partial in one all-reduce) unless
         ``XQT_B200_REDUCE_BLOCKS`` asks for more: measured on two GPUs the blocked form is slower at every M (M = 4096:
@@ -208,7 +238,8 @@ class W4A16SwiGLUMLP:
             "inter_local": self.inter_local,
             "kernels": {"m<=16": {"lanes": "w4a16_decode_cl_kernel", "rows128": "w4a16_decode_tc_kernel"}.get(
                             None if self.gate_up.tiled is None else self.gate_up.tiled.layout, "w4a16_decode_kernel"),
-                        "m>16": "gemm_w4a16_kernel", "gating": "swiglu_kernel"},
+                        "17<=m<=128": "gemm_w4a16_fused_kernel (where it fills the SMs) else dequant_w4_f16_kernel + gemm_f16_kernel",
+                        "m>128": "dequant_w4_f16_kernel + gemm_f16_kernel", "gating": "swiglu_kernel"},
         }
 
 
