@@ -698,7 +698,7 @@ def measure_other_configs(device, world, rank, barrier) -> list:
     _log(f"w8a8: full {t_full:.1f} us, gemm {t_gemm:.1f} us")
 
     # ---------------------------------------------------------------- SVDQuant W4A4, M=4096, K=3072, N=12288, rank 32
-    from xqt_b200.ops.w4a4 import pack_svdq_w4a4_linear, svdq_w4a4_linear
+    from xqt_b200.ops.w4a4 import bind_svdq_w4a4_linear, pack_svdq_w4a4_linear, svdq_w4a4_linear
 
     m, n, k, r = 4096, 12288, 3072, 32
     rot4 = quantize.randomized_rotation(128, seed=3)
@@ -723,14 +723,23 @@ def measure_other_configs(device, world, rank, barrier) -> list:
         cpu = (sec, runs, cores, "oracle.w4a4.w4a4_forward (rotation, group-64 int4 activations, per-slab integer GEMM, low rank)")
     for form, kernel, note in (("integer", "gemm_w4a4_kernel", "default form: exact FP8 operands on tcgen05 kind::f8f6f4, per-group fp32 scaling; meets the 1e-3 parity bar"),
                                ("dense", "gemm_f16_kernel", "opt-in form: operands expanded to fp16; rel-L2 1.2e-3 at this K, above the 1e-3 bar")):
-        call = lambda xx, f=form: svdq_w4a4_linear(xx, layer, form=f)  # noqa: E731
+        extra = {"note": note}
+        if form == "integer":
+            # the steady-state callable (workspace and operand cache bound once); the unbound call, which widens the
+            # weights on every call and allocates its buffers, is timed beside it
+            call = bind_svdq_w4a4_linear(layer, rows=m, operand_cache=True)
+            unbound = lambda xx: svdq_w4a4_linear(xx, layer, form="integer")  # noqa: E731
+            extra["call"] = "bind_svdq_w4a4_linear(packed, rows=M, operand_cache=True): weights also held as one operand byte each"
+            extra["unbound_us_per_call"] = round(_time_us(lambda: unbound(x4), barrier, reps=5, warm=1), 2)
+        else:
+            call = lambda xx, f=form: svdq_w4a4_linear(xx, layer, form=f)  # noqa: E731
         t4, clocks = _timed_with_clocks(lambda: call(x4), barrier, index, 5, 1, device)
         records.append(_record(
             f"cfg3_w4a4_svdquant_{form}", {"workload": "w4a4_svdquant_linear_M4096_K3072_N12288_r32", "form": form, "world": 1,
                                           "inputs": "1 % outlier channels x20; rank-32 factors from a truncated SVD of the rotated weight"},
             metric="w4a4_linear_throughput", unit="TOP/s", work=ops4, us=t4, bound="tensor", peak=i8_peak, peak_source=i8_kind, kernel=kernel,
             algorithmic="2*M*N*K over the full forward (rotate + quantise + low-rank down + GEMM with low-rank up)", clocks=clocks,
-            e2e=_e2e_us(x_host, call, barrier, 3, device), cpu=cpu if form == "integer" else None, extra={"note": note}))
+            e2e=_e2e_us(x_host, call, barrier, 3, device), cpu=cpu if form == "integer" else None, extra=extra))
         _log(f"w4a4 {form}: {t4:.1f} us")
     records.append({"name": "i8_library_gemm_peak", "value": round(i8_peak, 1), "unit": "TOP/s", "source": i8_kind})
     return records
@@ -738,7 +747,7 @@ def measure_other_configs(device, world, rank, barrier) -> list:
 
 def run_single_case(args) -> None:
     """One of the other configurations alone, a few eager calls: the small command used for ncu
-    captures of the GEMM-shaped kernels (`--case mlp:M`, `--case w8a8`, `--case w4a4[:integer|dense]`)."""
+    captures of the GEMM-shaped kernels (`--case mlp:M`, `--case w8a8`, `--case w4a4[:integer|dense|cached]`)."""
 
     from xqt_b200 import quantize
 
@@ -768,13 +777,15 @@ def run_single_case(args) -> None:
         fn = lambda: convrot_w8a8_linear(x, packed, rot_size=256)  # noqa: E731
         work = 2.0 * m * n * k
     elif name == "w4a4":
-        from xqt_b200.ops.w4a4 import pack_svdq_w4a4_linear, svdq_w4a4_linear
+        from xqt_b200.ops.w4a4 import pack_svdq_w4a4_linear, svdq_w4a4_linear, with_operand_cache
 
         m, n, k, r = 4096, 12288, 3072, 32
         rot4 = quantize.randomized_rotation(128, seed=3)
         layer = pack_svdq_w4a4_linear(torch.randn((n, k), device=device) * 0.02, torch.randn((r, k), device=device) * 0.05,
                                       torch.randn((n, r), device=device) * 0.05, None, rotation=rot4)
         x4 = torch.randn((m, k), device=device, dtype=torch.bfloat16)
+        if arg == "cached":                       # the integer form with the weights' operand bytes held by the layer
+            layer, arg = with_operand_cache(layer), "integer"
         fn = lambda: svdq_w4a4_linear(x4, layer, form=arg or "integer")  # noqa: E731
         work = 2.0 * m * n * k
     else:

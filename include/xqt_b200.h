@@ -232,6 +232,8 @@ int xqt_b200_w4a16_decode_static_status(unsigned int* host_status, xqt_b200_stre
  *                    convrot_4bit.py:669-679), replicated into scales [M, K/64]
  *                 5: the scales and codes of 4, every code written as the byte sign << 7 | magnitude (read as
  *                    FP8 E4M3 that is code * 2^-9 exactly): the operand form xqt_b200_w4a4_gemm consumes
+ *                 6: as 5 (group_size 64 or 0) with the scales tile-major, [ceil(M/128)][K/64][128] floats (row r,
+ *                    slot g at ((r/128)*K/64 + g)*128 + r%128): what xqt_b200_w4a4_gemm takes with flag 1
  *   codes         one byte per element [M, K] in every mode (int8 for 8 and 4);  rotated: [M, K] act_dtype or
  *                 NULL (the rotated, rounded activation, input of the W4A4 low-rank branch)
  */
@@ -279,16 +281,25 @@ int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const fl
  *               use), then scratch the call fills itself: the la operand images and the weights widened to one
  *               sign-magnitude byte each ([N, K], converted once per call by a streaming pre-pass so that the GEMM
  *               takes both operands by TMA; the packed 4-bit storage stays the only persistent copy).
+ *   flags       bit 0: act_scales is tile-major (quant_bits 6 above); bit 1: la points at the operand images
+ *               xqt_b200_lowrank_down wrote through la_image (ceil(M/128) images of 16 KiB, 128-byte aligned: row r
+ *               holds bf16 [hi(32) | lo(32)] of its 32 values, 16-byte chunk c at c ^ (r & 7)) instead of fp32 [M,32].
+ *               With both set the call launches the GEMM alone (plus the weight widening unless weight_bytes is given).
+ *   weight_bytes  null, or the [N, K] bytes xqt_b200_w4a4_expand_weight made of qweight once (16-byte aligned): an
+ *               operand cache the caller chooses to hold (one byte per weight beside the packed half byte); the
+ *               per-call widening pass is then skipped and qweight may be null.
  */
 size_t xqt_b200_w4a4_workspace_bytes(int m, int n, int k);
-int xqt_b200_lowrank_down(const void* rotated, const void* down, float* la, int m, int k, int act_dtype,
+int xqt_b200_lowrank_down(const void* rotated, const void* down, float* la, void* la_image, int m, int k, int act_dtype,
                           xqt_b200_stream_t stream);
 size_t xqt_b200_w4a4_aux_tile_bytes(int k);
 int xqt_b200_w4a4_supported(int m, int n, int k);
+int xqt_b200_w4a4_expand_weight(const void* qweight, void* weight_bytes, int n, int k,
+                                xqt_b200_stream_t stream);
 int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const void* qweight,
-                       const void* aux, const float* la, const float* bias, void* output, int m, int n,
-                       int k, int out_dtype, void* workspace, size_t workspace_bytes,
-                       xqt_b200_stream_t stream);
+                       const void* weight_bytes, const void* aux, const float* la, const float* bias,
+                       void* output, int m, int n, int k, int out_dtype, int flags, void* workspace,
+                       size_t workspace_bytes, xqt_b200_stream_t stream);
 
 /* The same linear in its operand-dequantised form, for M >= 256 (xqt_b200_w4a4_dense_preferred):
  * both operands are expanded once per call to fp16 -- code * scale, an exact fp32 product rounded

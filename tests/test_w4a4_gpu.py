@@ -87,6 +87,24 @@ def test_convrot_w4a4_without_low_rank_and_fp16():
     assert o16.rel_l2(out.cpu(), ref) <= 1e-3
 
 
+def test_operand_cache_gives_the_same_bits():
+    """Weights held in operand form (one byte each) by the layer: same output as widening them on every call."""
+
+    from xqt_b200.ops.w4a4 import bind_svdq_w4a4_linear, with_operand_cache
+    m, n, k, rank = 200, 384, 1024, 16
+    rot = quantize.randomized_rotation(128, seed=6)
+    x = _outliers(torch.randn((m, k), generator=seeded(3)), 5).to(torch.bfloat16).to(DEV)
+    packed_w, scale, down, up = _layer(n, k, rank, 31, rot)
+    layer = pack_svdq_w4a4_linear(None, down.to(DEV), up.to(DEV), None, packed_residual=packed_w.to(DEV),
+                                  residual_scale=scale.to(DEV), rotation=rot)
+    plain = svdq_w4a4_linear(x, layer)
+    cached = with_operand_cache(layer)
+    assert cached.weight_bytes.shape == (n, k) and layer.weight_bytes is None
+    assert torch.equal(svdq_w4a4_linear(x, cached), plain)
+    assert torch.equal(bind_svdq_w4a4_linear(layer, rows=m, operand_cache=True)(x), plain)
+    assert native.workspace_status(DEV) == 0
+
+
 def test_dense_form_is_opt_in_and_close_to_the_integer_form():
     m, n, k, rank = 300, 264, 512, 8
     assert native.library().xqt_b200_w4a4_dense_preferred(m, n, k) == 1      # faster here, but never chosen silently

@@ -32,10 +32,11 @@ size_t w4a16_gemm_tc_workspace_bytes(int m, int n, int k);
 bool w4a16_gemm_tc_any_zero_point(int m);
 bool w4a16_gemm_tc_supported(int m, int n, int k, int padded_k, int group_size);
 bool w4a16_gemm_fused_preferred(int m, int n, int k, int padded_k, int group_size);
-int lowrank_down_launch(const void*, const void*, float*, int, int, int, cudaStream_t);
+int lowrank_down_launch(const void*, const void*, float*, void*, int, int, int, cudaStream_t);
 size_t w4a4_workspace_bytes(int m, int n, int k);
-int w4a4_gemm_launch(const void*, const float*, const void*, const void*, const float*, const float*, void*, int, int, int,
-                     int, void*, cudaStream_t);
+int w4a4_gemm_launch(const void*, const float*, const void*, const void*, const void*, const float*, const float*, void*, int,
+                     int, int, int, int, void*, cudaStream_t);
+int w4a4_expand_weight_launch(const void*, void*, int, int, cudaStream_t);
 size_t w4a4_aux_tile_bytes(int k);
 bool w4a4_gemm_supported(int m, int n, int k);
 int rotate_quant_launch(const void*, const float*, void*, float*, void*, int, int, int, int, int, int, int, cudaStream_t);
@@ -270,25 +271,30 @@ int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const fl
                         reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
 }
 
-int xqt_b200_lowrank_down(const void* rotated, const void* down, float* la, int m, int k, int act_dtype,
+int xqt_b200_lowrank_down(const void* rotated, const void* down, float* la, void* la_image, int m, int k, int act_dtype,
                           xqt_b200_stream_t stream) {
   if (m == 0) return 0;
-  XQT_REQUIRE(rotated != nullptr && down != nullptr && la != nullptr);
+  XQT_REQUIRE(rotated != nullptr && down != nullptr && (la != nullptr || la_image != nullptr));
   XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
-  return lowrank_down_launch(rotated, down, la, m, k, act_dtype, (cudaStream_t)stream);
+  return lowrank_down_launch(rotated, down, la, la_image, m, k, act_dtype, (cudaStream_t)stream);
 }
 
 size_t xqt_b200_w4a4_aux_tile_bytes(int k) { return k > 0 && k % 64 == 0 ? w4a4_aux_tile_bytes(k) : 0; }
 
 int xqt_b200_w4a4_supported(int m, int n, int k) { return w4a4_gemm_supported(m, n, k) ? 1 : 0; }
 
-int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const void* qweight, const void* aux,
-                       const float* la, const float* bias, void* output, int m, int n, int k, int out_dtype,
-                       void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
+int xqt_b200_w4a4_gemm(const void* act_codes, const float* act_scales, const void* qweight, const void* weight_bytes,
+                       const void* aux, const float* la, const float* bias, void* output, int m, int n, int k,
+                       int out_dtype, int flags, void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
   if (m == 0) return 0;
   XQT_REQUIRE(m > 0 && workspace != nullptr && workspace_bytes >= w4a4_workspace_bytes(m, n, k) && ((uintptr_t)workspace & 255) == 0);
-  return w4a4_gemm_launch(act_codes, act_scales, qweight, aux, la, bias, output, m, n, k, out_dtype, workspace,
-                          (cudaStream_t)stream);
+  XQT_REQUIRE((flags & ~3) == 0);
+  return w4a4_gemm_launch(act_codes, act_scales, qweight, weight_bytes, aux, la, bias, output, m, n, k, out_dtype, flags,
+                          workspace, (cudaStream_t)stream);
+}
+
+int xqt_b200_w4a4_expand_weight(const void* qweight, void* weight_bytes, int n, int k, xqt_b200_stream_t stream) {
+  return w4a4_expand_weight_launch(qweight, weight_bytes, n, k, (cudaStream_t)stream);
 }
 
 size_t xqt_b200_w4a4_workspace_bytes(int m, int n, int k) {

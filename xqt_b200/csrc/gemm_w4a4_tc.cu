@@ -154,18 +154,19 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
     tmem_ld_16x256b_x4(tlane + (pair % kPairBufs) * (2 * kBN), ra);
     const uint32_t sw = scale_addr + (colq * 32 + 2 * c2) * 4;                  // this thread's first column pair of a w_scale row
     const uint32_t sr = scale_addr + 1024 + (quarter * 32 + rq) * 4;            // its first row of an a_scale row
-    float acc[32];                                    // [row i][column group j][x]: acc[8 i + 2 j + x]
+    unsigned long long acc[16];                       // [row i][column group j]: columns (8 j + 2 c2, + 1) of row row0 + 8 i as one f32x2
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    // 16 rows (i0, i0 + 1) x 32 columns: acc += r * (a_s[row] * w_s[column])
-    auto fold = [&](const uint32_t (&r)[16], const float2 (&ws)[4], const float (&sa)[4], int i0) {
+    for (int i = 0; i < 16; ++i) acc[i] = 0ull;
+    // 16 rows (i0, i0 + 1) x 32 columns: acc += r * (a_s[row] * w_s[column]), two columns per packed instruction
+    auto fold = [&](const uint32_t (&r)[16], const unsigned long long (&ws)[4], const float (&sa)[4], int i0) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int ii = 0; ii < 2; ++ii) {
+        const int i = i0 + ii;
+        const unsigned long long sa2 = f32x2_pack(sa[i], sa[i]);
 #pragma unroll
-        for (int ii = 0; ii < 2; ++ii) {
-          const int i = i0 + ii;
-          acc[8 * i + 2 * j] = fmaf(__uint_as_float(r[4 * j + 2 * ii]), __fmul_rn(sa[i], ws[j].x), acc[8 * i + 2 * j]);
-          acc[8 * i + 2 * j + 1] = fmaf(__uint_as_float(r[4 * j + 2 * ii + 1]), __fmul_rn(sa[i], ws[j].y), acc[8 * i + 2 * j + 1]);
+        for (int j = 0; j < 4; ++j) {
+          const unsigned long long r2 = f32x2_pack(__uint_as_float(r[4 * j + 2 * ii]), __uint_as_float(r[4 * j + 2 * ii + 1]));
+          acc[4 * i + j] = f32x2_fma(r2, f32x2_mul(sa2, ws[j]), acc[4 * i + j]);
         }
       }
     };
@@ -181,13 +182,10 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
         const uint32_t swg = sw + slot * kScaleSlotBytes + h * (kBN * 4);
         const uint32_t srg = sr + slot * kScaleSlotBytes + h * (kBM * 4);
         const uint32_t tslab = tlane + pb * (2 * kBN) + h * kBN;
-        float2 ws[4];
+        unsigned long long ws[4];
         float sa[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {                  // columns 8 j + 2 c2, + 1
-          const unsigned long long w = w44_lds64(swg + j * 32);
-          f32x2_unpack(w, ws[j].x, ws[j].y);
-        }
+        for (int j = 0; j < 4; ++j) ws[j] = w44_lds64(swg + j * 32);     // columns 8 j + 2 c2, + 1
 #pragma unroll
         for (int i = 0; i < 4; ++i) sa[i] = w44_lds32f(srg + 32 * i);   // rows row0 + 8 i
         tmem_wait_ld_dep(ra);                          // rows 0-15 of the slab
@@ -218,10 +216,8 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
 #pragma unroll
-        for (int ii = 0; ii < 2; ++ii) {
-          acc[8 * ii + 2 * j] += __uint_as_float(ra[4 * j + 2 * ii]);
-          acc[8 * ii + 2 * j + 1] += __uint_as_float(ra[4 * j + 2 * ii + 1]);
-        }
+        for (int ii = 0; ii < 2; ++ii)
+          acc[4 * ii + j] = f32x2_add(acc[4 * ii + j], f32x2_pack(__uint_as_float(ra[4 * j + 2 * ii]), __uint_as_float(ra[4 * j + 2 * ii + 1])));
       }
       tmem_wait_ld_dep(rb);
       tc_fence_before();
@@ -230,10 +226,8 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
 #pragma unroll
-        for (int ii = 0; ii < 2; ++ii) {
-          acc[8 * (2 + ii) + 2 * j] += __uint_as_float(rb[4 * j + 2 * ii]);
-          acc[8 * (2 + ii) + 2 * j + 1] += __uint_as_float(rb[4 * j + 2 * ii + 1]);
-        }
+        for (int ii = 0; ii < 2; ++ii)
+          acc[4 * (2 + ii) + j] = f32x2_add(acc[4 * (2 + ii) + j], f32x2_pack(__uint_as_float(rb[4 * j + 2 * ii]), __uint_as_float(rb[4 * j + 2 * ii + 1])));
       }
       ++pair;
     }
@@ -249,7 +243,7 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
       // before: v[j] holds columns 8 j + 2 c2 (+1); after: columns 8 c2 + 2 j (+1).
       unsigned long long v[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = f32x2_pack(acc[8 * i + 2 * j], acc[8 * i + 2 * j + 1]);
+      for (int j = 0; j < 4; ++j) v[j] = acc[4 * i + j];
       // 4 x 4 transpose over the lanes c2 = 0..3 in two exchange steps
 #pragma unroll
       for (int step = 1; step <= 2; step <<= 1) {
@@ -512,36 +506,61 @@ static size_t w4a4_images_bytes(int m) { return (size_t)ceil_div(m, w4a4::kBM) *
 static size_t w4a4_scales_bytes(int m, int k) { return (size_t)ceil_div(m, w4a4::kBM) * w4a4::kBM * (k / 64) * sizeof(float); }
 size_t w4a4_workspace_bytes(int m, int n, int k) { return 256 + w4a4_images_bytes(m) + w4a4_scales_bytes(m, k) + (size_t)n * k; }
 
-int w4a4_gemm_launch(const void* a_codes, const float* a_scale, const void* qweight, const void* aux, const float* la,
-                     const float* bias, void* out, int m, int n, int k, int out_dtype, void* workspace,
-                     cudaStream_t stream) {
+int w4a4_expand_weight_launch(const void* qweight, void* weight_bytes, int n, int k, cudaStream_t stream) {
+  XQT_REQUIRE(qweight != nullptr && weight_bytes != nullptr && n > 0 && k > 0 && k % 32 == 0);
+  XQT_REQUIRE(((uintptr_t)qweight & 15) == 0 && ((uintptr_t)weight_bytes & 15) == 0);
+  const size_t chunks = (size_t)n * k / 32;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const size_t want = (chunks + 255) / 256;
+  w44_expand_kernel<<<(unsigned)(want < (size_t)sms * 8 ? want : (size_t)sms * 8), 256, 0, stream>>>(
+      reinterpret_cast<const uint4*>(qweight), reinterpret_cast<uint4*>(weight_bytes), chunks);
+  return launch_status();
+}
+
+// weight_bytes: null, or the [N, K] sign-magnitude bytes w4a4_expand_weight_launch made of qweight (a caller-held
+// operand cache: the per-call widening pass is skipped).  flags bit 0: a_scale is already tile-major
+// [ceil(M/128)][K/64][128] (rotate_quant mode 6); bit 1: la points at the operand images lowrank_down wrote, not at
+// fp32 [M, 32] -- the two preparation launches are skipped.
+int w4a4_gemm_launch(const void* a_codes, const float* a_scale, const void* qweight, const void* weight_bytes,
+                     const void* aux, const float* la, const float* bias, void* out, int m, int n, int k, int out_dtype,
+                     int flags, void* workspace, cudaStream_t stream) {
   unsigned int* status = reinterpret_cast<unsigned int*>(workspace);
   XQT_REQUIRE(w4a4_gemm_supported(m, n, k));
-  XQT_REQUIRE(a_codes != nullptr && a_scale != nullptr && qweight != nullptr && aux != nullptr && la != nullptr &&
-              out != nullptr && status != nullptr);
-  XQT_REQUIRE(((uintptr_t)qweight & 15) == 0 && ((uintptr_t)aux & 15) == 0 && ((uintptr_t)la & 15) == 0 &&
-              ((uintptr_t)out & 15) == 0 && ((uintptr_t)a_codes & 15) == 0);
+  XQT_REQUIRE(a_codes != nullptr && a_scale != nullptr && (qweight != nullptr || weight_bytes != nullptr) && aux != nullptr &&
+              la != nullptr && out != nullptr && status != nullptr);
+  XQT_REQUIRE(((uintptr_t)aux & 15) == 0 && ((uintptr_t)la & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+              ((uintptr_t)a_codes & 15) == 0 && ((uintptr_t)weight_bytes & 15) == 0);
   W4A4Params p{};
   p.m = m; p.n = n; p.k = k; p.groups = k / 64;
   p.aux_tile_bytes = (int)w4a4_aux_tile_bytes(k);
   p.aux = (const uint8_t*)aux; p.bias = bias;
   uint8_t* images = reinterpret_cast<uint8_t*>(workspace) + 256;
   float* scales_t = reinterpret_cast<float*>(images + w4a4_images_bytes(m));
-  uint8_t* b_bytes = reinterpret_cast<uint8_t*>(scales_t) + w4a4_scales_bytes(m, k);
+  const uint8_t* b_bytes = reinterpret_cast<const uint8_t*>(weight_bytes);
   const int mpad = ceil_div(m, w4a4::kBM) * w4a4::kBM;
-  w44_scale_transpose_kernel<<<dim3(mpad / 32, ceil_div(p.groups, 32)), 256, 0, stream>>>(a_scale, scales_t, m, p.groups, mpad);
-  XQT_CUDA(cudaGetLastError());
-  p.a_scale_t = scales_t;
+  if (flags & 1) {
+    XQT_REQUIRE(((uintptr_t)a_scale & 15) == 0);
+    p.a_scale_t = a_scale;
+  } else {
+    w44_scale_transpose_kernel<<<dim3(mpad / 32, ceil_div(p.groups, 32)), 256, 0, stream>>>(a_scale, scales_t, m, p.groups, mpad);
+    XQT_CUDA(cudaGetLastError());
+    p.a_scale_t = scales_t;
+  }
   XQT_REQUIRE(((uintptr_t)images & 15) == 0);
-  w44_la_image_kernel<<<ceil_div(m, w4a4::kBM), 128, 0, stream>>>(la, images);
-  XQT_CUDA(cudaGetLastError());
-  const size_t chunks = (size_t)n * k / 32;
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const size_t want = (chunks + 255) / 256;
-  w44_expand_kernel<<<(unsigned)(want < (size_t)sms * 8 ? want : (size_t)sms * 8), 256, 0, stream>>>(
-      reinterpret_cast<const uint4*>(qweight), reinterpret_cast<uint4*>(b_bytes), chunks);
-  XQT_CUDA(cudaGetLastError());
+  if (flags & 2) {
+    XQT_REQUIRE(((uintptr_t)la & 127) == 0);
+    images = const_cast<uint8_t*>(reinterpret_cast<const uint8_t*>(la));
+  } else {
+    w44_la_image_kernel<<<ceil_div(m, w4a4::kBM), 128, 0, stream>>>(la, images);
+    XQT_CUDA(cudaGetLastError());
+  }
+  if (b_bytes == nullptr) {
+    uint8_t* scratch_bytes = reinterpret_cast<uint8_t*>(scales_t) + w4a4_scales_bytes(m, k);
+    const int rc = w4a4_expand_weight_launch(qweight, scratch_bytes, n, k, stream);
+    if (rc != 0) return rc;
+    b_bytes = scratch_bytes;
+  }
   p.la_tiles = images;
   p.out = out; p.status = status;
   if (out_dtype == XQT_B200_BF16) return launch_w4a4<__nv_bfloat16>(a_codes, b_bytes, p, stream);

@@ -32,12 +32,15 @@ __device__ __forceinline__ void lr_mma<__nv_bfloat16>(float (&c)[4], uint32_t a0
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// down: [32, K] (rows >= rank are zero), out: [M, 32] fp32.  A CTA owns 16 rows; its four warps take every fourth
+// down: [32, K] (rows >= rank are zero), out: [M, 32] fp32 (may be null).  image (may be null): the same values as the
+// W4A4 GEMM's tensor-core operand, one 16 KiB image per 128 rows: row r holds bf16 [hi(32) | lo(32)], hi = bf16(v),
+// lo = bf16(v - hi), its eight 16-byte chunks stored at chunk index c ^ (r & 7) (128-byte swizzle).  A CTA owns 16 rows; its four warps take every fourth
 // 32-K chunk each and add their partial strips through shared memory in warp order (M / 16 CTAs: 256 at M = 4096,
 // enough to keep every SM streaming).
 template <typename T>
 __global__ void __launch_bounds__(kLrWarps * 32)
-lowrank_down_kernel(const T* __restrict__ x, const T* __restrict__ down, float* __restrict__ out, int m, int k) {
+lowrank_down_kernel(const T* __restrict__ x, const T* __restrict__ down, float* __restrict__ out,
+                    unsigned char* __restrict__ image, int m, int k) {
   __shared__ float part[kLrWarps][16][33];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -77,19 +80,27 @@ lowrank_down_kernel(const T* __restrict__ x, const T* __restrict__ down, float* 
       float s = 0.f;
 #pragma unroll
       for (int wv = 0; wv < kLrWarps; ++wv) s += part[wv][r][c];
-      out[(size_t)(row0 + r) * 32 + c] = s;
+      if (out != nullptr) out[(size_t)(row0 + r) * 32 + c] = s;
+      if (image != nullptr) {
+        const int row = row0 + r;
+        unsigned char* dst = image + (size_t)row * 128;        // tiles of 128 rows x 128 bytes are contiguous
+        const __nv_bfloat16 hi = __float2bfloat16_rn(s), lo = __float2bfloat16_rn(s - __bfloat162float(hi));
+        *reinterpret_cast<__nv_bfloat16*>(dst + ((((c >> 3)) ^ (row & 7)) << 4) + (c & 7) * 2) = hi;
+        *reinterpret_cast<__nv_bfloat16*>(dst + ((((c >> 3) + 4) ^ (row & 7)) << 4) + (c & 7) * 2) = lo;
+      }
     }
   }
 }
 
-int lowrank_down_launch(const void* x, const void* down, float* out, int m, int k, int act_dtype, cudaStream_t stream) {
-  XQT_REQUIRE(m > 0 && k > 0 && k % 32 == 0);
-  XQT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)down & 15) == 0 && ((uintptr_t)out & 7) == 0);
+int lowrank_down_launch(const void* x, const void* down, float* out, void* image, int m, int k, int act_dtype,
+                        cudaStream_t stream) {
+  XQT_REQUIRE(m > 0 && k > 0 && k % 32 == 0 && (out != nullptr || image != nullptr));
+  XQT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)down & 15) == 0 && ((uintptr_t)out & 7) == 0 && ((uintptr_t)image & 127) == 0);
   const int grid = ceil_div(m, 16);
   if (act_dtype == XQT_B200_BF16)
-    lowrank_down_kernel<__nv_bfloat16><<<grid, kLrWarps * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)down, out, m, k);
+    lowrank_down_kernel<__nv_bfloat16><<<grid, kLrWarps * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)down, out, (unsigned char*)image, m, k);
   else
-    lowrank_down_kernel<__half><<<grid, kLrWarps * 32, 0, stream>>>((const __half*)x, (const __half*)down, out, m, k);
+    lowrank_down_kernel<__half><<<grid, kLrWarps * 32, 0, stream>>>((const __half*)x, (const __half*)down, out, (unsigned char*)image, m, k);
   return launch_status();
 }
 

@@ -22,6 +22,9 @@
 //   mode 5: the codes and scales of mode 4, each code written as the byte sign << 7 | magnitude.  Read as
 //           FP8 E4M3 that byte is the subnormal/first-binade value code * 2^-9 exactly (magnitudes 0..15
 //           are linear there), the operand form of the W4A4 GEMM's tcgen05 kind::f8f6f4 MMA.
+//   mode 6: mode 5 with the scales written tile-major, [ceil(M/128)][K/64][128] (the scale of row r and 64-K slot g at
+//           ((r / 128) * K/64 + g) * 128 + r % 128): the order in which the W4A4 GEMM's producer fetches the two scale
+//           rows of a 128-K stage with one 1 KiB copy.  Needs group 64 or 0.
 // Codes are written as one byte each in every mode (Blackwell has no int4 MMA).
 #include "common.cuh"
 
@@ -29,6 +32,10 @@ namespace xqt_b200 {
 
 constexpr int kRqThreads = 256;
 
+// flags of the int4 modes: bit 0 sign-magnitude bytes, bit 1 tile-major scales
+__device__ __forceinline__ size_t rq_scale_index(int row, int g, int groups, int flags) {
+  return (flags & 2) ? ((size_t)(row >> 7) * groups + g) * 128 + (row & 127) : (size_t)row * groups + g;
+}
 __device__ __forceinline__ int8_t rq_encode(float q, int signmag) {
   const int c = (int)q;
   return (int8_t)(signmag ? ((c < 0 ? 0x80 : 0) | (c < 0 ? -c : c)) : c);
@@ -38,7 +45,8 @@ template <typename T>
 __global__ void __launch_bounds__(kRqThreads)
 rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_scale, int8_t* __restrict__ codes,
                     float* __restrict__ scales, T* __restrict__ x_rot, int k, int rot_kind, int rot_block, int mode,
-                    int group, int signmag) {
+                    int group, int flags) {
+  const int signmag = flags & 1;
   extern __shared__ float v[];  // [k]
   __shared__ float s_red[kRqThreads / 32];
   __shared__ float s_scale;
@@ -111,7 +119,7 @@ rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_sc
     }
     __syncthreads();
     const float sc = s_scale;
-    for (int gi = tid; gi < k / 64; gi += kRqThreads) scales[(size_t)row * (k / 64) + gi] = sc;
+    for (int gi = tid; gi < k / 64; gi += kRqThreads) scales[rq_scale_index(row, gi, k / 64, flags)] = sc;
     for (int i = tid; i < k; i += kRqThreads) {
       const float q = fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), -8.f), 7.f);
       codes[(size_t)row * k + i] = rq_encode(q, signmag);
@@ -123,7 +131,7 @@ rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_sc
       float mx = 0.f;
       for (int e = 0; e < group; ++e) mx = fmaxf(mx, fabsf(v[gi * group + e]));
       const float sc = fmaxf(__fdiv_rn(mx, 7.0f), 1e-6f);
-      scales[(size_t)row * groups + gi] = sc;
+      scales[rq_scale_index(row, gi, groups, flags)] = sc;
       for (int e = 0; e < group; ++e) {
         const float q = fminf(fmaxf(rintf(__fdiv_rn(v[gi * group + e], sc)), -8.f), 7.f);
         codes[(size_t)row * k + gi * group + e] = rq_encode(q, signmag);
@@ -142,7 +150,8 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ column_scale, int8_t* __restrict__ codes,
                          float* __restrict__ scales, T* __restrict__ x_rot, int k, int rot_kind, int rot_block, int mode,
-                         int group, int signmag) {
+                         int group, int flags) {
+  const int signmag = flags & 1;
   __shared__ float s_red[32];
   __shared__ float s_scale;
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
@@ -284,13 +293,13 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
     }
     __syncthreads();
     sc = s_scale;
-    if (active && (tid & 3) == 0) scales[(size_t)row * (k / 64) + tid / 4] = sc;     // one 64-K slot per four threads
+    if (active && (tid & 3) == 0) scales[rq_scale_index(row, tid / 4, k / 64, flags)] = sc;     // one 64-K slot per four threads
     lo_clamp = -8.f; hi_clamp = 7.f;
   } else {
     // group of `group` elements = group/16 adjacent lanes (group is 16, 32, 64, ... <= 512)
     for (int off = 1; off < group / 16; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
     sc = fmaxf(__fdiv_rn(amax, 7.0f), 1e-6f);
-    if (active && (tid % (group / 16)) == 0) scales[(size_t)row * (k / group) + (tid * 16) / group] = sc;
+    if (active && (tid % (group / 16)) == 0) scales[rq_scale_index(row, (tid * 16) / group, k / group, flags)] = sc;
     lo_clamp = -8.f; hi_clamp = 7.f;
   }
   if (active) {
@@ -314,9 +323,11 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
 
 int rotate_quant_launch(const void* x, const float* column_scale, void* codes, float* scales, void* x_rot, int m, int k,
                         int rot_kind, int rot_block, int mode, int group, int act_dtype, cudaStream_t stream) {
-  XQT_REQUIRE(m > 0 && k > 0 && (mode == 8 || mode == 4 || mode == 5));
-  const int signmag = mode == 5 ? 1 : 0;      // mode 5: the int4 codes of mode 4, written as sign-magnitude bytes
-  if (mode == 5) mode = 4;
+  XQT_REQUIRE(m > 0 && k > 0 && (mode == 8 || mode == 4 || mode == 5 || mode == 6));
+  // modes 5, 6: the int4 codes of mode 4 written as sign-magnitude bytes; mode 6 also orders the scales tile-major
+  const int signmag = mode == 5 ? 1 : (mode == 6 ? 3 : 0);
+  if (mode == 6) XQT_REQUIRE(group == 0 || group == 64);
+  if (mode == 5 || mode == 6) mode = 4;
   XQT_REQUIRE(rot_kind >= 0 && rot_kind <= 2);
   if (rot_kind != 0) {
     XQT_REQUIRE(rot_block >= 1 && k % rot_block == 0 && column_scale != nullptr);

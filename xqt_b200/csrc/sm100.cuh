@@ -293,6 +293,22 @@ __device__ __forceinline__ unsigned long long f32x2_pack(float lo, float hi) {
 __device__ __forceinline__ void f32x2_unpack(unsigned long long v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
 }
+// packed fp32 arithmetic: one instruction for two lanes of a register pair (round to nearest, as the scalar forms)
+__device__ __forceinline__ unsigned long long f32x2_mul(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ unsigned long long f32x2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long f32x2_add(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 // One K block of four SS MMA steps (descriptors a0..a3 / b0..b3), its commit to `done_bar`, and --
 // issued first, consumed last -- one poll of `next_bar`: the 150-cycle round trip of the poll runs
 // while the MMAs are being issued.  Returns whether `next_bar` had completed `next_parity`.

@@ -55,11 +55,12 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_rotate_quantize": (_I, [_P] * 5 + [_I] * 7 + [_P]),
     "xqt_b200_quantize_per_tensor": (_I, [_P] * 4 + [_I] * 3 + [ctypes.c_float, _P]),
     "xqt_b200_w8a8_gemm": (_I, [_P] * 6 + [_I] * 4 + [_P, _Z, _P]),
-    "xqt_b200_lowrank_down": (_I, [_P] * 3 + [_I] * 3 + [_P]),
+    "xqt_b200_lowrank_down": (_I, [_P] * 4 + [_I] * 3 + [_P]),
     "xqt_b200_w4a4_aux_tile_bytes": (_Z, [_I]),
     "xqt_b200_w4a4_supported": (_I, [_I] * 3),
     "xqt_b200_w4a4_workspace_bytes": (_Z, [_I] * 3),
-    "xqt_b200_w4a4_gemm": (_I, [_P] * 7 + [_I] * 4 + [_P, _Z, _P]),
+    "xqt_b200_w4a4_gemm": (_I, [_P] * 8 + [_I] * 5 + [_P, _Z, _P]),
+    "xqt_b200_w4a4_expand_weight": (_I, [_P, _P, _I, _I, _P]),
     "xqt_b200_w4a4_dense_workspace_bytes": (_Z, [_I] * 3),
     "xqt_b200_w4a4_dense_preferred": (_I, [_I] * 3),
     "xqt_b200_w4a4_dense": (_I, [_P] * 8 + [_I] * 4 + [_P, _Z, _P]),

@@ -22,12 +22,16 @@ def _column_scale(rotation: Rotation, device: torch.device) -> torch.Tensor:
 
 
 def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, group_size: int = 64,
-                    return_rotated: bool = False, out: tuple | None = None, sign_magnitude: bool = False):
+                    return_rotated: bool = False, out: tuple | None = None, sign_magnitude: bool = False,
+                    tiled_scales: bool = False):
     """-> (codes int8 ``[M,K]``, scales fp32 ``[M]`` (bits=8) or ``[M, K/group]`` (bits=4)[, rotated x]).
 
     ``sign_magnitude`` (bits=4 only) writes each int4 code as the byte ``sign << 7 | magnitude`` -- read as
     FP8 E4M3 that is ``code * 2**-9`` exactly, the operand form of the W4A4 GEMM; :func:`decode_sign_magnitude`
     turns such bytes back into two's-complement codes.
+
+    ``tiled_scales`` (with ``sign_magnitude``, group 64 or 0) orders the scales tile-major for the W4A4 GEMM: the
+    returned buffer has ``ceil(M/128)*128`` rows of storage and holds ``[ceil(M/128)][K/64][128]``.
 
     ``out = (codes, scales[, rotated])`` supplies preallocated buffers whose leading ``M`` rows are
     written (a workspace sized for at least M rows): the call then allocates nothing."""
@@ -38,6 +42,8 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
         raise XQTBackendError("rotate_quantize supports 8-bit per-token or 4-bit per-group codes")
     if sign_magnitude and bits != 4:
         raise XQTBackendError("sign-magnitude bytes are the form of 4-bit codes only")
+    if tiled_scales and not (sign_magnitude and int(group_size) in (0, 64)):
+        raise XQTBackendError("tile-major scales go with sign-magnitude codes of group 64 (or per-token) only")
     x = x.contiguous()
     m, k = int(x.shape[0]), int(x.shape[1])
     device = x.device
@@ -47,14 +53,15 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
     if bits == 4 and (k % 64 if per_token4 else k % group_size):
         raise XQTBackendError("K must be a multiple of the activation group size")
     scale_groups = k // 64 if per_token4 else (k // group_size if bits == 4 else 0)
+    scale_rows = -(-m // 128) * 128 if tiled_scales else m
     if out is None:
         codes = torch.empty((m, k), device=device, dtype=torch.int8)
-        scales = torch.empty((m,) if bits == 8 else (m, scale_groups), device=device, dtype=torch.float32)
+        scales = torch.empty((m,) if bits == 8 else (scale_rows, scale_groups), device=device, dtype=torch.float32)
         rotated = torch.empty_like(x) if return_rotated else None
     else:
-        codes, scales = out[0][:m], out[1][:m]
+        codes, scales = out[0][:m], out[1][:scale_rows]
         rotated = out[2][:m] if return_rotated else None
-        want_scales = (m,) if bits == 8 else (m, scale_groups)
+        want_scales = (m,) if bits == 8 else (scale_rows, scale_groups)
         if codes.dtype != torch.int8 or tuple(codes.shape) != (m, k) or not codes.is_contiguous() \
                 or scales.dtype != torch.float32 or tuple(scales.shape) != want_scales or not scales.is_contiguous() \
                 or (rotated is not None and (rotated.dtype != x.dtype or tuple(rotated.shape) != (m, k) or not rotated.is_contiguous())):
@@ -65,7 +72,7 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
             code = native.library().xqt_b200_rotate_quantize(
                 x.data_ptr(), native.ptr(cs), codes.data_ptr(), scales.data_ptr(), native.ptr(rotated), m, k,
                 _KIND[None if rotation is None else rotation.kind], 0 if rotation is None else rotation.block,
-                5 if sign_magnitude else bits, int(group_size), native.DTYPE_CODE[x.dtype], native.stream_handle(device))
+                (6 if tiled_scales else 5) if sign_magnitude else bits, int(group_size), native.DTYPE_CODE[x.dtype], native.stream_handle(device))
         native.check(code, "xqt_b200_rotate_quantize")
     return (codes, scales, rotated) if return_rotated else (codes, scales)
 

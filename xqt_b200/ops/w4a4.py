@@ -21,7 +21,7 @@ which is why it is not the default.
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 
 import torch
 
@@ -50,6 +50,7 @@ class PackedSVDQW4A4Linear:
     dtype: torch.dtype
     rotation: Rotation | None = None
     act_granularity: str = "group"     # "group": one scale per (token, 64 K); "token": one per token (ConvRot artifact form)
+    weight_bytes: torch.Tensor | None = None   # uint8 [N, K]: operand cache of `with_operand_cache` (None: widened per call)
 
     @property
     def padded_rank(self) -> int:
@@ -169,7 +170,7 @@ def allocate_w4a4_workspace(rows: int, packed: PackedSVDQW4A4Linear, *, with_lor
         lora = torch.zeros((-(-rows // TILE) * TILE, RANK_PAD), dtype=torch.float32, device=device)
     return W4A4Workspace(
         quantized_activation=torch.empty((rows, k), dtype=torch.int8, device=device),
-        activation_scales=torch.empty((rows, k // GROUP), dtype=torch.float32, device=device),
+        activation_scales=torch.empty((-(-rows // TILE) * TILE, k // GROUP), dtype=torch.float32, device=device),   # room for the tile-major order
         lora_activation=lora, rotated_activation=rotated)
 
 
@@ -229,13 +230,22 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
     dense = form == "dense"
     if form not in ("auto", "dense", "integer"):
         raise XQTBackendError("form must be auto, dense or integer")
-    # the integer form's GEMM takes the codes as sign-magnitude bytes (FP8 E4M3 operands), the dense form as int8
+    # The integer form's GEMM takes the codes as sign-magnitude bytes (FP8 E4M3 operands), the dense form as int8.
+    # direct: the prologue kernels write the GEMM's own operand forms (tile-major scales, low-rank operand images), so
+    # the GEMM call launches no preparation kernel; callers that want the parts back, or scale the low-rank
+    # activations, take the row-major forms.
+    direct = not dense and not return_parts and lora_scale == 1.0
     codes, scales, rotated = rotate_quantize(x, packed.rotation, bits=4, group_size=GROUP if packed.act_granularity == "group" else 0,
-                                             return_rotated=True, out=buffers, sign_magnitude=not dense)
+                                             return_rotated=True, out=buffers, sign_magnitude=not dense, tiled_scales=direct)
     if workspace is not None and workspace.lora_activation is not None:
         la = workspace.lora_activation          # rows past M stay zero: the kernels only write rows < M
+    elif direct and packed.rank:
+        la = torch.empty((-(-m // TILE) * TILE, RANK_PAD), device=device, dtype=torch.float32)   # holds the operand images
     else:
         la = torch.zeros((-(-m // TILE) * TILE, RANK_PAD), device=device, dtype=torch.float32)
+    # flags 1 | 2: scales tile-major, la holds operand images (without a low-rank branch la is all zero bits, which is
+    # a zero image as well as a zero matrix)
+    flags = 3 if direct else 0
     stream = native.stream_handle(device)
     # auto keeps the integer form: it is the one that meets the 1e-3 parity bar at every K (the dense
     # form is about 3.5x faster at M >= 256 and within 1.2e-3)
@@ -248,7 +258,8 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
                     rotated.data_ptr(), packed.down.data_ptr(), la.data_ptr(), m, k, native.DTYPE_CODE[packed.dtype],
                     scratch.data_ptr(), scratch.numel(), stream), "xqt_b200_lowrank_down_tc")
             else:
-                native.check(lib.xqt_b200_lowrank_down(rotated.data_ptr(), packed.down.data_ptr(), la.data_ptr(), m, k,
+                native.check(lib.xqt_b200_lowrank_down(rotated.data_ptr(), packed.down.data_ptr(), 0 if direct else la.data_ptr(),
+                                                       la.data_ptr() if direct else 0, m, k,
                                                        native.DTYPE_CODE[packed.dtype], stream), "xqt_b200_lowrank_down")
             if lora_scale != 1.0:
                 la[:m].mul_(float(lora_scale))
@@ -259,8 +270,8 @@ def svdq_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, work
                 native.DTYPE_CODE[packed.dtype], scratch.data_ptr(), scratch.numel(), stream), "xqt_b200_w4a4_dense")
         else:
             native.check(lib.xqt_b200_w4a4_gemm(
-                codes.data_ptr(), scales.data_ptr(), packed.qweight.data_ptr(), packed.aux.data_ptr(), la.data_ptr(),
-                native.ptr(packed.bias), out.data_ptr(), m, n, k, native.DTYPE_CODE[packed.dtype], scratch.data_ptr(),
+                codes.data_ptr(), scales.data_ptr(), packed.qweight.data_ptr(), native.ptr(packed.weight_bytes), packed.aux.data_ptr(), la.data_ptr(),
+                native.ptr(packed.bias), out.data_ptr(), m, n, k, native.DTYPE_CODE[packed.dtype], flags, scratch.data_ptr(),
                 scratch.numel(), stream), "xqt_b200_w4a4_gemm")
     out = out.reshape(*inputs.shape[:-1], n)
     if return_parts:
@@ -282,12 +293,30 @@ def convrot_w4a4_linear(inputs: torch.Tensor, packed: PackedSVDQW4A4Linear, *, r
     return svdq_w4a4_linear(inputs, packed, workspace=workspace)
 
 
+def with_operand_cache(packed: PackedSVDQW4A4Linear) -> PackedSVDQW4A4Linear:
+    """The layer with its weights also held in the GEMM's operand form (one sign-magnitude byte per weight, ``[N, K]``
+    uint8 beside the packed half byte): the integer form then skips its per-call widening pass.  A memory-for-time
+    choice of the caller; the packed storage stays the layer's definition."""
+
+    if packed.weight_bytes is not None:
+        return packed
+    n, k, device = packed.output_features, packed.input_features, packed.qweight.device
+    widened = torch.empty((n, k), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        native.check(native.library().xqt_b200_w4a4_expand_weight(packed.qweight.data_ptr(), widened.data_ptr(), n, k,
+                                                                   native.stream_handle(device)), "xqt_b200_w4a4_expand_weight")
+    return replace(packed, weight_bytes=widened)
+
+
 def bind_svdq_w4a4_linear(packed: PackedSVDQW4A4Linear, workspace: W4A4Workspace | None = None, *, rows: int,
-                          lora_scale: float = 1.0):
+                          lora_scale: float = 1.0, operand_cache: bool = False):
     """Validated state for the steady-state path (cf. svdq_w4a4_sm89.py:1264-1318): the workspace owns the
-    codes, scales, rotated activation and low-rank activation, so a call allocates only its output."""
+    codes, scales, rotated activation and low-rank activation, so a call allocates only its output.
+    ``operand_cache``: hold the weights in operand form as well (see ``with_operand_cache``)."""
 
     rows = int(rows)
+    if operand_cache:
+        packed = with_operand_cache(packed)
     if workspace is None:
         workspace = allocate_w4a4_workspace(rows, packed, with_lora_rank=packed.rank)
     if workspace.padded_rows < rows or (packed.rank and workspace.lora_activation is None):
@@ -305,4 +334,4 @@ def bind_svdq_w4a4_linear(packed: PackedSVDQW4A4Linear, workspace: W4A4Workspace
 
 __all__ = ["PackedSVDQW4A4Linear", "W4A4Workspace", "allocate_w4a4_workspace", "bind_svdq_w4a4_linear", "convrot_w4a4_linear",
            "native_convrot_w4a4_shape_supported", "native_w4a4_available", "native_w4a4_shape_supported", "native_w4a4_version",
-           "pack_svdq_w4a4_linear", "svdq_w4a4_linear"]
+           "pack_svdq_w4a4_linear", "svdq_w4a4_linear", "with_operand_cache"]
