@@ -166,6 +166,12 @@ int xqt_b200_w4a16_decode_tc(const void* activation, const void* row_weights, co
  *                 unfused `residual + projection(x)` that AWQW4A16Linear.bind_residual keeps
  *                 (xqt/runtime/modules/awq_w4a16_linear.py:665-737); 0: one rounding after the add
  *                 (the GEMM contract, xqt/kernels/ops/gemm/reference.py:362-390)
+ *                 bit 1: fused SwiGLU of a horizontally fused gate/up layer (the gate/up fusion with SiLU gating of
+ *                 xqt/kernels/ops/_impl/cute/convrot_w8a8_sm89.py:664-917 at decode sizes): the layer's rows were laid
+ *                 out so that every 128-row tile holds 64 gate rows followed by their 64 up rows; output is
+ *                 [M, N/2] act_dtype = silu(gate) * up, each projection rounded to act_dtype first (the bits of the
+ *                 unfused linear -> SwiGLU).  N a multiple of 128, no residual, no fp32 output; bias, if given, is in
+ *                 the layer's (interleaved) row order.
  *   status        NULL, or a device word the kernel sets to 64 when the bounded wait for its
  *                 activation copy ran out (the result is then undefined; nothing hangs)
  * Needs no workspace: the K pieces of a tile are the CTAs of one thread-block cluster and reduce

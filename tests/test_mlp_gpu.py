@@ -184,3 +184,23 @@ def test_mlp_block_as_cuda_graph_matches_eager_calls():
         got = replay().clone()
         assert torch.equal(got, block(x))
     assert native.workspace_status(dev) == 0
+
+
+@pytest.mark.parametrize("m", [1, 16, 40])
+def test_fused_swiglu_decode_epilogue_has_the_bits_of_the_unfused_form(m, monkeypatch):
+    """gate/up + SwiGLU as one decode launch (interleaved tiles, gating in the kernel's epilogue) against the same
+    block built with the fusion off: identical outputs."""
+
+    from xqt_b200 import native
+    from xqt_b200.ops.mlp import W4A16SwiGLUMLP
+    dev = torch.device("cuda", 0)
+    gate, up, down = _weights(1024, 2048 + 128, 30)         # 34 tiles of 64 + 64 rows
+    x = torch.randn((m, 1024), generator=seeded(m + 7)).to(torch.bfloat16).to(dev)
+    fused = W4A16SwiGLUMLP(gate, up, down, device=dev)
+    assert fused.gate_up.glu
+    monkeypatch.setenv("XQT_B200_FUSED_SWIGLU", "0")
+    plain = W4A16SwiGLUMLP(gate, up, down, device=dev)
+    assert not plain.gate_up.glu
+    assert torch.equal(fused(x), plain(x))
+    assert torch.equal(fused.gate_up.gated(x), plain._swiglu(plain.gate_up(x)))
+    assert native.workspace_status(dev) == 0

@@ -212,7 +212,7 @@ int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights
                                 const void* lane_zeros, const float* bias, const void* residual, void* output, int m, int n, int k,
                                 int group_size, int nibble_signed, int act_dtype, int param_dtype, int out_dtype,
                                 int epilogue_flags, unsigned int* status, xqt_b200_stream_t stream) {
-  XQT_REQUIRE(m >= 0 && n > 0 && k > 0 && (epilogue_flags & ~1) == 0);
+  XQT_REQUIRE(m >= 0 && n > 0 && k > 0 && (epilogue_flags & ~3) == 0);
   XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
   XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
   if (m == 0) return 0;

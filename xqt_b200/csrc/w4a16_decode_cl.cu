@@ -8,7 +8,9 @@
 // global memory into registers with 16-byte loads (512 contiguous bytes per warp and request), three
 // 64-K half blocks ahead of the arithmetic (a four-slot register ring), and asks for the rest of its
 // piece into L2 with bulk prefetches on entry; nothing in the main loop waits on a barrier.
-// Measured alternatives that lost: staging the weights through per-warp shared-memory rings filled by
+// Measured alternatives that lost: staging the activations with 16-byte loads by all threads and adding the group
+// sums on the way, in place of the bulk copies and the tensor-core pass (slower at every M: each batch of loads is an
+// L2 round trip, 0.2-0.5 us more at M = 1 and 2-3 us more at M = 16); staging the weights through per-warp shared-memory rings filled by
 // bulk copies (64 registers, four CTAs per SM: 11.5 us against 9.4 us on the 31 MB layers), an
 // 80-register build for three CTAs per SM (12.9 us: future kernels' CTAs crowd the SMs), and per-owner
 // mbarrier arrivals in place of the closing cluster barrier (11.2 us).
@@ -72,6 +74,7 @@ struct DecodeClParams {
   unsigned int* status; // may be null
   int m, n, k, out_f32;
   int round_first;      // 1: round the projection to T before the residual is added (unfused `residual + proj` numerics)
+  int glu;              // 1: a tile is 64 gate channels followed by their 64 up channels; out[M, N/2] = silu(gate) * up
   int kblocks, pieces, kw;
   int per, rem;         // kblocks = pieces * per + rem: piece i starts at i * per + min(i, rem)
   int xrow_bytes;       // shared-memory row stride of x
@@ -455,7 +458,29 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
     __syncthreads();
   }
   // this CTA finishes tokens rank, rank + S, ...
-  {
+  if (p.glu) {
+    // SwiGLU of a horizontally fused gate/up layer whose rows were interleaved per tile: channel ch < 64 of the tile is
+    // gate row 64 tile + ch, channel 64 + ch its up row.  Both sums are rounded to T first, as the unfused form stores
+    // them, and gated with the arithmetic of swiglu_kernel: the result has the same bits as linear -> swiglu.
+    const int own = p.m > (int)rank ? (p.m - (int)rank + (int)S - 1) / (int)S : 0;
+    const int half_n = p.n >> 1;
+    for (int idx = tid; idx < own * (kTileRows / 2); idx += nthreads) {
+      const int li = idx >> 6, ch = idx & 63;
+      const int token = li * (int)S + (int)rank;
+      float g = 0.f, u = 0.f;
+      for (uint32_t src = 0; src < S; ++src) {
+        const uint32_t a = redc_s + ((src * p.own_max + li) * kRedStride + ch) * 4;
+        g += cl_lds32f(a);
+        u += cl_lds32f(a + 64 * 4);
+      }
+      if (p.bias != nullptr) {
+        g += p.bias[tile * kTileRows + ch];
+        u += p.bias[tile * kTileRows + 64 + ch];
+      }
+      const float gx = to_float<T>(from_float<T>(g)), ux = to_float<T>(from_float<T>(u));
+      reinterpret_cast<T*>(p.out)[(size_t)token * half_n + tile * (kTileRows / 2) + ch] = from_float<T>(gx / (1.0f + expf(-gx)) * ux);
+    }
+  } else {
     const int own = p.m > (int)rank ? (p.m - (int)rank + (int)S - 1) / (int)S : 0;
     for (int idx = tid; idx < own * kTileRows; idx += nthreads) {
       const int li = idx >> 7, ch = idx & 127;
@@ -621,6 +646,8 @@ int w4a16_decode_cl_launch(const void* x, const void* wt, const void* scl, const
   p.m = m; p.n = n; p.k = k; p.out_f32 = out_f32;
   p.round_first = (epilogue_flags & 1) != 0;
   XQT_REQUIRE(!(p.round_first && out_f32));
+  p.glu = (epilogue_flags & 2) != 0;
+  XQT_REQUIRE(!p.glu || (n % kTileRows == 0 && !out_f32 && residual == nullptr));
   p.kblocks = kblocks; p.kw = plan.kw; p.pieces = plan.kw * plan.s;
   XQT_REQUIRE(p.pieces >= 1 && p.pieces <= kblocks);
   const int slice_max = (kblocks * plan.kw + p.pieces - 1) / p.pieces + 1;   // upper bound of any CTA's slice

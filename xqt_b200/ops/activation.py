@@ -13,12 +13,15 @@ _scale_cache: dict[tuple, torch.Tensor] = {}
 
 
 def _column_scale(rotation: Rotation, device: torch.device) -> torch.Tensor:
-    key = (rotation.kind, rotation.block, None if rotation.signs is None else tuple(rotation.signs.tolist()), str(device))
+    """The rotation's column factors on ``device``, cached per Rotation object (the entry keeps the object alive, so
+    its id cannot be reused; building a key from the sign vector on every call cost more host time than the launch)."""
+
+    key = (id(rotation), device.type, device.index)
     cached = _scale_cache.get(key)
-    if cached is None:
-        cached = rotation.column_scale.to(device).contiguous()
+    if cached is None or cached[0] is not rotation:
+        cached = (rotation, rotation.column_scale.to(device).contiguous())
         _scale_cache[key] = cached
-    return cached
+    return cached[1]
 
 
 def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, group_size: int = 64,

@@ -22,7 +22,7 @@ from .. import native
 from ..contracts import PackedWeight, PackedWeightMetadata
 from ..errors import XQTBackendError
 from ..parallel import shard_packed_weight
-from .w4a16 import bind_w4a16_decode, prepare_decode, w4a16_linear
+from .w4a16 import bind_w4a16_decode, glu_row_order, prepare_decode, w4a16_linear
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -64,19 +64,49 @@ CHUNKED_DECODE_MAX_ROWS = 48
 class _Linear:
     """One W4A16 layer on a device with both execution forms: decode layout and canonical bytes."""
 
-    def __init__(self, weight: PackedWeight, device: torch.device, dtype: torch.dtype) -> None:
+    def __init__(self, weight: PackedWeight, device: torch.device, dtype: torch.dtype, glu: bool = False) -> None:
         meta = weight.metadata
         self.n, self.k = meta.logical_shape
         self.group, self.signed, self.dtype = int(meta.group_size), bool(meta.nibble_signed), dtype
         self.qweight = weight.qweight.to(device).contiguous()
         self.scales = weight.scales.to(device).contiguous()
         self.zeros = None if weight.zero_points is None else weight.zero_points.to(device).contiguous()
-        self.tiled = prepare_decode(self.qweight, self.scales, self.zeros, group_size=self.group, nibble_signed=self.signed)
         self._bound: dict[tuple[int, torch.dtype], object] = {}
+        self._gated: dict[int, object] = {}
+        # glu: this is a fused [gate; up] layer.  Where the decode layout is the lanes one its tiles are built from the
+        # rows in glu_row_order, and `gated` runs linear + SwiGLU as one decode launch; `tiled` then serves only that.
+        self.glu, self.tiled = False, None
+        if glu and self.n % 128 == 0:
+            order = glu_row_order(self.n // 2).to(device)
+            tiled = prepare_decode(self.qweight[order], self.scales[order], None if self.zeros is None else self.zeros[order],
+                                   group_size=self.group, nibble_signed=self.signed)
+            if tiled.layout == "lanes":
+                self.glu, self.tiled = True, tiled
+        if self.tiled is None:
+            self.tiled = prepare_decode(self.qweight, self.scales, self.zeros, group_size=self.group, nibble_signed=self.signed)
+
+    def gated(self, x: torch.Tensor) -> torch.Tensor | None:
+        """``silu(gate) * up`` of a fused gate/up layer in one decode launch per 16 rows, or None where that form does
+        not apply (not a glu layer, too many rows)."""
+
+        m = int(x.shape[0])
+        if not self.glu or m > CHUNKED_DECODE_MAX_ROWS:
+            return None
+        out = torch.empty((m, self.n // 2), device=x.device, dtype=self.dtype)
+        for r0 in range(0, m, 16):
+            rows = min(16, m - r0)
+            run = self._gated.get(rows)
+            if run is None:
+                run = bind_w4a16_decode(self.tiled, rows=rows, dtype=self.dtype, glu=True)
+                self._gated[rows] = run
+            run(x if rows == m else x[r0:r0 + rows], out if rows == m else out[r0:r0 + rows])
+        return out
 
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         m = int(x.shape[0])
         odt = self.dtype if out_dtype is None else out_dtype
+        if self.glu and m <= CHUNKED_DECODE_MAX_ROWS:
+            raise XQTBackendError("a glu layer's decode tiles are interleaved: call gated()")
         if m <= 16 and (odt == self.dtype or self.tiled.layout in ("rows128", "lanes")):
             run = self._bound.get((m, odt))
             if run is None:
@@ -144,7 +174,7 @@ class W4A16SwiGLUMLP:
             self.down = _InjectedLinear(down, local_linear)
             peer_reduce = False
         else:
-            self.gate_up = _Linear(_concat_rows(gate, up), device, dtype)
+            self.gate_up = _Linear(_concat_rows(gate, up), device, dtype, glu=swiglu_fn is None and os.environ.get("XQT_B200_FUSED_SWIGLU", "1") not in {"0", ""})
             self.down = _Linear(down, device, dtype)
         self.hidden, self.inter_local = self.down.n, self.down.k
         # decode sizes (M <= 16): the partial sums of down are added by our own kernel over NVLink peer
@@ -158,7 +188,9 @@ class W4A16SwiGLUMLP:
             self._peer = PeerAllReduce(device, 16 * self.hidden, group)
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        h = self._swiglu(self.gate_up(x))
+        h = self.gate_up.gated(x) if isinstance(self.gate_up, _Linear) else None     # decode sizes: one launch
+        if h is None:
+            h = self._swiglu(self.gate_up(x))
         if self.world == 1:
             return self.down(h)
         m = int(h.shape[0])
@@ -239,7 +271,8 @@ class W4A16SwiGLUMLP:
             "kernels": {"m<=16": {"lanes": "w4a16_decode_cl_kernel", "rows128": "w4a16_decode_tc_kernel"}.get(
                             None if self.gate_up.tiled is None else self.gate_up.tiled.layout, "w4a16_decode_kernel"),
                         "17<=m<=128": "gemm_w4a16_fused_kernel (where it fills the SMs) else dequant_w4_f16_kernel + gemm_f16_kernel",
-                        "m>128": "dequant_w4_f16_kernel + gemm_f16_kernel", "gating": "swiglu_kernel"},
+                        "m>128": "dequant_w4_f16_kernel + gemm_f16_kernel",
+                        "gating": "w4a16_decode_cl_kernel epilogue (m <= 48) / swiglu_kernel" if getattr(self.gate_up, "glu", False) else "swiglu_kernel"},
         }
 
 

@@ -198,12 +198,27 @@ def decode_supported(m: int, n: int, k: int, group_size: int) -> bool:
     return bool(native.library().xqt_b200_w4a16_decode_supported(int(m), int(n), int(k), int(group_size)))
 
 
+def glu_row_order(inter: int) -> torch.Tensor:
+    """Row permutation of a horizontally fused ``[gate; up]`` weight (``2*inter`` rows) that puts, into every 128-row
+    tile, 64 gate rows followed by their 64 up rows -- the order the decode kernel's fused SwiGLU epilogue expects."""
+
+    if inter % 64:
+        raise XQTBackendError("fused SwiGLU decode needs the intermediate size to be a multiple of 64")
+    base = torch.arange(inter).reshape(inter // 64, 1, 64)
+    return torch.cat((base, base + inter), dim=1).reshape(-1)
+
+
 def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None = None,
-                      out_dtype: torch.dtype | None = None):
+                      out_dtype: torch.dtype | None = None, glu: bool = False):
     """Hot-callable for the decode kernel on a :class:`xqt_b200.prepack.TiledW4` layer:
     ``run(x, out=None, residual=None) -> Tensor`` for a fixed row count (1..16).  Static tensors are
     validated here, once; each call checks the activation and makes one C-ABI call
-    (cf. ``bind_awq_w4a16_decode``, xqt/kernels/ops/_impl/cuda/awq_w4a16_sm89.py:217-302)."""
+    (cf. ``bind_awq_w4a16_decode``, xqt/kernels/ops/_impl/cuda/awq_w4a16_sm89.py:217-302).
+
+    ``glu`` (``lanes`` layout): the layer is a fused gate/up projection whose rows were laid out with
+    :func:`glu_row_order`; the kernel's epilogue gates them, ``run`` returns ``silu(gate) * up`` as ``[rows, N/2]``
+    with the bits of the unfused linear -> SwiGLU (the horizontally fused gate/up + SwiGLU of
+    xqt/kernels/ops/_impl/cute/convrot_w8a8_sm89.py:664-917, at decode sizes)."""
 
     device = tiled.weights.device
     if device.type != "cuda":
@@ -217,7 +232,9 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
     lib = native.library()
     use_tc = tiled.layout == "rows128"
     if tiled.layout == "lanes":
-        return _bind_decode_lanes(tiled, rows=rows, dtype=dtype, bias=bias, odt=odt)
+        return _bind_decode_lanes(tiled, rows=rows, dtype=dtype, bias=bias, odt=odt, glu=glu)
+    if glu:
+        raise XQTBackendError("the fused SwiGLU epilogue is served by the lanes decode layout only")
     if use_tc:
         if not tiled.integer_zero_points:
             raise XQTBackendError("the tcgen05 decode kernel needs integer zero points in [0, 119]")
@@ -269,11 +286,14 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
     return run
 
 
-def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None, odt: torch.dtype):
+def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None, odt: torch.dtype, glu: bool = False):
     """``bind_w4a16_decode`` for the ``lanes`` layout (cluster split-K kernel: no workspace)."""
 
     device = tiled.weights.device
     n, k = tiled.n, tiled.k
+    if glu and (n % 128 or odt != dtype):
+        raise XQTBackendError("fused SwiGLU decode: N must be a multiple of 128 and the output in the activation dtype")
+    n_out = n // 2 if glu else n
     lib = native.library()
     if not lib.xqt_b200_w4a16_decode_lanes_supported(rows, n, k, tiled.group_size):
         raise XQTBackendError(f"B200 W4A16 decode does not cover M={rows}, N={n}, K={k}, group={tiled.group_size}")
@@ -286,7 +306,7 @@ def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tens
     head = (tiled.weights.data_ptr(), tiled.params[0].data_ptr(),
             tiled.params[1].data_ptr() if tiled.has_zero_point else 0, native.ptr(bias32))
     tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), native.DTYPE_CODE[dtype],
-            native.DTYPE_CODE[tiled.params.dtype], native.DTYPE_CODE[odt], 0)
+            native.DTYPE_CODE[tiled.params.dtype], native.DTYPE_CODE[odt], 2 if glu else 0)
     index = device.index if device.index is not None else torch.cuda.current_device()
     status = native.status_word(device)
     status_ptr = status.data_ptr()
@@ -299,10 +319,12 @@ def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tens
         if torch.cuda.current_device() != index:
             raise XQTBackendError("bound B200 W4A16 decode: make the weight's device current before calling")
         if out is None:
-            out = torch.empty((rows, n), device=device, dtype=odt)
-        if residual is not None and (residual.dtype != dtype or tuple(residual.shape) != (rows, n)
+            out = torch.empty((rows, n_out), device=device, dtype=odt)
+        elif tuple(out.shape) != (rows, n_out) or out.dtype != odt or not out.is_contiguous():
+            raise XQTBackendError("bound B200 W4A16 decode: out must be contiguous [M, N] (N/2 with glu) in the output dtype")
+        if residual is not None and (glu or residual.dtype != dtype or tuple(residual.shape) != (rows, n)
                                      or not residual.is_contiguous() or odt != dtype):
-            raise XQTBackendError("bound B200 W4A16 decode: residual must be contiguous [M,N] in the activation dtype")
+            raise XQTBackendError("bound B200 W4A16 decode: residual must be contiguous [M,N] in the activation dtype (none with glu)")
         code = fn(x.data_ptr(), *head, native.ptr(residual), out.data_ptr(), *tail, status_ptr,
                   torch.cuda.current_stream(device).cuda_stream)
         if code != 0:
@@ -371,6 +393,6 @@ def _custom_op_fake(x, qweight, scales, zero_points, bias, residual, group_size,
 
 _register()
 
-__all__ = ["bind_w4a16_decode", "bind_w4a16_linear", "decode_supported", "prepare_decode", "select_variant",
+__all__ = ["bind_w4a16_decode", "bind_w4a16_linear", "decode_supported", "glu_row_order", "prepare_decode", "select_variant",
            "w4a16_decode_tiled",
            "w4a16_linear"]

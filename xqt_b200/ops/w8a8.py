@@ -292,16 +292,39 @@ def bind_convrot_w8a8_linear(packed: PackedConvRotW8A8Linear, workspace: ConvRot
         raise ValueError("workspace extent does not match rows / packed weights")
     rot = rotation if rotation is not None else (None if int(rot_size) == 1 else regular_rotation(int(rot_size)))
     device, k, n, dtype = packed.qweight.device, packed.input_features, packed.output_features, packed.dtype
-    buffers = (workspace.quantized_activation, workspace.activation_scales)
+    if k % (1 if rot is None else rot.block):
+        raise XQTBackendError("the rotated dimension must be a multiple of the rotation block")
+    # every pointer and code of the two library calls is resolved here; a call checks its input, allocates its output
+    # and makes the two calls (the general entry's per-call validation costs about as much host time as the kernels run)
+    from .activation import _KIND, _column_scale
+
+    lib = native.library()
+    codes, scales = workspace.quantized_activation[:rows], workspace.activation_scales[:rows]
+    column_scale = None if rot is None else _column_scale(rot, device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    scratch = native.workspace(device, 256, "gemm")
+    dcode = native.DTYPE_CODE[dtype]
+    prologue = (native.ptr(column_scale), codes.data_ptr(), scales.data_ptr(), 0, rows, k, _KIND[None if rot is None else rot.kind],
+                0 if rot is None else rot.block, 8, 0, dcode)
+    gemm_head = (codes.data_ptr(), packed.qweight.data_ptr(), scales.data_ptr(), packed.weight_scales.data_ptr(), native.ptr(packed.bias))
+    gemm_tail = (rows, n, k, dcode, scratch.data_ptr(), scratch.numel())
 
     def run(inputs: torch.Tensor) -> torch.Tensor:
         if inputs.dtype != dtype or inputs.device != device or inputs.shape[-1] != k or inputs.numel() != rows * k \
                 or not inputs.is_contiguous():
             raise XQTBackendError("bound ConvRot W8A8 call: input shape, dtype, device or layout mismatch")
-        codes, scales = rotate_quantize(inputs.view(rows, k), rot, bits=8, out=buffers)
-        return w8a8_gemm(codes, scales, packed).view(*inputs.shape[:-1], n)
+        if torch.cuda.current_device() != index:
+            raise XQTBackendError("bound ConvRot W8A8 call: make the weight's device current before calling")
+        out = torch.empty((*inputs.shape[:-1], n), device=device, dtype=dtype)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        code = lib.xqt_b200_rotate_quantize(inputs.data_ptr(), *prologue, stream)
+        if code == 0:
+            code = lib.xqt_b200_w8a8_gemm(*gemm_head, out.data_ptr(), *gemm_tail, stream)
+        if code != 0:
+            native.check(code, "bound ConvRot W8A8 (xqt_b200_rotate_quantize / xqt_b200_w8a8_gemm)")
+        return out
 
-    run.keep = (packed, workspace, rot)
+    run.keep = (packed, workspace, rot, column_scale, scratch)
     return run
 
 
