@@ -238,6 +238,8 @@ int xqt_b200_w4a16_decode_static_status(unsigned int* host_status, xqt_b200_stre
  *                    convrot_4bit.py:669-679), replicated into scales [M, K/64]
  *                 5: the scales and codes of 4, every code written as the byte sign << 7 | magnitude (read as
  *                    FP8 E4M3 that is code * 2^-9 exactly): the operand form xqt_b200_w4a4_gemm consumes
+ *                 9: as 8 with the scale rounded to act_dtype, scale = act_dtype(amax/127), 0 and all-zero codes for an
+ *                    all-zero token (the activation side of the SVDQuant W8A8 linear, gemm_w8a8.cuh:236-262)
  *                 6: as 5 (group_size 64 or 0) with the scales tile-major, [ceil(M/128)][K/64][128] floats (row r,
  *                    slot g at ((r/128)*K/64 + g)*128 + r%128): what xqt_b200_w4a4_gemm takes with flag 1
  *   codes         one byte per element [M, K] in every mode (int8 for 8 and 4);  rotated: [M, K] act_dtype or
@@ -264,6 +266,21 @@ int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const fl
                        const float* weight_scale, const float* bias, void* output, int m, int n,
                        int k, int out_dtype, void* workspace, size_t workspace_bytes,
                        xqt_b200_stream_t stream);
+
+/* SVDQuant W8A8 (int8 x int8 GEMM with a low-rank branch; replaces quantize_act_lora / gemm_lora of
+ * xqt/kernels/jit/csrc/quantization/svdq_w8a8_sm89_kernel.cu, called from _impl/cute/svdq_w8a8_sm89.py:258-312):
+ *   xqt_b200_rotate_quantize(quant_bits = 9, rot_kind 0): per-token scale act_dtype(amax/127), int8 codes
+ *   xqt_b200_lowrank_down:  la = x * down^T (fp32 [M,32])
+ *   xqt_b200_lowrank_up:    low = la16 [M,R] * up16 [N,R]^T in fp32 [M,N]; both operands act_dtype, R (rank_padded) a
+ *                           multiple of 64 with zero padding; dense tcgen05 GEMM
+ *   xqt_b200_w8a8_gemm_addend: xqt_b200_w8a8_gemm with `addend` (fp32 [M,N], 16-byte aligned, or NULL) added to
+ *                           acc * a_s * w_s + bias before the one rounding. */
+int xqt_b200_w8a8_gemm_addend(const void* act_codes, const void* weight_codes, const float* act_scale,
+                              const float* weight_scale, const float* bias, const float* addend,
+                              void* output, int m, int n, int k, int out_dtype, void* workspace,
+                              size_t workspace_bytes, xqt_b200_stream_t stream);
+int xqt_b200_lowrank_up(const void* la, const void* up, float* output, int m, int n, int rank_padded,
+                        int act_dtype, void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * W4A4 SVDQuant / ConvRot linear: after xqt_b200_rotate_quantize(quant_bits = 5, group 64)

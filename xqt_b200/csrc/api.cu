@@ -42,6 +42,10 @@ bool w4a4_gemm_supported(int m, int n, int k);
 int rotate_quant_launch(const void*, const float*, void*, float*, void*, int, int, int, int, int, int, int, cudaStream_t);
 int gemm_i8_launch(const void*, const void*, const float*, const float*, const float*, void*, int, int, int, int,
                    unsigned int*, cudaStream_t);
+int gemm_i8_addend_launch(const void*, const void*, const float*, const float*, const float*, const float*, void*, int, int, int,
+                          int, unsigned int*, cudaStream_t);
+int gemm_f16_launch_strided(const void*, long long, const void*, long long, const float*, const void*, void*, int, int, int, int,
+                            int, int, unsigned int*, cudaStream_t);
 size_t w4a4_dense_workspace_bytes(int m, int n, int k);
 bool w4a4_dense_supported(int m, int n, int k);
 int w4a4_dense_launch(const void*, const float*, const void*, const float*, const float*, const float*, const float*, void*,
@@ -269,6 +273,25 @@ int xqt_b200_w8a8_gemm(const void* act_codes, const void* weight_codes, const fl
   XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
   return gemm_i8_launch(act_codes, weight_codes, act_scale, weight_scale, bias, output, m, n, k, out_dtype,
                         reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
+}
+
+int xqt_b200_w8a8_gemm_addend(const void* act_codes, const void* weight_codes, const float* act_scale,
+                              const float* weight_scale, const float* bias, const float* addend, void* output, int m, int n,
+                              int k, int out_dtype, void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(workspace != nullptr && workspace_bytes >= 256);
+  return gemm_i8_addend_launch(act_codes, weight_codes, act_scale, weight_scale, bias, addend, output, m, n, k, out_dtype,
+                               reinterpret_cast<unsigned int*>(workspace), (cudaStream_t)stream);
+}
+
+int xqt_b200_lowrank_up(const void* la, const void* up, float* output, int m, int n, int rank_padded, int act_dtype,
+                        void* workspace, size_t workspace_bytes, xqt_b200_stream_t stream) {
+  if (m == 0) return 0;
+  XQT_REQUIRE(la != nullptr && up != nullptr && output != nullptr && workspace != nullptr && workspace_bytes >= 256);
+  XQT_REQUIRE(rank_padded >= 64 && rank_padded % 64 == 0 && (act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16));
+  return gemm_f16_launch_strided(la, rank_padded, up, rank_padded, nullptr, nullptr, output, m, n, rank_padded, act_dtype, 1,
+                                 act_dtype == XQT_B200_BF16 ? 1 : 0, reinterpret_cast<unsigned int*>(workspace),
+                                 (cudaStream_t)stream);
 }
 
 int xqt_b200_lowrank_down(const void* rotated, const void* down, float* la, void* la_image, int m, int k, int act_dtype,

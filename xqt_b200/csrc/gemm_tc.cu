@@ -35,6 +35,7 @@ struct GemmTcParams {
   const float* col_scale;   // [N]  weight scale per output channel
   const float* bias;        // [N] or null
   const void* residual;     // [M, N] in the output dtype or null (fp16 kind only)
+  const float* addend;      // [M, N] fp32 or null (int8 kind only): added before the one rounding (a low-rank branch)
   int out_f32;              // fp16 kind only: 1 = the output is fp32 (partial sums of a K-sharded layer)
   void* out;                // [M, N]
   unsigned int* status;
@@ -197,6 +198,12 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tm_a, const CUte
                   v[e] = (float)(int)r[j * 8 + e] * (rs * __ldg(p.col_scale + col + e));
                   if (p.bias != nullptr) v[e] += __ldg(p.bias + col + e);
                 }
+                if (p.addend != nullptr) {
+                  const float4* add = reinterpret_cast<const float4*>(p.addend + (size_t)row * p.n + col);
+                  const float4 a0 = __ldg(add), a1 = __ldg(add + 1);
+                  v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w;
+                  v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
+                }
                 store8<OutT>(out + (size_t)row * p.n + col, v);
               } else {
 #pragma unroll
@@ -341,16 +348,24 @@ static int launch_tc(const void* a, long long lda, const void* b, long long ldb,
   return launch_status();
 }
 
-// int8 A [M,K] x int8 B [N,K]^T, out = acc * row_scale[m] * col_scale[n] (+ bias[n])
+// int8 A [M,K] x int8 B [N,K]^T, out = acc * row_scale[m] * col_scale[n] (+ bias[n]) (+ addend[m,n], fp32)
+int gemm_i8_addend_launch(const void* a, const void* b, const float* row_scale, const float* col_scale, const float* bias,
+                          const float* addend, void* out, int m, int n, int k, int out_dtype, unsigned int* status,
+                          cudaStream_t stream);
 int gemm_i8_launch(const void* a, const void* b, const float* row_scale, const float* col_scale, const float* bias,
                    void* out, int m, int n, int k, int out_dtype, unsigned int* status, cudaStream_t stream) {
-  XQT_REQUIRE(m > 0 && n > 0 && k > 0 && k % 16 == 0 && n % 8 == 0);
+  return gemm_i8_addend_launch(a, b, row_scale, col_scale, bias, nullptr, out, m, n, k, out_dtype, status, stream);
+}
+int gemm_i8_addend_launch(const void* a, const void* b, const float* row_scale, const float* col_scale, const float* bias,
+                          const float* addend, void* out, int m, int n, int k, int out_dtype, unsigned int* status,
+                          cudaStream_t stream) {
+  XQT_REQUIRE(m > 0 && n > 0 && k > 0 && k % 16 == 0 && n % 8 == 0 && ((uintptr_t)addend & 15) == 0);
   XQT_REQUIRE(out_dtype == XQT_B200_BF16 || out_dtype == XQT_B200_FP16);
   XQT_REQUIRE(a != nullptr && b != nullptr && row_scale != nullptr && col_scale != nullptr && out != nullptr && status != nullptr);
   XQT_REQUIRE(((uintptr_t)out & 15) == 0);
   GemmTcParams p{};
   p.m = m; p.n = n; p.k = k;
-  p.row_scale = row_scale; p.col_scale = col_scale; p.bias = bias; p.out = out; p.status = status;
+  p.row_scale = row_scale; p.col_scale = col_scale; p.bias = bias; p.addend = addend; p.out = out; p.status = status;
   const bool wide = (n % 256 == 0);
   if (out_dtype == XQT_B200_BF16)
     return wide ? launch_tc<256, __nv_bfloat16, 0>(a, k, b, k, p, stream) : launch_tc<128, __nv_bfloat16, 0>(a, k, b, k, p, stream);

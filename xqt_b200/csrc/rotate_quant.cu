@@ -14,6 +14,10 @@
 // Quantisation, IEEE division and round-half-to-even throughout:
 //   mode 8: per token,  scale = max(amax, 1e-8) / 127, q = clamp(rint(x/scale), -128, 127)
 //           (xqt/kernels/ops/gemm/quantize.py:75-107)
+//   mode 9: per token, the scale rounded to the activation dtype: scale = T(amax / 127) (0 for an all-zero token, whose
+//           codes are 0), q = clamp(rint(x/scale), -128, 127) -- the activation side of the SVDQuant W8A8 linear
+//           (jit/include/nunchaku/gemm_w8a8.cuh:236-262; the reference multiplies by an approximate reciprocal where
+//           this divides)
 //   mode 4: per (token, group), scale = max(amax/7, 1e-6), q = clamp(rint(x/scale), -8, 7)
 //           (convrot_4bit.py:669-679 at the group granularity of gemm_w4a4.cuh:534-624);
 //           group == 0 selects the artifact's own per-token form (one scale per token,
@@ -32,7 +36,7 @@ namespace xqt_b200 {
 
 constexpr int kRqThreads = 256;
 
-// flags of the int4 modes: bit 0 sign-magnitude bytes, bit 1 tile-major scales
+// flags: bit 0 sign-magnitude bytes, bit 1 tile-major scales (int4 modes); bit 2 the per-token int8 scale is rounded to T
 __device__ __forceinline__ size_t rq_scale_index(int row, int g, int groups, int flags) {
   return (flags & 2) ? ((size_t)(row >> 7) * groups + g) * 128 + (row & 127) : (size_t)row * groups + g;
 }
@@ -97,12 +101,12 @@ rotate_quant_kernel(const T* __restrict__ x, const float* __restrict__ column_sc
     if (tid == 0) {
       float mx = 0.f;
       for (int w = 0; w < kRqThreads / 32; ++w) mx = fmaxf(mx, s_red[w]);
-      const float sc = __fdiv_rn(fmaxf(mx, 1e-8f), 127.0f);
+      const float sc = (flags & 4) ? to_float<T>(from_float<T>(__fdiv_rn(mx, 127.0f))) : __fdiv_rn(fmaxf(mx, 1e-8f), 127.0f);
       s_scale = sc;
       scales[row] = sc;
     }
     __syncthreads();
-    const float sc = fmaxf(s_scale, 1e-8f);
+    const float sc = (flags & 4) ? (s_scale > 0.f ? s_scale : 1.f) : fmaxf(s_scale, 1e-8f);
     for (int i = tid; i < k; i += kRqThreads) {
       const float q = fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), -128.f), 127.f);
       codes[(size_t)row * k + i] = (int8_t)(int)q;
@@ -274,12 +278,12 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
     if (tid == 0) {
       float mx = 0.f;
       for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, s_red[w]);
-      const float s0 = __fdiv_rn(fmaxf(mx, 1e-8f), 127.0f);
+      const float s0 = (flags & 4) ? to_float<T>(from_float<T>(__fdiv_rn(mx, 127.0f))) : __fdiv_rn(fmaxf(mx, 1e-8f), 127.0f);
       s_scale = s0;
       scales[row] = s0;
     }
     __syncthreads();
-    sc = fmaxf(s_scale, 1e-8f);
+    sc = (flags & 4) ? (s_scale > 0.f ? s_scale : 1.f) : fmaxf(s_scale, 1e-8f);
     lo_clamp = -128.f; hi_clamp = 127.f;
   } else if (group == 0) {
 #pragma unroll
@@ -323,11 +327,13 @@ rotate_quant_fast_kernel(const T* __restrict__ x, const float* __restrict__ colu
 
 int rotate_quant_launch(const void* x, const float* column_scale, void* codes, float* scales, void* x_rot, int m, int k,
                         int rot_kind, int rot_block, int mode, int group, int act_dtype, cudaStream_t stream) {
-  XQT_REQUIRE(m > 0 && k > 0 && (mode == 8 || mode == 4 || mode == 5 || mode == 6));
-  // modes 5, 6: the int4 codes of mode 4 written as sign-magnitude bytes; mode 6 also orders the scales tile-major
-  const int signmag = mode == 5 ? 1 : (mode == 6 ? 3 : 0);
+  XQT_REQUIRE(m > 0 && k > 0 && (mode == 8 || mode == 9 || mode == 4 || mode == 5 || mode == 6));
+  // modes 5, 6: the int4 codes of mode 4 written as sign-magnitude bytes; mode 6 also orders the scales tile-major;
+  // mode 9: mode 8 with the scale rounded to the activation dtype
+  const int signmag = mode == 5 ? 1 : (mode == 6 ? 3 : (mode == 9 ? 4 : 0));
   if (mode == 6) XQT_REQUIRE(group == 0 || group == 64);
   if (mode == 5 || mode == 6) mode = 4;
+  if (mode == 9) mode = 8;
   XQT_REQUIRE(rot_kind >= 0 && rot_kind <= 2);
   if (rot_kind != 0) {
     XQT_REQUIRE(rot_block >= 1 && k % rot_block == 0 && column_scale != nullptr);

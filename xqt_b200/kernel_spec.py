@@ -197,6 +197,8 @@ B200_KERNELS = (
                "ConvRot W8A8 linear: rotation + per-token int8 + tcgen05 kind::i8 GEMM"),
     KernelSpec("quantization.svdq_w4a4_linear", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.w4a4:svdq_w4a4_linear", SM100,
                "SVDQuant W4A4 linear with rank-r branch"),
+    KernelSpec("quantization.svdq_w8a8_linear", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.svdq_w8a8:svdq_w8a8_linear", SM100,
+               "SVDQuant W8A8 linear: per-token int8 (scale in the activation dtype) x per-channel int8 + rank-r branch"),
     KernelSpec("quantization.convrot_w4a4_rowwise_linear", KernelBackend.CUSTOM_CUDA,
                "xqt_b200.ops.w4a4:convrot_w4a4_linear", SM100, "ConvRot W4A4 linear (no low-rank branch)"),
     KernelSpec("quantization.gemm_int4_dequant", KernelBackend.CUSTOM_CUDA, "xqt_b200.ops.pattern:gemm_int4_dequant", SM100,

@@ -56,6 +56,8 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_quantize_per_tensor": (_I, [_P] * 4 + [_I] * 3 + [ctypes.c_float, _P]),
     "xqt_b200_w8a8_gemm": (_I, [_P] * 6 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_lowrank_down": (_I, [_P] * 4 + [_I] * 3 + [_P]),
+    "xqt_b200_lowrank_up": (_I, [_P] * 3 + [_I] * 4 + [_P, _Z, _P]),
+    "xqt_b200_w8a8_gemm_addend": (_I, [_P] * 7 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_w4a4_aux_tile_bytes": (_Z, [_I]),
     "xqt_b200_w4a4_supported": (_I, [_I] * 3),
     "xqt_b200_w4a4_workspace_bytes": (_Z, [_I] * 3),

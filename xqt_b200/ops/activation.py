@@ -26,7 +26,7 @@ def _column_scale(rotation: Rotation, device: torch.device) -> torch.Tensor:
 
 def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, group_size: int = 64,
                     return_rotated: bool = False, out: tuple | None = None, sign_magnitude: bool = False,
-                    tiled_scales: bool = False):
+                    tiled_scales: bool = False, scale_in_act_dtype: bool = False):
     """-> (codes int8 ``[M,K]``, scales fp32 ``[M]`` (bits=8) or ``[M, K/group]`` (bits=4)[, rotated x]).
 
     ``sign_magnitude`` (bits=4 only) writes each int4 code as the byte ``sign << 7 | magnitude`` -- read as
@@ -35,6 +35,9 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
 
     ``tiled_scales`` (with ``sign_magnitude``, group 64 or 0) orders the scales tile-major for the W4A4 GEMM: the
     returned buffer has ``ceil(M/128)*128`` rows of storage and holds ``[ceil(M/128)][K/64][128]``.
+
+    ``scale_in_act_dtype`` (bits=8): the per-token scale is ``T(amax/127)`` rounded to the activation dtype, 0 with
+    all-zero codes for an all-zero token -- the SVDQuant W8A8 activation form (gemm_w8a8.cuh:236-262).
 
     ``out = (codes, scales[, rotated])`` supplies preallocated buffers whose leading ``M`` rows are
     written (a workspace sized for at least M rows): the call then allocates nothing."""
@@ -45,6 +48,8 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
         raise XQTBackendError("rotate_quantize supports 8-bit per-token or 4-bit per-group codes")
     if sign_magnitude and bits != 4:
         raise XQTBackendError("sign-magnitude bytes are the form of 4-bit codes only")
+    if scale_in_act_dtype and bits != 8:
+        raise XQTBackendError("the activation-dtype scale is a form of the 8-bit per-token codes only")
     if tiled_scales and not (sign_magnitude and int(group_size) in (0, 64)):
         raise XQTBackendError("tile-major scales go with sign-magnitude codes of group 64 (or per-token) only")
     x = x.contiguous()
@@ -75,7 +80,7 @@ def rotate_quantize(x: torch.Tensor, rotation: Rotation | None, *, bits: int, gr
             code = native.library().xqt_b200_rotate_quantize(
                 x.data_ptr(), native.ptr(cs), codes.data_ptr(), scales.data_ptr(), native.ptr(rotated), m, k,
                 _KIND[None if rotation is None else rotation.kind], 0 if rotation is None else rotation.block,
-                (6 if tiled_scales else 5) if sign_magnitude else bits, int(group_size), native.DTYPE_CODE[x.dtype], native.stream_handle(device))
+                (6 if tiled_scales else 5) if sign_magnitude else (9 if scale_in_act_dtype else bits), int(group_size), native.DTYPE_CODE[x.dtype], native.stream_handle(device))
         native.check(code, "xqt_b200_rotate_quantize")
     return (codes, scales, rotated) if return_rotated else (codes, scales)
 
