@@ -265,8 +265,17 @@ def run_gpu_arm(args) -> None:
                 pw.qweight.to(device), pw.scales.to(device), pw.zero_points.to(device), group_size=GROUP,
                 nibble_signed=False)
         dev_layers.append(copy_layers)
-    dev_inputs = {key: x.to(device) for key, x in inputs.items()}
-    host_inputs = {key: x.pin_memory() for key, x in inputs.items()}
+    # The step's 16 activations live side by side in one device buffer (and one pinned host buffer): the kernels read
+    # views of it, so the end-to-end arm refills it with ONE host-to-device copy and replays the same graphs.
+    in_total = sum(x.numel() for x in inputs.values())
+    x_dev_all = torch.empty(in_total, device=device, dtype=torch.bfloat16)
+    x_host_all = torch.empty(in_total, dtype=torch.bfloat16).pin_memory()
+    dev_inputs, off = {}, 0
+    for key, x in inputs.items():
+        x_host_all[off:off + x.numel()].copy_(x.reshape(-1))
+        dev_inputs[key] = x_dev_all[off:off + x.numel()].view(x.shape)
+        off += x.numel()
+    x_dev_all.copy_(x_host_all)
     # hot-callables bound once per (pool copy, layer, M): the per-call host work is one C-ABI call
     bound = {}
     for copy in range(pool):
@@ -361,15 +370,14 @@ def run_gpu_arm(args) -> None:
     # --- end to end through the public API with host buffers
     result = packed_all if world > 1 else packed          # what the caller reads back: all ranks' columns
     host_out = torch.empty(result.shape, dtype=torch.bfloat16).pin_memory()
-    h2d = sum(inputs[(k, m)].numel() * 2 for k, _ in SHAPES for m in MS)
+    h2d = x_host_all.numel() * 2
     d2h = result.numel() * 2
 
     def e2e_step(i):
-        copy = i % pool
-        for (k, n) in SHAPES:
-            for m in MS:
-                x = host_inputs[(k, m)].to(device, non_blocking=True)
-                one_problem(copy, k, n, m, x)
+        # one copy in (every activation of the step, from pinned host memory), the step's kernels from their CUDA
+        # graph (the public bound callables, captured once), one copy out of every output, then the host waits
+        x_dev_all.copy_(x_host_all, non_blocking=True)
+        graphs[i % pool].replay()
         gather_step()
         host_out.copy_(result, non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -440,7 +448,9 @@ def run_gpu_arm(args) -> None:
         },
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps},
+                "ms_per_step": e2e_ms / args.steps,
+                "form": "per step: one copy of the 16 activations from pinned host memory, the 16 bound decode calls replayed "
+                        "from their CUDA graph, one copy of all outputs to pinned host memory, host waits"},
         "gpu_launches": timed_launches,
         "detail": detail,
         "other_configs": extras,
