@@ -111,13 +111,14 @@ __device__ __forceinline__ uint2 signmag8(uint32_t w) {
   return make_uint2(__byte_perm(e, o, 0x5140), __byte_perm(e, o, 0x7362));
 }
 
-// packed nibbles [N, K/2] -> sign-magnitude bytes [N, K]; a thread converts 16 packed bytes (32 weights)
+// packed nibbles [N, K/2] -> sign-magnitude bytes [N, K]; a thread converts 8 packed bytes into one 16-byte store, so a
+// warp's loads (256 bytes) and stores (512 bytes) are contiguous.  `chunks` counts 16-byte packed pieces.
 __global__ void __launch_bounds__(256) w44_expand_kernel(const uint4* __restrict__ packed, uint4* __restrict__ bytes, size_t chunks) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (size_t)gridDim.x * blockDim.x) {
-    const uint4 v = __ldg(packed + i);
-    const uint2 a = signmag8(v.x), b = signmag8(v.y), c = signmag8(v.z), d = signmag8(v.w);
-    bytes[2 * i] = make_uint4(a.x, a.y, b.x, b.y);
-    bytes[2 * i + 1] = make_uint4(c.x, c.y, d.x, d.y);
+  const uint2* src = reinterpret_cast<const uint2*>(packed);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < 2 * chunks; i += (size_t)gridDim.x * blockDim.x) {
+    const uint2 v = __ldg(src + i);
+    const uint2 a = signmag8(v.x), b = signmag8(v.y);
+    bytes[i] = make_uint4(a.x, a.y, b.x, b.y);
   }
 }
 
