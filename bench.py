@@ -621,8 +621,9 @@ def measure_other_configs(device, world, rank, barrier) -> list:
             warm = lambda: blocks[0](x)  # noqa: E731
             call_name, direct = "W4A16SwiGLUMLP.__call__ (eager launches)", False
             us_cold, clocks, us_graph = us_eager, clocks_eager, None
-            if world == 1:
-                # the public graph form of the block (one CUDA graph per weight copy): no host gaps between its launches
+            if world == 1 or all(getattr(b._peer, "counted", False) for b in blocks):
+                # the public graph form of the block (one CUDA graph per weight copy): no host gaps between its launches;
+                # with several ranks the reduction inside is the counted peer-memory kernel, every rank replays in step
                 replays = [b.capture(m) for b in blocks]
                 for rp in replays:
                     rp.input.copy_(x)

@@ -188,6 +188,17 @@ int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights
                                 const void* lane_zeros, const float* bias, const void* residual, void* output, int m, int n, int k,
                                 int group_size, int nibble_signed, int act_dtype, int param_dtype,
                                 int out_dtype, int epilogue_flags, unsigned int* status, xqt_b200_stream_t stream);
+/* xqt_b200_w4a16_decode_lanes whose output slot is chosen on the device: with out_select != NULL the result is written
+ * at output + ((*out_select + 1) & 1) * out_select_stride bytes (stride a multiple of 16; not with epilogue flag 2).
+ * *out_select is the finished-call counter of xqt_b200_peer_allreduce_counted, read after the kernel's dependency on
+ * the previous launch: a row-parallel decode layer writes its fp32 partial into the slot the next counted reduction
+ * reads, with nothing in the launch arguments changing from call to call (CUDA-graph replay). */
+int xqt_b200_w4a16_decode_lanes_select(const void* activation, const void* lane_weights, const void* lane_scales,
+                                       const void* lane_zeros, const float* bias, const void* residual, void* output,
+                                       int m, int n, int k, int group_size, int nibble_signed, int act_dtype,
+                                       int param_dtype, int out_dtype, int epilogue_flags,
+                                       const unsigned int* out_select, size_t out_select_stride,
+                                       unsigned int* status, xqt_b200_stream_t stream);
 
 /* W4A16 decode with the scratch built into the library: same operation, arguments and result as
  * xqt_b200_w4a16_decode_tiled, minus the workspace pair.  It has no counterpart in the reference.
@@ -366,6 +377,16 @@ int xqt_b200_peer_allreduce(const void* const* partials, void* const* flags, int
                             unsigned int call, long long count, int n, const float* bias, void* output,
                             int out_dtype, unsigned int spin_limit, unsigned int* status,
                             xqt_b200_stream_t stream);
+/* The same reduction with the call number kept in device memory, so that the launch can be captured into a CUDA
+ * graph and replayed: counter[0] (zero before the first call, this rank's own device memory, 2 x uint32) counts the
+ * finished calls; the kernel works as call counter[0] + 1, reads slot (call & 1) of every rank's two-slot partial buffer
+ * (partials[r] = slot 0, the slots slot_stride elements apart) and publishes the new count when its last block ends.
+ * The kernel that writes this rank's partial selects the same slot from the same word
+ * (xqt_b200_w4a16_decode_lanes_select).  Every rank must make the same sequence of calls. */
+int xqt_b200_peer_allreduce_counted(const void* const* partials, void* const* flags, int rank, int world,
+                                    unsigned int* counter, long long slot_stride, long long count, int n,
+                                    const float* bias, void* output, int out_dtype,
+                                    unsigned int spin_limit, unsigned int* status, xqt_b200_stream_t stream);
 
 /* SwiGLU gating between the projections of an MLP: output[m, i] = silu(gate_up[m, i]) * gate_up[m, inter + i],
  * evaluated in fp32 and rounded once.  gate_up is [M, 2*inter] (the gate and up projections fused

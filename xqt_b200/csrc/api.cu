@@ -21,7 +21,7 @@ int w4a16_decode_tc_launch(const void*, const void*, const void*, const float*, 
 size_t w4a16_decode_tc_workspace_bytes();
 bool w4a16_decode_tc_supported(int m, int n, int k, int group_size);
 int w4a16_decode_cl_launch(const void*, const void*, const void*, const void*, const float*, const void*, void*, int, int, int,
-                           int, int, int, int, int, int, unsigned int*, cudaStream_t);
+                           int, int, int, int, int, int, const unsigned int*, long long, unsigned int*, cudaStream_t);
 bool w4a16_decode_cl_supported(int m, int n, int k, int group_size);
 void w4a16_decode_cl_set_plan(int kw, int s);
 void w4a16_decode_cl_get_plan(int m, int n, int k, int* kw, int* s);
@@ -52,7 +52,7 @@ int w4a4_dense_launch(const void*, const float*, const void*, const float*, cons
                       int, int, int, int, void*, size_t, cudaStream_t);
 int lowrank_down_tc_launch(const void*, const void*, float*, int, int, int, unsigned int*, cudaStream_t);
 int peer_allreduce_launch(const void* const*, void* const*, int, int, unsigned int, long long, int, const float*, void*, int,
-                          unsigned int, unsigned int*, cudaStream_t);
+                          unsigned int, unsigned int*, unsigned int*, long long, cudaStream_t);
 int w4a16_decode_static_status(unsigned int*, cudaStream_t);
 int quant_per_tensor_launch(const void*, void*, float*, float*, int, int, int, float, cudaStream_t);
 }  // namespace xqt_b200
@@ -212,10 +212,26 @@ int xqt_b200_w4a16_decode_lanes_set_plan(int warp_quads, int cluster) {
   return 0;
 }
 
+int xqt_b200_w4a16_decode_lanes_select(const void* activation, const void* lane_weights, const void* lane_scales,
+                                       const void* lane_zeros, const float* bias, const void* residual, void* output, int m,
+                                       int n, int k, int group_size, int nibble_signed, int act_dtype, int param_dtype,
+                                       int out_dtype, int epilogue_flags, const unsigned int* out_select,
+                                       size_t out_select_stride, unsigned int* status, xqt_b200_stream_t stream);
+
 int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights, const void* lane_scales,
                                 const void* lane_zeros, const float* bias, const void* residual, void* output, int m, int n, int k,
                                 int group_size, int nibble_signed, int act_dtype, int param_dtype, int out_dtype,
                                 int epilogue_flags, unsigned int* status, xqt_b200_stream_t stream) {
+  return xqt_b200_w4a16_decode_lanes_select(activation, lane_weights, lane_scales, lane_zeros, bias, residual, output, m, n, k,
+                                            group_size, nibble_signed, act_dtype, param_dtype, out_dtype, epilogue_flags,
+                                            nullptr, 0, status, stream);
+}
+
+int xqt_b200_w4a16_decode_lanes_select(const void* activation, const void* lane_weights, const void* lane_scales,
+                                       const void* lane_zeros, const float* bias, const void* residual, void* output, int m,
+                                       int n, int k, int group_size, int nibble_signed, int act_dtype, int param_dtype,
+                                       int out_dtype, int epilogue_flags, const unsigned int* out_select,
+                                       size_t out_select_stride, unsigned int* status, xqt_b200_stream_t stream) {
   XQT_REQUIRE(m >= 0 && n > 0 && k > 0 && (epilogue_flags & ~3) == 0);
   XQT_REQUIRE(act_dtype == XQT_B200_FP16 || act_dtype == XQT_B200_BF16);
   XQT_REQUIRE(param_dtype == XQT_B200_FP16 || param_dtype == XQT_B200_BF16 || param_dtype == XQT_B200_FP32);
@@ -224,7 +240,7 @@ int xqt_b200_w4a16_decode_lanes(const void* activation, const void* lane_weights
   XQT_REQUIRE(out_dtype == act_dtype || out_dtype == XQT_B200_FP32);
   return w4a16_decode_cl_launch(activation, lane_weights, lane_scales, lane_zeros, bias, residual, output, m, n, k, group_size,
                                 nibble_signed, act_dtype, param_dtype, out_dtype == XQT_B200_FP32 ? 1 : 0, epilogue_flags,
-                                status, (cudaStream_t)stream);
+                                out_select, (long long)out_select_stride, status, (cudaStream_t)stream);
 }
 
 int xqt_b200_w4a16_decode_tiled_static(const void* activation, const void* tiled_weights, const void* tiled_params,
@@ -356,7 +372,16 @@ int xqt_b200_peer_allreduce(const void* const* partials, void* const* flags, int
                             unsigned int spin_limit, unsigned int* status, xqt_b200_stream_t stream) {
   XQT_REQUIRE(status != nullptr);
   return peer_allreduce_launch(partials, flags, rank, world, call, count, n, bias, output, out_dtype, spin_limit, status,
-                               (cudaStream_t)stream);
+                               nullptr, 0, (cudaStream_t)stream);
+}
+
+int xqt_b200_peer_allreduce_counted(const void* const* partials, void* const* flags, int rank, int world,
+                                    unsigned int* counter, long long slot_stride, long long count, int n,
+                                    const float* bias, void* output, int out_dtype, unsigned int spin_limit,
+                                    unsigned int* status, xqt_b200_stream_t stream) {
+  XQT_REQUIRE(status != nullptr && counter != nullptr);
+  return peer_allreduce_launch(partials, flags, rank, world, 0u, count, n, bias, output, out_dtype, spin_limit, status,
+                               counter, slot_stride, (cudaStream_t)stream);
 }
 
 int xqt_b200_swiglu(const void* gate_up, void* output, int m, int inter, int dtype, xqt_b200_stream_t stream) {

@@ -17,6 +17,12 @@
 // records kTimeout in the status word -- which may live in pinned host memory, so that the host sees
 // it without a synchronisation -- skips the wait and finishes through its normal path; the output is
 // then not the sum and the caller must treat the call as failed.
+//
+// Counted form (graph-safe): the call number lives in device memory instead of a launch argument.  `counter[0]` holds
+// the number of finished calls; every block reads it on entry, works as call counter[0] + 1 on slot (call & 1) of the
+// two-slot partial buffers, and the block that finishes last (ticket in counter[1]) publishes the new count.  The
+// kernel that wrote the partial picked its slot from the same word (the decode kernel's out_select), so a captured
+// graph replays correctly: nothing in the launch arguments changes from call to call.
 #include "common.cuh"
 
 namespace xqt_b200 {
@@ -38,6 +44,8 @@ struct PeerReduceParams {
   void* out;                              // [count] in T
   unsigned int* status;
   unsigned int spin_limit;                // polls before the wait for a peer gives up
+  unsigned int* counter;                  // counted form: [0] finished calls, [1] block tickets; null otherwise
+  long long slot_stride;                  // counted form: elements between the two slots of every partial buffer
 };
 
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
@@ -52,15 +60,21 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 template <typename T>
 __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReduceParams p) {
   using namespace par;
+  unsigned int call = p.call;
+  long long slot_off = 0;
+  if (p.counter != nullptr) {
+    call = *reinterpret_cast<volatile unsigned int*>(p.counter) + 1u;
+    slot_off = (call & 1u) ? p.slot_stride : 0;
+  }
   // (1) signal and wait.  Block 0 signals (the partial was written by the kernel before this one on
   // the same stream, so it is complete); every block waits on this rank's own flag array.
   if (blockIdx.x == 0 && threadIdx.x < p.world && (int)threadIdx.x != p.rank)
-    st_release_sys(p.flags[threadIdx.x] + p.rank, p.call);
+    st_release_sys(p.flags[threadIdx.x] + p.rank, call);
   if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
     const unsigned int* f = p.flags[p.rank] + threadIdx.x;
     unsigned int spins = 0;
     // call numbers only grow: "signalled this call or a later one"
-    while ((int)(ld_acquire_sys(f) - p.call) < 0) {
+    while ((int)(ld_acquire_sys(f) - call) < 0) {
       if (++spins >= p.spin_limit) {
         st_release_sys(p.status, (unsigned int)kTimeout);   // device or pinned host memory
         break;
@@ -76,7 +90,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReducePar
     float4 part[kMaxWorld];
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r)
-      if (r < p.world) part[r] = __ldcg(reinterpret_cast<const float4*>(p.partial[r]) + v);   // all loads in flight
+      if (r < p.world) part[r] = __ldcg(reinterpret_cast<const float4*>(p.partial[r] + slot_off) + v);   // all loads in flight
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r)
       if (r < p.world) {
@@ -90,13 +104,28 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReducePar
     T o[4] = {from_float<T>(acc.x), from_float<T>(acc.y), from_float<T>(acc.z), from_float<T>(acc.w)};
     *reinterpret_cast<uint2*>(out + v * 4) = *reinterpret_cast<const uint2*>(o);
   }
+  if (p.counter != nullptr) {
+    // every block has read counter[0] before it takes its ticket; the last one publishes the finished call
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(p.counter + 1, 1u) == gridDim.x - 1) {
+        p.counter[1] = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile unsigned int*>(p.counter) = call;
+      }
+    }
+  }
 }
 
+// counter == nullptr: `call` is this call's number and partials[r] the slot in use; else the counted form: partials[r]
+// is slot 0 of rank r's two-slot buffer, the slots slot_stride elements apart, and `call` is ignored
 int peer_allreduce_launch(const void* const* partials, void* const* flags, int rank, int world, unsigned int call,
                           long long count, int n, const float* bias, void* out, int out_dtype, unsigned int spin_limit,
-                          unsigned int* status, cudaStream_t stream) {
+                          unsigned int* status, unsigned int* counter, long long slot_stride, cudaStream_t stream) {
   using namespace par;
-  XQT_REQUIRE(world >= 2 && world <= kMaxWorld && rank >= 0 && rank < world && call > 0);
+  XQT_REQUIRE(world >= 2 && world <= kMaxWorld && rank >= 0 && rank < world && (call > 0 || counter != nullptr));
+  XQT_REQUIRE(counter == nullptr || (slot_stride >= count && slot_stride % 4 == 0));
   XQT_REQUIRE(count > 0 && count % 4 == 0 && n > 0 && n % 4 == 0 && count % n == 0);
   XQT_REQUIRE(partials != nullptr && flags != nullptr && out != nullptr && status != nullptr);
   XQT_REQUIRE(out_dtype == XQT_B200_BF16 || out_dtype == XQT_B200_FP16);
@@ -109,6 +138,7 @@ int peer_allreduce_launch(const void* const* partials, void* const* flags, int r
   }
   p.rank = rank; p.world = world; p.call = call; p.count = count; p.n = n; p.bias = bias; p.out = out; p.status = status;
   p.spin_limit = spin_limit == 0 ? kSpin : spin_limit;
+  p.counter = counter; p.slot_stride = slot_stride;
   const long long vecs = count / 4;
   long long blocks = (vecs + 255) / 256;
   if (blocks > 148) blocks = 148;

@@ -74,6 +74,8 @@ struct DecodeClParams {
   unsigned int* status; // may be null
   int m, n, k, out_f32;
   int round_first;      // 1: round the projection to T before the residual is added (unfused `residual + proj` numerics)
+  const unsigned int* out_select;   // null, or a device word w: the output goes to out + ((w + 1) & 1) * out_select_stride bytes
+  long long out_select_stride;      // (the slot of a two-slot buffer that the counted peer reduction will read next)
   int glu;              // 1: a tile is 64 gate channels followed by their 64 up channels; out[M, N/2] = silu(gate) * up
   int kblocks, pieces, kw;
   int per, rem;         // kblocks = pieces * per + rem: piece i starts at i * per + min(i, rem)
@@ -482,6 +484,8 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
     }
   } else {
     const int own = p.m > (int)rank ? (p.m - (int)rank + (int)S - 1) / (int)S : 0;
+    unsigned char* out_base = reinterpret_cast<unsigned char*>(p.out);
+    if (p.out_select != nullptr && ((*reinterpret_cast<const volatile unsigned int*>(p.out_select) + 1u) & 1u)) out_base += p.out_select_stride;
     for (int idx = tid; idx < own * kTileRows; idx += nthreads) {
       const int li = idx >> 7, ch = idx & 127;
       const int token = li * (int)S + (int)rank;
@@ -495,8 +499,8 @@ w4a16_decode_cl_kernel(const DecodeClParams p) {
           if (p.round_first) sum = to_float<T>(from_float<T>(sum));
           sum += to_float<T>(reinterpret_cast<const T*>(p.residual)[o]);     // may alias out: read before the store below
         }
-        if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = sum;
-        else reinterpret_cast<T*>(p.out)[o] = from_float<T>(sum);
+        if (p.out_f32) reinterpret_cast<float*>(out_base)[o] = sum;
+        else reinterpret_cast<T*>(out_base)[o] = from_float<T>(sum);
       }
     }
   }
@@ -632,7 +636,8 @@ static int dcl_dispatch(const DecodeClParams& p, int group_size, int nt, int gri
 
 int w4a16_decode_cl_launch(const void* x, const void* wt, const void* scl, const void* zer, const float* bias, const void* residual,
                            void* out, int m, int n, int k, int group_size, int nibble_signed, int act_dtype,
-                           int param_dtype, int out_f32, int epilogue_flags, unsigned int* status, cudaStream_t stream) {
+                           int param_dtype, int out_f32, int epilogue_flags, const unsigned int* out_select,
+                           long long out_select_stride, unsigned int* status, cudaStream_t stream) {
   using namespace dcl;
   XQT_REQUIRE(w4a16_decode_cl_supported(m, n, k, group_size));
   XQT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)wt & 31) == 0 && ((uintptr_t)scl & 15) == 0 && ((uintptr_t)zer & 15) == 0);
@@ -646,6 +651,8 @@ int w4a16_decode_cl_launch(const void* x, const void* wt, const void* scl, const
   p.m = m; p.n = n; p.k = k; p.out_f32 = out_f32;
   p.round_first = (epilogue_flags & 1) != 0;
   XQT_REQUIRE(!(p.round_first && out_f32));
+  p.out_select = out_select; p.out_select_stride = out_select_stride;
+  XQT_REQUIRE(out_select == nullptr || (out_select_stride % 16 == 0 && (epilogue_flags & 2) == 0));
   p.glu = (epilogue_flags & 2) != 0;
   XQT_REQUIRE(!p.glu || (n % kTileRows == 0 && !out_f32 && residual == nullptr));
   p.kblocks = kblocks; p.kw = plan.kw; p.pieces = plan.kw * plan.s;

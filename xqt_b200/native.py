@@ -49,6 +49,7 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a16_decode_lanes_plan": (_I, [_I] * 4 + [ctypes.POINTER(_I), ctypes.POINTER(_I)]),
     "xqt_b200_w4a16_decode_lanes_set_plan": (_I, [_I, _I]),
     "xqt_b200_w4a16_decode_lanes": (_I, [_P] * 7 + [_I] * 9 + [_P, _P]),
+    "xqt_b200_w4a16_decode_lanes_select": (_I, [_P] * 7 + [_I] * 9 + [_P, _Z, _P, _P]),
     "xqt_b200_w4a16_decode_tiled_static": (_I, [_P] * 6 + [_I] * 8 + [_P]),
     "xqt_b200_w4a16_decode_static_scratch_bytes": (_Z, []),
     "xqt_b200_w4a16_decode_static_max_n": (_I, []),
@@ -68,6 +69,7 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a4_dense": (_I, [_P] * 8 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_lowrank_down_tc": (_I, [_P] * 3 + [_I] * 3 + [_P, _Z, _P]),
     "xqt_b200_peer_allreduce": (_I, [_P, _P, _I, _I, ctypes.c_uint, ctypes.c_longlong, _I, _P, _P, _I, ctypes.c_uint, _P, _P]),
+    "xqt_b200_peer_allreduce_counted": (_I, [_P, _P, _I, _I, _P, ctypes.c_longlong, ctypes.c_longlong, _I, _P, _P, _I, ctypes.c_uint, _P, _P]),
     "xqt_b200_w4a16_decode_static_status": (_I, [ctypes.POINTER(ctypes.c_uint), _P]),
     "xqt_b200_swiglu": (_I, [_P, _P, _I, _I, _I, _P]),
     "xqt_b200_workspace_status": (_I, [_P, ctypes.POINTER(ctypes.c_uint), _P]),

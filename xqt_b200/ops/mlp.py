@@ -130,6 +130,17 @@ class _Linear:
         return w4a16_linear(x, self.qweight, self.scales, self.zeros, group_size=self.group,
                             nibble_signed=self.signed, k=self.k, out_dtype=odt, out=out)
 
+    def partial_into(self, x: torch.Tensor, peer) -> None:
+        """Decode-size fp32 partial sums of a K-sharded layer, written into the slot of ``peer`` (a counted
+        :class:`xqt_b200.parallel.PeerAllReduce`) that its next reduction reads; the kernel picks the slot on the device."""
+
+        m = int(x.shape[0])
+        run = self._bound.get((m, "peer"))
+        if run is None:
+            run = bind_w4a16_decode(self.tiled, rows=m, dtype=self.dtype, out_dtype=torch.float32, out_select=peer.out_select)
+            self._bound[(m, "peer")] = run
+        run(x, peer.partial(m, self.n))
+
     def rows(self, x: torch.Tensor, n0: int, n1: int, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         """The output channels [n0, n1) only: ``x @ W[n0:n1]^T`` (a row block of the canonical weight is contiguous)."""
 
@@ -185,7 +196,8 @@ class W4A16SwiGLUMLP:
         if world > 1 and peer_reduce and self.down.tiled is not None and self.down.tiled.layout in ("rows128", "lanes"):
             from ..parallel import PeerAllReduce
 
-            self._peer = PeerAllReduce(device, 16 * self.hidden, group)
+            # on the lanes layout the reduction is the counted (graph-safe) form: the call number lives on the device
+            self._peer = PeerAllReduce(device, 16 * self.hidden, group, counted=self.down.tiled.layout == "lanes")
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         h = self.gate_up.gated(x) if isinstance(self.gate_up, _Linear) else None     # decode sizes: one launch
@@ -195,7 +207,10 @@ class W4A16SwiGLUMLP:
             return self.down(h)
         m = int(h.shape[0])
         if self._peer is not None and m <= 16:
-            self.down(h, out_dtype=torch.float32, out=self._peer.partial(m, self.hidden))
+            if self._peer.counted:
+                self.down.partial_into(h, self._peer)
+            else:
+                self.down(h, out_dtype=torch.float32, out=self._peer.partial(m, self.hidden))
             return self._peer.reduce(m, self.hidden, dtype=self.dtype)
         blocks = self._reduce_blocks(m)
         if blocks == 1 or not isinstance(self.down, _Linear):
@@ -218,15 +233,18 @@ class W4A16SwiGLUMLP:
         return out
 
     def capture(self, rows: int):
-        """The block for a fixed row count as one CUDA graph (single-GPU blocks; the decode kernels chain through
-        programmatic dependent launch inside the graph, so the three launches run without host gaps -- what xqt's
-        graph decode runtime does around its modules, xqt/runtime/graph_decode.py).  Returns ``replay`` with
+        """The block for a fixed row count as one CUDA graph (the decode kernels chain through programmatic dependent
+        launch inside the graph, so the launches run without host gaps -- what xqt's graph decode runtime does around
+        its modules, xqt/runtime/graph_decode.py).  Single-GPU blocks at any row count; with more ranks the decode
+        sizes, whose reduction is the counted peer-memory kernel (every rank must then capture and replay in step: the
+        same number of calls on every rank).  Returns ``replay`` with
         ``replay.input`` (``[rows, hidden]``, written by the caller, e.g. the target of its host-to-device copy) and
         ``replay.output``; ``replay()`` launches the graph on the current stream and returns ``replay.output``."""
 
-        if self.world != 1:
-            raise XQTBackendError("capture: the peer-memory reduction takes its call number from the host and cannot be captured")
         rows = int(rows)
+        if self.world != 1 and not (self._peer is not None and self._peer.counted and rows <= 16):
+            raise XQTBackendError("capture: with more than one rank only the decode sizes (rows <= 16) on the counted "
+                                  "peer-memory reduction can be captured (NCCL collectives stay outside graphs here)")
         device = self.gate_up.qweight.device
         static_in = torch.zeros((rows, self.hidden), device=device, dtype=self.dtype)
         side = torch.cuda.Stream(device)

@@ -209,7 +209,7 @@ def glu_row_order(inter: int) -> torch.Tensor:
 
 
 def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None = None,
-                      out_dtype: torch.dtype | None = None, glu: bool = False):
+                      out_dtype: torch.dtype | None = None, glu: bool = False, out_select: tuple[int, int] | None = None):
     """Hot-callable for the decode kernel on a :class:`xqt_b200.prepack.TiledW4` layer:
     ``run(x, out=None, residual=None) -> Tensor`` for a fixed row count (1..16).  Static tensors are
     validated here, once; each call checks the activation and makes one C-ABI call
@@ -218,7 +218,11 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
     ``glu`` (``lanes`` layout): the layer is a fused gate/up projection whose rows were laid out with
     :func:`glu_row_order`; the kernel's epilogue gates them, ``run`` returns ``silu(gate) * up`` as ``[rows, N/2]``
     with the bits of the unfused linear -> SwiGLU (the horizontally fused gate/up + SwiGLU of
-    xqt/kernels/ops/_impl/cute/convrot_w8a8_sm89.py:664-917, at decode sizes)."""
+    xqt/kernels/ops/_impl/cute/convrot_w8a8_sm89.py:664-917, at decode sizes).
+
+    ``out_select = (device word address, stride in bytes)`` (``lanes`` layout): the kernel writes at
+    ``out + ((word + 1) & 1) * stride`` -- the slot of a two-slot buffer that the counted peer reduction reads next
+    (:class:`xqt_b200.parallel.PeerAllReduce`, ``counted=True``)."""
 
     device = tiled.weights.device
     if device.type != "cuda":
@@ -232,9 +236,9 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
     lib = native.library()
     use_tc = tiled.layout == "rows128"
     if tiled.layout == "lanes":
-        return _bind_decode_lanes(tiled, rows=rows, dtype=dtype, bias=bias, odt=odt, glu=glu)
-    if glu:
-        raise XQTBackendError("the fused SwiGLU epilogue is served by the lanes decode layout only")
+        return _bind_decode_lanes(tiled, rows=rows, dtype=dtype, bias=bias, odt=odt, glu=glu, out_select=out_select)
+    if glu or out_select is not None:
+        raise XQTBackendError("the fused SwiGLU epilogue and the device-selected output slot are served by the lanes decode layout only")
     if use_tc:
         if not tiled.integer_zero_points:
             raise XQTBackendError("the tcgen05 decode kernel needs integer zero points in [0, 119]")
@@ -286,7 +290,8 @@ def bind_w4a16_decode(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tenso
     return run
 
 
-def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None, odt: torch.dtype, glu: bool = False):
+def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tensor | None, odt: torch.dtype, glu: bool = False,
+                       out_select: tuple[int, int] | None = None):
     """``bind_w4a16_decode`` for the ``lanes`` layout (cluster split-K kernel: no workspace)."""
 
     device = tiled.weights.device
@@ -302,11 +307,15 @@ def _bind_decode_lanes(tiled, *, rows: int, dtype: torch.dtype, bias: torch.Tens
     bias32 = None if bias is None else bias.reshape(-1).to(device=device, dtype=torch.float32).contiguous()
     if bias32 is not None and bias32.numel() != n:
         raise XQTBackendError("B200 W4A16 bias must have N elements")
-    fn = lib.xqt_b200_w4a16_decode_lanes
+    if out_select is not None and glu:
+        raise XQTBackendError("the device-selected output slot does not combine with the fused SwiGLU epilogue")
+    fn = lib.xqt_b200_w4a16_decode_lanes if out_select is None else lib.xqt_b200_w4a16_decode_lanes_select
     head = (tiled.weights.data_ptr(), tiled.params[0].data_ptr(),
             tiled.params[1].data_ptr() if tiled.has_zero_point else 0, native.ptr(bias32))
     tail = (rows, n, k, tiled.group_size, int(tiled.nibble_signed), native.DTYPE_CODE[dtype],
             native.DTYPE_CODE[tiled.params.dtype], native.DTYPE_CODE[odt], 2 if glu else 0)
+    if out_select is not None:
+        tail = tail + (int(out_select[0]), int(out_select[1]))
     index = device.index if device.index is not None else torch.cuda.current_device()
     status = native.status_word(device)
     status_ptr = status.data_ptr()

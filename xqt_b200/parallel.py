@@ -135,7 +135,7 @@ class PeerAllReduce:
 
     MAX_WORLD = 8
 
-    def __init__(self, device: torch.device, max_elements: int, group=None) -> None:
+    def __init__(self, device: torch.device, max_elements: int, group=None, counted: bool = False) -> None:
         import ctypes
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -160,19 +160,33 @@ class PeerAllReduce:
         self._flags = array(*flag_ptrs)
         self._call = 0
         self._native = native
+        # counted form: the call number lives in device memory ([0] finished calls, [1] block tickets), the kernels pick
+        # the slot from it, and a launch may be captured into a CUDA graph (see reduce)
+        self.counted = bool(counted)
+        self._counter = torch.zeros(4, dtype=torch.int32, device=device) if counted else None
         # the kernel reports a peer that never signalled here; pinned, so the host reads it without a sync
         self._host_status = torch.zeros(16, dtype=torch.int32).pin_memory()
         self.spin_limit = 0          # 0 = the kernel's default bound (2^22 polls)
         torch.cuda.synchronize(device)
         dist.barrier(group)          # every rank's zeros are in place before anybody signals
 
+    @property
+    def out_select(self) -> tuple[int, int]:
+        """``(address of the finished-call counter, bytes between the two slots)`` for the kernel that writes this rank's
+        partial (counted form): it then stores at ``partial(...) + ((counter + 1) & 1) * stride``."""
+
+        if not self.counted:
+            raise XQTBackendError("PeerAllReduce: out_select belongs to the counted form")
+        return self._counter.data_ptr(), self.max_elements * 4
+
     def partial(self, rows: int, n: int) -> torch.Tensor:
-        """This rank's fp32 ``[rows, n]`` slot for the NEXT call of ``reduce``."""
+        """This rank's fp32 ``[rows, n]`` slot for the NEXT call of ``reduce`` (counted form: slot 0, from which the
+        writing kernel steps to the slot in use through ``out_select``)."""
 
         count = rows * n
         if count > self.max_elements:
             raise XQTBackendError("PeerAllReduce: partial larger than the buffer it was built with")
-        slot = (self._call + 1) & 1
+        slot = 0 if self.counted else (self._call + 1) & 1
         return self._buffer[slot * self.max_elements: slot * self.max_elements + count].view(rows, n)
 
     def reduce(self, rows: int, n: int, *, bias: torch.Tensor | None = None, dtype: torch.dtype = torch.bfloat16,
@@ -180,10 +194,23 @@ class PeerAllReduce:
         native = self._native
         if n % 4 or dtype not in (torch.float16, torch.bfloat16):
             raise XQTBackendError("PeerAllReduce: N must be a multiple of 4 and the output fp16 or bf16")
+        if self.counted:
+            # nothing in this launch changes from call to call: it may be captured and replayed
+            if not torch.cuda.is_current_stream_capturing():
+                self.check()
+            if out is None:
+                out = torch.empty((rows, n), device=self.device, dtype=dtype)
+            with torch.cuda.device(self.device):
+                code = native.library().xqt_b200_peer_allreduce_counted(
+                    self._partials[0], self._flags, self.rank, self.world, self._counter.data_ptr(), self.max_elements, rows * n, n,
+                    native.ptr(bias), out.data_ptr(), native.DTYPE_CODE[dtype], int(self.spin_limit),
+                    self._host_status.data_ptr(), native.stream_handle(self.device))
+            native.check(code, "xqt_b200_peer_allreduce_counted")
+            return out
         if torch.cuda.is_current_stream_capturing():
             # the call number is a host-side counter passed by value: a replayed graph would repeat it,
             # its wait would pass at once and it would sum partials that are still being written
-            raise XQTBackendError("PeerAllReduce.reduce cannot be captured into a CUDA graph")
+            raise XQTBackendError("PeerAllReduce.reduce with a host call number cannot be captured into a CUDA graph (build it with counted=True)")
         self.check()
         self._call += 1
         if out is None:
