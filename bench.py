@@ -10,7 +10,8 @@ of the 16 problems divided by the step time (the reference's "weights + aux" con
 weights are rotated through a pool larger than L2 so every launch streams from HBM.
 
 At N > 1 every layer is column-partitioned over N (rank r owns rows [r N/g, (r+1) N/g)), x is
-replicated, and the output slices are concatenated by an NCCL all-gather: strong scaling.
+replicated, and the output slices are concatenated by a peer-memory all-gather kernel inside the step's
+CUDA graph (NCCL all-gather as the fall-back): strong scaling.
 
 `--impl reference` times the CPU restatement of the reference's own path for the same sweep on
 the host cores (rank 0 only).  It is the only mode that executes anything under oracle/, besides
@@ -276,25 +277,38 @@ def run_gpu_arm(args) -> None:
         dev_inputs[key] = x_dev_all[off:off + x.numel()].view(x.shape)
         off += x.numel()
     x_dev_all.copy_(x_host_all)
+    # Every problem's local output [m, n/world] is a slice of one packed buffer.  With more than one rank the packed
+    # buffers of a step are concatenated (column-parallel layers) by our peer-memory all-gather kernel, launched inside
+    # the step's CUDA graph: the decode kernels write into the gatherer's two-slot buffer, picking the slot on the device
+    # (XQT_B200_PEER_GATHER=0, or no symmetric memory: one NCCL all-gather per step, outside the graph).
+    sizes = {(n, m): m * (n // world) for _, n in SHAPES for m in MS}
+    total = sum(sizes.values())
+    gatherer, out_select = None, None
+    if world > 1 and os.environ.get("XQT_B200_PEER_GATHER", "1") not in {"0", ""}:
+        try:
+            from xqt_b200.parallel import PeerAllGather
+
+            gatherer = PeerAllGather(device, total * 2)
+            out_select = gatherer.out_select
+        except Exception as exc:  # noqa: BLE001 - symmetric memory unavailable: NCCL
+            _log(f"peer all-gather unavailable ({exc}); NCCL all-gather")
+            gatherer = None
+    packed = gatherer.slot0.view(torch.bfloat16)[:total] if gatherer is not None else torch.empty(total, device=device, dtype=torch.bfloat16)
+    outputs, off = {}, 0
+    for key, count in sizes.items():
+        outputs[key] = packed[off:off + count].view(key[1], key[0] // world)
+        off += count
+    packed_all = torch.empty((world, total), device=device, dtype=torch.bfloat16) if world > 1 else None
     # hot-callables bound once per (pool copy, layer, M): the per-call host work is one C-ABI call
     bound = {}
     for copy in range(pool):
         for (k, n) in SHAPES:
             for m in MS:
-                bound[(copy, k, n, m)] = bind_w4a16_decode(dev_layers[copy][(k, n)], rows=m, dtype=torch.bfloat16)
-    # Every problem's local output [m, n/world] is a slice of one packed buffer; with more than one
-    # rank the packed buffer of a step is gathered with one NCCL all-gather (column-parallel layers).
-    sizes = {(n, m): m * (n // world) for _, n in SHAPES for m in MS}
-    packed = torch.empty(sum(sizes.values()), device=device, dtype=torch.bfloat16)
-    outputs, off = {}, 0
-    for key, count in sizes.items():
-        outputs[key] = packed[off:off + count].view(key[1], key[0] // world)
-        off += count
-    packed_all = torch.empty((world, packed.numel()), device=device, dtype=torch.bfloat16) if world > 1 else None
+                bound[(copy, k, n, m)] = bind_w4a16_decode(dev_layers[copy][(k, n)], rows=m, dtype=torch.bfloat16, out_select=out_select)
     launches = 0
 
     def gather_step():
-        if world > 1:
+        if world > 1 and gatherer is None:
             dist.all_gather_into_tensor(packed_all.view(-1), packed)
 
     def one_problem(copy, k, n, m, x):
@@ -308,6 +322,8 @@ def run_gpu_arm(args) -> None:
         for (k, n) in SHAPES:
             for m in MS:
                 one_problem(copy, k, n, m, dev_inputs[(k, m)])
+        if gatherer is not None:
+            gatherer.gather(packed_all, total * 2)          # inside the graph: the step is one replay
 
     # the launch-bound local part of a step (16 kernels of a few microseconds) is captured in CUDA
     # graphs, one per pool copy; the timed region replays them.  Collectives stay outside the graphs.
@@ -325,7 +341,7 @@ def run_gpu_arm(args) -> None:
             graphs.append(graph)
     torch.cuda.synchronize()
     _log("graphs captured")
-    launches_per_step = len(SHAPES) * len(MS)
+    launches_per_step = len(SHAPES) * len(MS) + (1 if gatherer is not None else 0)      # + the all-gather kernel
 
     def step(i):
         nonlocal launches
@@ -438,7 +454,7 @@ def run_gpu_arm(args) -> None:
         "dtype": "bf16", "data": "synthetic",
         "config": {
             "workload": "w4a16_decode_gemv_sweep", "shapes_kn": SHAPES, "m": MS, "group_size": GROUP,
-            "weight_scheme": "uint4 RTN, bf16 scale+zero", "parallelism": "single" if world == 1 else f"column-parallel x{world}, one NCCL all-gather of the step's outputs per step",
+            "weight_scheme": "uint4 RTN, bf16 scale+zero", "parallelism": "single" if world == 1 else f"column-parallel x{world}, " + ("one peer-memory all-gather kernel (NVLink peer loads, %d bytes per rank) inside the step's CUDA graph" % (total * 2) if gatherer is not None else "one NCCL all-gather of the step's outputs per step"),
             "l2": f"weights rotated through a pool of {pool} copies ({pool * bytes_per_copy / 1e6:.0f} MB > 126 MB L2)",
         },
         "roofline": {

@@ -388,6 +388,16 @@ int xqt_b200_peer_allreduce_counted(const void* const* partials, void* const* fl
                                     const float* bias, void* output, int out_dtype,
                                     unsigned int spin_limit, unsigned int* status, xqt_b200_stream_t stream);
 
+/* Concatenation step of column-parallel layers over NVLink peer memory, counted (graph-safe) like
+ * xqt_b200_peer_allreduce_counted: sources[r] is slot 0 of rank r's two-slot byte buffer (the slots slot_stride_bytes
+ * apart), into whose slot (counter + 1) & 1 rank r's kernels wrote `bytes` bytes (xqt_b200_w4a16_decode_lanes_select with
+ * the same counter word); output [world][bytes] receives every rank's bytes in rank order (plain 16-byte peer loads).
+ * bytes and slot_stride_bytes multiples of 16; same bounded wait and status as the reduction. */
+int xqt_b200_peer_allgather_counted(const void* const* sources, void* const* flags, int rank, int world,
+                                    unsigned int* counter, long long slot_stride_bytes, long long bytes,
+                                    void* output, unsigned int spin_limit, unsigned int* status,
+                                    xqt_b200_stream_t stream);
+
 /* SwiGLU gating between the projections of an MLP: output[m, i] = silu(gate_up[m, i]) * gate_up[m, inter + i],
  * evaluated in fp32 and rounded once.  gate_up is [M, 2*inter] (the gate and up projections fused
  * horizontally into one linear), output [M, inter].  Replaces xqt_convrot_w8a8_sm89_fused_swiglu

@@ -97,6 +97,44 @@ for step in range(4):
     gathered = [torch.empty_like(a) for _ in range(world)]
     dist.all_gather(gathered, a)
     assert all(torch.equal(g, gathered[0]) for g in gathered)
+# peer-memory all-gather (counted form) of bytes written through a device-selected slot, eagerly and from a graph
+from xqt_b200.parallel import PeerAllGather
+from xqt_b200.ops.w4a16 import bind_w4a16_decode, prepare_decode
+rows, n_local = 4, 512
+gatherer = PeerAllGather(dev, rows * n_local * 2)
+layer = mk(n_local, 1024, 50 + rank)
+tiled = prepare_decode(layer.qweight.to(dev), layer.scales.to(dev), layer.zero_points.to(dev), group_size=128, nibble_signed=False)
+run = bind_w4a16_decode(tiled, rows=rows, dtype=torch.bfloat16, out_select=gatherer.out_select)
+plain = bind_w4a16_decode(tiled, rows=rows, dtype=torch.bfloat16)
+local = gatherer.slot0.view(torch.bfloat16)[: rows * n_local].view(rows, n_local)
+everything = torch.empty((world, rows, n_local), device=dev, dtype=torch.bfloat16)
+def gathered_step(x):
+    run(x, local)
+    gatherer.gather(everything, rows * n_local * 2)
+xs = [torch.randn((rows, 1024), generator=seeded(300 + i)).to(torch.bfloat16).to(dev) for i in range(6)]
+static_x = xs[0].clone()
+for i in range(3):
+    gathered_step(xs[i])
+    want = [torch.empty((rows, n_local), device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    dist.all_gather(want, plain(xs[i]))
+    torch.cuda.synchronize()
+    gatherer.check()
+    assert all(torch.equal(everything[r], want[r]) for r in range(world)), ("gather", i)
+side = torch.cuda.Stream(dev)
+side.wait_stream(torch.cuda.current_stream(dev))
+with torch.cuda.stream(side):
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        gathered_step(static_x)
+torch.cuda.current_stream(dev).wait_stream(side)
+for i in range(3, 6):
+    static_x.copy_(xs[i])
+    graph.replay()
+    want = [torch.empty((rows, n_local), device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    dist.all_gather(want, plain(xs[i]))
+    torch.cuda.synchronize()
+    gatherer.check()
+    assert all(torch.equal(everything[r], want[r]) for r in range(world)), ("gather graph", i)
 dist.destroy_process_group()
 '''
 

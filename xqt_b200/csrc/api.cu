@@ -53,6 +53,8 @@ int w4a4_dense_launch(const void*, const float*, const void*, const float*, cons
 int lowrank_down_tc_launch(const void*, const void*, float*, int, int, int, unsigned int*, cudaStream_t);
 int peer_allreduce_launch(const void* const*, void* const*, int, int, unsigned int, long long, int, const float*, void*, int,
                           unsigned int, unsigned int*, unsigned int*, long long, cudaStream_t);
+int peer_allgather_launch(const void* const*, void* const*, int, int, unsigned int*, long long, long long, void*, unsigned int,
+                          unsigned int*, cudaStream_t);
 int w4a16_decode_static_status(unsigned int*, cudaStream_t);
 int quant_per_tensor_launch(const void*, void*, float*, float*, int, int, int, float, cudaStream_t);
 }  // namespace xqt_b200
@@ -382,6 +384,13 @@ int xqt_b200_peer_allreduce_counted(const void* const* partials, void* const* fl
   XQT_REQUIRE(status != nullptr && counter != nullptr);
   return peer_allreduce_launch(partials, flags, rank, world, 0u, count, n, bias, output, out_dtype, spin_limit, status,
                                counter, slot_stride, (cudaStream_t)stream);
+}
+
+int xqt_b200_peer_allgather_counted(const void* const* sources, void* const* flags, int rank, int world,
+                                    unsigned int* counter, long long slot_stride_bytes, long long bytes, void* output,
+                                    unsigned int spin_limit, unsigned int* status, xqt_b200_stream_t stream) {
+  return peer_allgather_launch(sources, flags, rank, world, counter, slot_stride_bytes, bytes, output, spin_limit, status,
+                               (cudaStream_t)stream);
 }
 
 int xqt_b200_swiglu(const void* gate_up, void* output, int m, int inter, int dtype, xqt_b200_stream_t stream) {

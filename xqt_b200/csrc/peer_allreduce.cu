@@ -120,6 +120,77 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerReducePar
 
 // counter == nullptr: `call` is this call's number and partials[r] the slot in use; else the counted form: partials[r]
 // is slot 0 of rank r's two-slot buffer, the slots slot_stride elements apart, and `call` is ignored
+// All-gather over peer memory, counted form only: after the same hand-shake every rank copies slot (call & 1) of every
+// rank's buffer (its own included) into out[r * vecs ...] with 16-byte peer loads.  The concatenation step of
+// column-parallel layers whose outputs the ranks wrote into their own two-slot buffers (decode kernels with out_select).
+struct PeerGatherParams {
+  const uint4* source[par::kMaxWorld];    // slot 0 of rank r's buffer (peer pointers)
+  unsigned int* flags[par::kMaxWorld];
+  int rank, world;
+  long long vecs;                         // 16-byte pieces per rank
+  long long slot_stride;                  // 16-byte pieces between the two slots
+  uint4* out;                             // [world][vecs]
+  unsigned int* status;
+  unsigned int spin_limit;
+  unsigned int* counter;                  // [0] finished calls, [1] block tickets
+};
+
+__global__ void __launch_bounds__(256) peer_allgather_kernel(const PeerGatherParams p) {
+  using namespace par;
+  const unsigned int call = *reinterpret_cast<volatile unsigned int*>(p.counter) + 1u;
+  const long long slot_off = (call & 1u) ? p.slot_stride : 0;
+  if (blockIdx.x == 0 && threadIdx.x < p.world && (int)threadIdx.x != p.rank)
+    st_release_sys(p.flags[threadIdx.x] + p.rank, call);
+  if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
+    const unsigned int* f = p.flags[p.rank] + threadIdx.x;
+    unsigned int spins = 0;
+    while ((int)(ld_acquire_sys(f) - call) < 0) {
+      if (++spins >= p.spin_limit) {
+        st_release_sys(p.status, (unsigned int)kTimeout);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const long long total = p.vecs * p.world;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / p.vecs);
+    const long long v = i - (long long)r * p.vecs;
+    p.out[i] = __ldcg(p.source[r] + slot_off + v);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.counter + 1, 1u) == gridDim.x - 1) {
+      p.counter[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(p.counter) = call;
+    }
+  }
+}
+
+int peer_allgather_launch(const void* const* sources, void* const* flags, int rank, int world, unsigned int* counter,
+                          long long slot_stride_bytes, long long bytes, void* out, unsigned int spin_limit,
+                          unsigned int* status, cudaStream_t stream) {
+  using namespace par;
+  XQT_REQUIRE(world >= 2 && world <= kMaxWorld && rank >= 0 && rank < world && counter != nullptr);
+  XQT_REQUIRE(bytes > 0 && bytes % 16 == 0 && slot_stride_bytes >= bytes && slot_stride_bytes % 16 == 0);
+  XQT_REQUIRE(sources != nullptr && flags != nullptr && out != nullptr && status != nullptr && ((uintptr_t)out & 15) == 0);
+  PeerGatherParams p{};
+  for (int r = 0; r < world; ++r) {
+    XQT_REQUIRE(sources[r] != nullptr && flags[r] != nullptr && ((uintptr_t)sources[r] & 15) == 0);
+    p.source[r] = reinterpret_cast<const uint4*>(sources[r]);
+    p.flags[r] = reinterpret_cast<unsigned int*>(flags[r]);
+  }
+  p.rank = rank; p.world = world; p.vecs = bytes / 16; p.slot_stride = slot_stride_bytes / 16;
+  p.out = reinterpret_cast<uint4*>(out); p.status = status; p.counter = counter;
+  p.spin_limit = spin_limit == 0 ? kSpin : spin_limit;
+  long long blocks = (p.vecs * world + 255) / 256;
+  if (blocks > 148) blocks = 148;
+  peer_allgather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
+  return launch_status();
+}
+
 int peer_allreduce_launch(const void* const* partials, void* const* flags, int rank, int world, unsigned int call,
                           long long count, int n, const float* bias, void* out, int out_dtype, unsigned int spin_limit,
                           unsigned int* status, unsigned int* counter, long long slot_stride, cudaStream_t stream) {

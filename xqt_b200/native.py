@@ -69,6 +69,7 @@ SIGNATURES: dict[str, tuple] = {
     "xqt_b200_w4a4_dense": (_I, [_P] * 8 + [_I] * 4 + [_P, _Z, _P]),
     "xqt_b200_lowrank_down_tc": (_I, [_P] * 3 + [_I] * 3 + [_P, _Z, _P]),
     "xqt_b200_peer_allreduce": (_I, [_P, _P, _I, _I, ctypes.c_uint, ctypes.c_longlong, _I, _P, _P, _I, ctypes.c_uint, _P, _P]),
+    "xqt_b200_peer_allgather_counted": (_I, [_P, _P, _I, _I, _P, ctypes.c_longlong, ctypes.c_longlong, _P, ctypes.c_uint, _P, _P]),
     "xqt_b200_peer_allreduce_counted": (_I, [_P, _P, _I, _I, _P, ctypes.c_longlong, ctypes.c_longlong, _I, _P, _P, _I, ctypes.c_uint, _P, _P]),
     "xqt_b200_w4a16_decode_static_status": (_I, [ctypes.POINTER(ctypes.c_uint), _P]),
     "xqt_b200_swiglu": (_I, [_P, _P, _I, _I, _I, _P]),

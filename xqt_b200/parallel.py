@@ -234,4 +234,75 @@ class PeerAllReduce:
                                   "the affected outputs are not valid")
 
 
-__all__ = ["ColumnParallelLinear", "PeerAllReduce", "RowParallelLinear", "shard_packed_weight"]
+class PeerAllGather:
+    """Concatenation of the ranks' output bytes over NVLink peer memory, graph-safe (the counted form of
+    :class:`PeerAllReduce`: the call number lives in device memory).
+
+    Every rank's kernels write their ``nbytes`` of output into ``slot0`` stepped by ``out_select`` (the decode kernel
+    selects the slot of this two-slot buffer on the device); ``gather(out)`` launches the kernel that signals the
+    peers, waits for them (bounded) and copies every rank's slot into ``out[rank]``.  All launches have fixed
+    arguments, so a step of local kernels followed by ``gather`` can be captured into one CUDA graph; every rank must
+    make the same sequence of calls."""
+
+    def __init__(self, device: torch.device, nbytes: int, group=None) -> None:
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import native
+
+        group = dist.group.WORLD if group is None else group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if not 2 <= self.world <= PeerAllReduce.MAX_WORLD:
+            raise XQTBackendError(f"PeerAllGather serves 2..{PeerAllReduce.MAX_WORLD} ranks")
+        self.device, self.nbytes = device, int(-(-int(nbytes) // 256) * 256)
+        self._buffer = symm_mem.empty(2 * self.nbytes + 256, dtype=torch.uint8, device=device)
+        self._buffer.zero_()
+        handle = symm_mem.rendezvous(self._buffer, group)
+        self._handle = handle
+        base = [int(ptr) for ptr in handle.buffer_ptrs]
+        array = ctypes.c_void_p * self.world
+        self._sources = array(*base)
+        self._flags = array(*[b + 2 * self.nbytes for b in base])
+        self._counter = torch.zeros(4, dtype=torch.int32, device=device)
+        self._host_status = torch.zeros(16, dtype=torch.int32).pin_memory()
+        self._native = native
+        self.spin_limit = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    @property
+    def slot0(self) -> torch.Tensor:
+        """This rank's slot 0 as uint8 ``[nbytes]``: the address the writing kernels are given (with ``out_select``)."""
+
+        return self._buffer[: self.nbytes]
+
+    @property
+    def out_select(self) -> tuple[int, int]:
+        return self._counter.data_ptr(), self.nbytes
+
+    def gather(self, out: torch.Tensor, nbytes: int | None = None) -> torch.Tensor:
+        """``out`` (contiguous, ``world * nbytes`` bytes): rank r's bytes at ``[r * nbytes, (r + 1) * nbytes)``."""
+
+        native = self._native
+        count = self.nbytes if nbytes is None else int(nbytes)
+        if count % 16 or count > self.nbytes or out.numel() * out.element_size() != self.world * count or not out.is_contiguous():
+            raise XQTBackendError("PeerAllGather: out must hold world * nbytes contiguous bytes, nbytes a multiple of 16")
+        if not torch.cuda.is_current_stream_capturing():
+            self.check()
+        with torch.cuda.device(self.device):
+            code = native.library().xqt_b200_peer_allgather_counted(
+                self._sources, self._flags, self.rank, self.world, self._counter.data_ptr(), self.nbytes, count, out.data_ptr(),
+                int(self.spin_limit), self._host_status.data_ptr(), native.stream_handle(self.device))
+        native.check(code, "xqt_b200_peer_allgather_counted")
+        return out
+
+    def check(self) -> None:
+        if int(self._host_status[0]) != 0:
+            code = int(self._host_status[0])
+            self._host_status.zero_()
+            raise XQTBackendError(f"PeerAllGather: a rank did not signal within the wait bound (status {code}); "
+                                  "the gathered outputs are not valid")
+
+
+__all__ = ["ColumnParallelLinear", "PeerAllGather", "PeerAllReduce", "RowParallelLinear", "shard_packed_weight"]
