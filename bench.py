@@ -339,6 +339,15 @@ def run_gpu_arm(args) -> None:
             with torch.cuda.graph(graph, stream=side):
                 local_step(i)
             graphs.append(graph)
+        # `pool` consecutive steps (one per weight copy) as ONE graph, for runs of steps: a replay's start-up cost and the
+        # lost overlap between the last kernel of one graph and the first of the next are then paid once per `pool`
+        # steps.  Only where a step is all kernels (one rank, or the peer-memory all-gather inside the graph).
+        run_graph = None
+        if world == 1 or gatherer is not None:
+            run_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(run_graph, stream=side):
+                for i in range(pool):
+                    local_step(i)
     torch.cuda.synchronize()
     _log("graphs captured")
     launches_per_step = len(SHAPES) * len(MS) + (1 if gatherer is not None else 0)      # + the all-gather kernel
@@ -349,6 +358,18 @@ def run_gpu_arm(args) -> None:
         gather_step()
         launches += launches_per_step
 
+    def run_steps(count):
+        """`count` steps: whole rounds over the weight copies from the multi-step graph, the rest step by step."""
+        nonlocal launches
+        done = 0
+        if run_graph is not None:
+            for _ in range(count // pool):
+                run_graph.replay()
+            done = (count // pool) * pool
+            launches += done * launches_per_step
+        for i in range(done, count):
+            step(i)
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -356,6 +377,7 @@ def run_gpu_arm(args) -> None:
 
     for i in range(max(args.warmup, 3)):
         step(i)
+    run_steps(pool)
     barrier()
     launches = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -363,8 +385,7 @@ def run_gpu_arm(args) -> None:
     with sampler:
         barrier()
         e0.record()
-        for i in range(args.steps):
-            step(i)
+        run_steps(args.steps)
         e1.record()
         barrier()
         ms_total = e0.elapsed_time(e1)
@@ -456,6 +477,8 @@ def run_gpu_arm(args) -> None:
             "workload": "w4a16_decode_gemv_sweep", "shapes_kn": SHAPES, "m": MS, "group_size": GROUP,
             "weight_scheme": "uint4 RTN, bf16 scale+zero", "parallelism": "single" if world == 1 else f"column-parallel x{world}, " + ("one peer-memory all-gather kernel (NVLink peer loads, %d bytes per rank) inside the step's CUDA graph" % (total * 2) if gatherer is not None else "one NCCL all-gather of the step's outputs per step"),
             "l2": f"weights rotated through a pool of {pool} copies ({pool * bytes_per_copy / 1e6:.0f} MB > 126 MB L2)",
+            "launch": (f"CUDA-graph replay: runs of {pool} steps (one per weight copy) are one graph, the remaining steps one graph each"
+                       if run_graph is not None else "CUDA-graph replay, one graph per step"),
         },
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
