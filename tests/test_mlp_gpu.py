@@ -241,7 +241,7 @@ def test_mlp_block_as_cuda_graph_matches_eager_calls():
     assert native.workspace_status(dev) == 0
 
 
-@pytest.mark.parametrize("m", [1, 16, 40])
+@pytest.mark.parametrize("m", [1, 16, 24])
 def test_fused_swiglu_decode_epilogue_has_the_bits_of_the_unfused_form(m, monkeypatch):
     """gate/up + SwiGLU as one decode launch (interleaved tiles, gating in the kernel's epilogue) against the same
     block built with the fusion off: identical outputs."""

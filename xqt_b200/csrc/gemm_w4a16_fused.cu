@@ -39,7 +39,8 @@ namespace w4f {
 constexpr int kBM = 128, kBN = 128, kBK = 64;
 constexpr int kFirstEpiWarp = 2, kEpiWarps = 4, kFirstDqWarp = 6, kDqWarps = 8;
 constexpr int kDqGroups = 4, kDqGroupWarps = kDqWarps / kDqGroups;   // stage it is converted by warp group it % kDqGroups
-constexpr int kThreads = (kFirstDqWarp + kDqWarps) * 32;   // 448
+constexpr int kRawWarp = kFirstDqWarp + kDqWarps;          // producer of the packed-weight ring (a warp of its own)
+constexpr int kThreads = (kRawWarp + 1) * 32;              // 480
 constexpr int kMaxStages = 6, kMaxRaw = 8;
 constexpr int kABlockBytes = kBM * 128, kBBytes = kBN * 128;
 constexpr int kRawBytes = kBN * (kBK / 2);                  // 4 KiB of packed nibbles per stage
@@ -185,37 +186,44 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
       atomicExch(p.status, (unsigned int)kTimeout);
     }
   };
+  auto guarded_wait2 = [&](uint32_t b0, uint32_t parity0, uint32_t b1, uint32_t parity1) {
+    if (s_abort == 0u && !mbar_wait2(b0, parity0, b1, parity1)) {
+      s_abort = 1u;
+      atomicExch(p.status, (unsigned int)kTimeout);
+    }
+  };
 
   if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer: packed weights and activation blocks
-    // One thread feeds both rings in order: the packed-weight tile of step j, then the activation blocks of step
-    // j - lead (the weight ring is deeper by `lead`, so the weights run ahead of the conversion).
+    // ---------------------------------------------------------------- TMA producer of the activation blocks
     if (elect_one()) {
-      const int lead = nr - ns;
-      const uint32_t raw_addr = smem_addr(raw_base);
-      uint32_t rit = 0, it = 0;
-      int rtile = blockIdx.x, rkb = 0, atile = blockIdx.x, akb = 0;
-      while (atile < total_tiles) {
-        if (rtile < total_tiles) {
-          const W4FTile rt = w4f_tile(p, rtile);
-          const int r = rit % nr;
-          guarded_wait(bar(kBarRawEmpty + r), ((rit / nr) & 1) ^ 1);
-          mbar_expect_tx(bar(kBarRawFull + r), kRawBytes);
-          tma_load_2d(raw_addr + (uint32_t)r * kRawBytes, &tm_w, (rt.kb0 + rkb) * (kBK / 2), rt.nt * kBN, bar(kBarRawFull + r));
-          ++rit;
-          if (++rkb == rt.kbn) { rkb = 0; rtile += gridDim.x; }
-        }
-        if ((int)rit > lead + (int)it || rtile >= total_tiles) {
-          const W4FTile t = w4f_tile(p, atile);
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const W4FTile t = w4f_tile(p, tile);
+        for (int kb = 0; kb < t.kbn; ++kb, ++it) {
           const int s = it % ns;
           guarded_wait(bar(kBarEmpty + s), ((it / ns) & 1) ^ 1);
           unsigned char* st = tiles + (size_t)s * kStageBytes;
           mbar_expect_tx(bar(kBarFull + s), kABytes);
 #pragma unroll
           for (int mb = 0; mb < MT; ++mb)      // a block past the last token row is filled with zeros
-            tma_load_2d(smem_addr(st + mb * kABlockBytes), &tm_a, (t.kb0 + akb) * kBK, (t.mc * MT + mb) * kBM, bar(kBarFull + s));
-          ++it;
-          if (++akb == t.kbn) { akb = 0; atile += gridDim.x; }
+            tma_load_2d(smem_addr(st + mb * kABlockBytes), &tm_a, (t.kb0 + kb) * kBK, (t.mc * MT + mb) * kBM, bar(kBarFull + s));
+        }
+      }
+    }
+  } else if (warp == kRawWarp) {
+    // ---------------------------------------------------------------- TMA producer of the packed weights
+    // A warp of its own: the weight ring runs as far ahead of the conversion as it has slots, whatever the activation
+    // ring is waiting for (one thread feeding both rings in order tied the weights of step j to the stage of step j - 2).
+    if (elect_one()) {
+      const uint32_t raw_addr = smem_addr(raw_base);
+      uint32_t rit = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const W4FTile t = w4f_tile(p, tile);
+        for (int kb = 0; kb < t.kbn; ++kb, ++rit) {
+          const int r = rit % nr;
+          guarded_wait(bar(kBarRawEmpty + r), ((rit / nr) & 1) ^ 1);
+          mbar_expect_tx(bar(kBarRawFull + r), kRawBytes);
+          tma_load_2d(raw_addr + (uint32_t)r * kRawBytes, &tm_w, (t.kb0 + kb) * (kBK / 2), t.nt * kBN, bar(kBarRawFull + r));
         }
       }
     }
@@ -231,9 +239,11 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         tc_fence_after();
         for (int kb = 0; kb < t.kbn; ++kb, ++it) {
           const int s = it % ns;
-          if (!ready) guarded_wait(bar(kBarReady + s), (it / ns) & 1);   // weights dequantised (their writers saw the activations land)
+          // both operands of the stage: the weights dequantised (Ready) and the activation blocks landed (Full); the
+          // dequantisation warps do not wait for the activations, only for the stage to be free
+          if (!ready) guarded_wait2(bar(kBarReady + s), (it / ns) & 1, bar(kBarFull + s), (it / ns) & 1);
           // a barrier test takes about 200 cycles to answer: the next stage's travels while this stage's MMAs are issued
-          ready = mbar_try_wait(bar(kBarReady + (it + 1) % ns), ((it + 1) / ns) & 1);
+          ready = mbar_try_wait2(bar(kBarReady + (it + 1) % ns), ((it + 1) / ns) & 1, bar(kBarFull + (it + 1) % ns), ((it + 1) / ns) & 1);
           tc_fence_after();
           const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
           const uint64_t bdesc = umma_desc_sw128(a_addr + kABytes);
@@ -401,11 +411,13 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           raw[rr][0] = src[0];
           raw[rr][1] = src[1];
         }
-        if (!ahead_full) guarded_wait(bar(kBarFull + s), (it / ns) & 1);   // the stage is free again (and its activations have landed)
+        // The stage's weight half is free once the MMAs of its previous use have completed (Empty).  Waiting for the
+        // activation blocks instead (Full) put a TMA round trip, issued only after Empty, on every stage's critical path.
+        if (!ahead_full) guarded_wait(bar(kBarEmpty + s), ((it / ns) & 1) ^ 1);
         // this group's next stage: its two barriers are tested while this stage is converted
         const uint32_t nx = it + kDqGroups;
         ahead_raw = mbar_try_wait(bar(kBarRawFull + nx % nr), (nx / nr) & 1);
-        ahead_full = mbar_try_wait(bar(kBarFull + nx % ns), (nx / ns) & 1);
+        ahead_full = mbar_try_wait(bar(kBarEmpty + nx % ns), ((nx / ns) & 1) ^ 1);
         unsigned char* bt = tiles + (size_t)s * kStageBytes + kABytes;
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
@@ -438,11 +450,14 @@ bool w4a16_gemm_fused_supported(int m, int n, int k, int padded_k, int group_siz
   return m >= 1 && n % 8 == 0 && k == padded_k && k % 64 == 0 && (group_size == 64 || group_size == 128);
 }
 
-// Measured on B200 (bf16, group 128): with few channel tiles (N = 4096: 32 tiles, split over K) the fused kernel
-// beats the two-pass form up to M = 128 (K = 14336: 76 us against 131 us at M = 64); with hundreds of tiles
-// (N = 28672) the two are level at M <= 128 (134 / 125 us) and the two-pass form is ahead from M = 256.
+// Measured on B200 (bf16, group 128), fused against two-pass: N = 4096, K = 14336 (32 channel tiles, split over K):
+// 48 / 51 / 55 / 115 / 201 us against 121 / 121 / 122 / 125 / 129 us at M = 32 / 64 / 128 / 256 / 512; N = 28672, K = 4096
+// (224 tiles): 74 / 74 / 77 / 191 / 360 us against 110 / 110 / 111 / 130 / 175 us.  So: one token block (M <= 128) always;
+// two blocks (M <= 256) where the channel tiles do not fill the SMs; beyond that the weights would be converted once per
+// 256-token chunk and the two-pass form wins.
 bool w4a16_gemm_fused_preferred(int m, int n, int k, int padded_k, int group_size) {
-  if (!w4a16_gemm_fused_supported(m, n, k, padded_k, group_size) || m <= 16 || m > w4f::kBM) return false;
+  if (!w4a16_gemm_fused_supported(m, n, k, padded_k, group_size) || m <= 16 || m > 2 * w4f::kBM) return false;
+  if (m <= w4f::kBM) return true;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   return ceil_div(n, w4f::kBN) * 2 <= sms;

@@ -58,7 +58,7 @@ def _concat_rows(a: PackedWeight, b: PackedWeight) -> PackedWeight:
         metadata=PackedWeightMetadata(**values))
 
 
-CHUNKED_DECODE_MAX_ROWS = 48
+CHUNKED_DECODE_MAX_ROWS = 32
 
 
 class _Linear:
@@ -116,7 +116,7 @@ class _Linear:
         if m <= CHUNKED_DECODE_MAX_ROWS and self.tiled.layout == "lanes":
             # a few decode passes over 16-row chunks: the packed weights of a layer (tens of MB) stay in the 126 MB
             # L2 between passes, and each pass runs at the decode kernel's rate -- measured ahead of the GEMM forms
-            # up to three passes
+            # up to two passes (from 33 rows the fused tcgen05 GEMM is ahead)
             if out is None:
                 out = torch.empty((m, self.n), device=x.device, dtype=odt)
             for r0 in range(0, m, 16):
@@ -290,7 +290,7 @@ class W4A16SwiGLUMLP:
                             None if self.gate_up.tiled is None else self.gate_up.tiled.layout, "w4a16_decode_kernel"),
                         "17<=m<=128": "gemm_w4a16_fused_kernel (where it fills the SMs) else dequant_w4_f16_kernel + gemm_f16_kernel",
                         "m>128": "dequant_w4_f16_kernel + gemm_f16_kernel",
-                        "gating": "w4a16_decode_cl_kernel epilogue (m <= 48) / swiglu_kernel" if getattr(self.gate_up, "glu", False) else "swiglu_kernel"},
+                        "gating": "w4a16_decode_cl_kernel epilogue (m <= 32) / swiglu_kernel" if getattr(self.gate_up, "glu", False) else "swiglu_kernel"},
         }
 
 
