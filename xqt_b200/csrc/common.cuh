@@ -67,6 +67,17 @@ __device__ __forceinline__ float load_param(const void* base, int dtype, size_t 
   return __half2float(reinterpret_cast<const __half*>(base)[i]);
 }
 
+// The same in two steps, so that a prefetch does not wait for its own data: the raw bits now, the value when needed.
+__device__ __forceinline__ uint32_t load_param_bits(const void* base, int dtype, size_t i) {
+  if (dtype == XQT_B200_FP32) return reinterpret_cast<const uint32_t*>(base)[i];
+  return reinterpret_cast<const unsigned short*>(base)[i];
+}
+__device__ __forceinline__ float param_from_bits(uint32_t bits, int dtype) {
+  if (dtype == XQT_B200_FP32) return __uint_as_float(bits);
+  if (dtype == XQT_B200_BF16) return __uint_as_float(bits << 16);
+  return __half2float(__ushort_as_half((unsigned short)bits));
+}
+
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + __expf(-v)); }
 
 }  // namespace xqt_b200

@@ -242,8 +242,6 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           // both operands of the stage: the weights dequantised (Ready) and the activation blocks landed (Full); the
           // dequantisation warps do not wait for the activations, only for the stage to be free
           if (!ready) guarded_wait2(bar(kBarReady + s), (it / ns) & 1, bar(kBarFull + s), (it / ns) & 1);
-          // a barrier test takes about 200 cycles to answer: the next stage's travels while this stage's MMAs are issued
-          ready = mbar_try_wait2(bar(kBarReady + (it + 1) % ns), ((it + 1) / ns) & 1, bar(kBarFull + (it + 1) % ns), ((it + 1) / ns) & 1);
           tc_fence_after();
           const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
           const uint64_t bdesc = umma_desc_sw128(a_addr + kABytes);
@@ -255,6 +253,9 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             for (int q = 0; q < 4; ++q) umma_ss<false>(d_tmem, adesc + 2 * q, bdesc + 2 * q, kIdesc, (kb != 0 || q != 0) ? 1u : 0u);
           }
           umma_commit(bar(kBarEmpty + s));
+          // the next stage's barriers, tested without blocking after this stage's MMAs are on their way
+          ready = mbar_test_wait(bar(kBarReady + (it + 1) % ns), ((it + 1) / ns) & 1) &&
+                  mbar_test_wait(bar(kBarFull + (it + 1) % ns), ((it + 1) / ns) & 1);
         }
         umma_commit(bar(kBarTileFull + buf));
       }
@@ -375,33 +376,35 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
       }
       // scale and zero point of this group's next stage, requested one of its stages (four K blocks) ahead: they come
       // from L2 or DRAM, and a stage converted by this group has no other load to hide them behind
-      float nsc[2] = {0.f, 0.f}, nzp[2] = {0.f, 0.f};
+      // (as raw bits: converting them here would make the prefetch wait for its own loads, an L2 round trip per stage)
+      uint32_t nsc[2] = {0u, 0u}, nzp[2] = {0u, 0u};
       bool have_next = false;
-      auto fetch_params = [&](int kb, float (&sc)[2], float (&zp)[2]) {
+      auto fetch_params = [&](int kb, uint32_t (&sc)[2], uint32_t (&zp)[2]) {
         const int g = ((t.kb0 + kb) * kBK) / p.group_size;
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
-          sc[rr] = load_param(p.scales, p.param_dtype, prow[rr] + g);
-          zp[rr] = p.zeros != nullptr ? load_param(p.zeros, p.param_dtype, prow[rr] + g) : 0.f;
+          sc[rr] = load_param_bits(p.scales, p.param_dtype, prow[rr] + g);
+          zp[rr] = p.zeros != nullptr ? load_param_bits(p.zeros, p.param_dtype, prow[rr] + g) : 0u;
         }
       };
       for (int kb = 0; kb < t.kbn; ++kb, ++it) {
         if ((int)(it % kDqGroups) != grp) continue;
         const int s = it % ns, r = it % nr;
-        float sc[2], zp[2];
+        uint32_t scb[2], zpb[2];
         if (have_next) {
 #pragma unroll
-          for (int rr = 0; rr < 2; ++rr) { sc[rr] = nsc[rr]; zp[rr] = nzp[rr]; }
+          for (int rr = 0; rr < 2; ++rr) { scb[rr] = nsc[rr]; zpb[rr] = nzp[rr]; }
         } else {
-          fetch_params(kb, sc, zp);
+          fetch_params(kb, scb, zpb);
         }
         have_next = kb + kDqGroups < t.kbn;
         if (have_next) fetch_params(kb + kDqGroups, nsc, nzp);
         __half2 off2[2], scale2[2];
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
-          off2[rr] = __float2half2_rn(zbase + zp[rr]);
-          scale2[rr] = __float2half2_rn(sc[rr]);
+          const float zp = p.zeros != nullptr ? param_from_bits(zpb[rr], p.param_dtype) : 0.f;
+          off2[rr] = __float2half2_rn(zbase + zp);
+          scale2[rr] = __float2half2_rn(param_from_bits(scb[rr], p.param_dtype));
         }
         if (!ahead_raw) guarded_wait(bar(kBarRawFull + r), (it / nr) & 1);
         uint4 raw[2][2];
@@ -416,8 +419,8 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         if (!ahead_full) guarded_wait(bar(kBarEmpty + s), ((it / ns) & 1) ^ 1);
         // this group's next stage: its two barriers are tested while this stage is converted
         const uint32_t nx = it + kDqGroups;
-        ahead_raw = mbar_try_wait(bar(kBarRawFull + nx % nr), (nx / nr) & 1);
-        ahead_full = mbar_try_wait(bar(kBarEmpty + nx % ns), ((nx / ns) & 1) ^ 1);
+        ahead_raw = mbar_test_wait(bar(kBarRawFull + nx % nr), (nx / nr) & 1);      // non-blocking: "not yet" is a normal answer
+        ahead_full = mbar_test_wait(bar(kBarEmpty + nx % ns), ((nx / ns) & 1) ^ 1);
         unsigned char* bt = tiles + (size_t)s * kStageBytes + kABytes;
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {

@@ -51,6 +51,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test.  try_wait may suspend the thread for a while when the phase is not complete (measured: about 800
+// cycles per unsuccessful call); a look-ahead poll that expects "not yet" as a normal answer must use this form.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // false when the attempt limit ran out
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; ++i)
