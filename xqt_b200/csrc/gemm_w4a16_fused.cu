@@ -454,16 +454,12 @@ bool w4a16_gemm_fused_supported(int m, int n, int k, int padded_k, int group_siz
 }
 
 // Measured on B200 (bf16, group 128), fused against two-pass: N = 4096, K = 14336 (32 channel tiles, split over K):
-// 48 / 51 / 55 / 115 / 201 us against 121 / 121 / 122 / 125 / 129 us at M = 32 / 64 / 128 / 256 / 512; N = 28672, K = 4096
-// (224 tiles): 74 / 74 / 77 / 191 / 360 us against 110 / 110 / 111 / 130 / 175 us.  So: one token block (M <= 128) always;
-// two blocks (M <= 256) where the channel tiles do not fill the SMs; beyond that the weights would be converted once per
-// 256-token chunk and the two-pass form wins.
+// 45 / 47 / 52 / 70 / 109 us against 122 / 122 / 122 / 125 / 128 us at M = 32 / 64 / 128 / 256 / 512; N = 28672, K = 4096
+// (224 tiles): 71 / 72 / 74 / 89 / 159 us against 110 / 110 / 111 / 129 / 172 us.  So up to 512 tokens (two 256-token
+// chunks, the weights converted once per chunk); beyond that the two-pass form, whose conversion cost does not grow
+// with M, is ahead.
 bool w4a16_gemm_fused_preferred(int m, int n, int k, int padded_k, int group_size) {
-  if (!w4a16_gemm_fused_supported(m, n, k, padded_k, group_size) || m <= 16 || m > 2 * w4f::kBM) return false;
-  if (m <= w4f::kBM) return true;
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return ceil_div(n, w4f::kBN) * 2 <= sms;
+  return w4a16_gemm_fused_supported(m, n, k, padded_k, group_size) && m > 16 && m <= 4 * w4f::kBM;
 }
 
 struct W4FusedPlan {
