@@ -127,6 +127,17 @@ __device__ __forceinline__ W4FTile w4f_tile(const W4FusedParams& p, int tile) {
   return t;
 }
 
+// Position in a ring of `n` slots that is walked in fixed steps: slot index and phase parity kept incrementally (a
+// runtime `it % n` / `it / n` pair per stage is two integer divisions on every role's critical path).
+struct W4FRing {
+  uint32_t slot, phase, n;
+  __device__ __forceinline__ W4FRing(uint32_t start, uint32_t slots) : slot(start % slots), phase((start / slots) & 1u), n(slots) {}
+  __device__ __forceinline__ void advance(uint32_t step) {
+    slot += step;
+    while (slot >= n) { slot -= n; phase ^= 1u; }
+  }
+};
+
 template <int MT, typename T>
 __global__ void __launch_bounds__(w4f::kThreads, 1)
 gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
@@ -196,12 +207,12 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer of the activation blocks
     if (elect_one()) {
-      uint32_t it = 0;
+      W4FRing st_ring(0, ns);
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const W4FTile t = w4f_tile(p, tile);
-        for (int kb = 0; kb < t.kbn; ++kb, ++it) {
-          const int s = it % ns;
-          guarded_wait(bar(kBarEmpty + s), ((it / ns) & 1) ^ 1);
+        for (int kb = 0; kb < t.kbn; ++kb, st_ring.advance(1)) {
+          const int s = st_ring.slot;
+          guarded_wait(bar(kBarEmpty + s), st_ring.phase ^ 1);
           unsigned char* st = tiles + (size_t)s * kStageBytes;
           mbar_expect_tx(bar(kBarFull + s), kABytes);
 #pragma unroll
@@ -216,12 +227,12 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     // ring is waiting for (one thread feeding both rings in order tied the weights of step j to the stage of step j - 2).
     if (elect_one()) {
       const uint32_t raw_addr = smem_addr(raw_base);
-      uint32_t rit = 0;
+      W4FRing raw_ring(0, nr);
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const W4FTile t = w4f_tile(p, tile);
-        for (int kb = 0; kb < t.kbn; ++kb, ++rit) {
-          const int r = rit % nr;
-          guarded_wait(bar(kBarRawEmpty + r), ((rit / nr) & 1) ^ 1);
+        for (int kb = 0; kb < t.kbn; ++kb, raw_ring.advance(1)) {
+          const int r = raw_ring.slot;
+          guarded_wait(bar(kBarRawEmpty + r), raw_ring.phase ^ 1);
           mbar_expect_tx(bar(kBarRawFull + r), kRawBytes);
           tma_load_2d(raw_addr + (uint32_t)r * kRawBytes, &tm_w, (t.kb0 + kb) * (kBK / 2), t.nt * kBN, bar(kBarRawFull + r));
         }
@@ -230,18 +241,19 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      uint32_t it = 0, local = 0;
+      uint32_t local = 0;
+      W4FRing cur(0, ns), nxt(1, ns);
       bool ready = false;          // the current stage's barrier has already been seen complete
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
         const W4FTile t = w4f_tile(p, tile);
         const int buf = local & 1;
         guarded_wait(bar(kBarTileEmpty + buf), ((local >> 1) & 1) ^ 1);
         tc_fence_after();
-        for (int kb = 0; kb < t.kbn; ++kb, ++it) {
-          const int s = it % ns;
+        for (int kb = 0; kb < t.kbn; ++kb, cur.advance(1), nxt.advance(1)) {
+          const int s = cur.slot;
           // both operands of the stage: the weights dequantised (Ready) and the activation blocks landed (Full); the
           // dequantisation warps do not wait for the activations, only for the stage to be free
-          if (!ready) guarded_wait2(bar(kBarReady + s), (it / ns) & 1, bar(kBarFull + s), (it / ns) & 1);
+          if (!ready) guarded_wait2(bar(kBarReady + s), cur.phase, bar(kBarFull + s), cur.phase);
           tc_fence_after();
           const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
           const uint64_t bdesc = umma_desc_sw128(a_addr + kABytes);
@@ -254,8 +266,7 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           }
           umma_commit(bar(kBarEmpty + s));
           // the next stage's barriers, tested without blocking after this stage's MMAs are on their way
-          ready = mbar_test_wait(bar(kBarReady + (it + 1) % ns), ((it + 1) / ns) & 1) &&
-                  mbar_test_wait(bar(kBarFull + (it + 1) % ns), ((it + 1) / ns) & 1);
+          ready = mbar_test_wait(bar(kBarReady + nxt.slot), nxt.phase) && mbar_test_wait(bar(kBarFull + nxt.slot), nxt.phase);
         }
         umma_commit(bar(kBarTileFull + buf));
       }
@@ -363,7 +374,11 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     const int dt = threadIdx.x - kFirstDqWarp * 32;      // 0..255
     const int grp = dt >> 6, row_a = dt & 63;            // group of two warps; the thread's rows are row_a and row_a + 64
     const float zbase = 1024.f + (p.nibble_signed ? 8.f : 0.f);
-    uint32_t it = 0;
+    // This group converts the steps it = grp, grp + 4, grp + 8, ... of the CTA's run of steps (tiles back to back):
+    // ring cursors for its current step and the one after, advanced by kDqGroups; no division in the loop.
+    uint32_t it_base = 0;                                // index of the current tile's first step
+    W4FRing st_cur(grp, ns), st_nxt(grp + kDqGroups, ns), raw_cur(grp, nr), raw_nxt(grp + kDqGroups, nr);
+    const int gshift = p.group_size == 2 * kBK ? 1 : 0;  // quantisation group = one or two 64-K steps
     bool ahead_raw = false, ahead_full = false;          // this group's next stage was already seen ready
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const W4FTile t = w4f_tile(p, tile);
@@ -380,16 +395,17 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
       uint32_t nsc[2] = {0u, 0u}, nzp[2] = {0u, 0u};
       bool have_next = false;
       auto fetch_params = [&](int kb, uint32_t (&sc)[2], uint32_t (&zp)[2]) {
-        const int g = ((t.kb0 + kb) * kBK) / p.group_size;
+        const int g = (t.kb0 + kb) >> gshift;
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
           sc[rr] = load_param_bits(p.scales, p.param_dtype, prow[rr] + g);
           zp[rr] = p.zeros != nullptr ? load_param_bits(p.zeros, p.param_dtype, prow[rr] + g) : 0u;
         }
       };
-      for (int kb = 0; kb < t.kbn; ++kb, ++it) {
-        if ((int)(it % kDqGroups) != grp) continue;
-        const int s = it % ns, r = it % nr;
+      // the tile's first step of this group: the smallest kb with (it_base + kb) % kDqGroups == grp
+      for (int kb = (grp - (int)(it_base % kDqGroups)) & (kDqGroups - 1); kb < t.kbn; kb += kDqGroups,
+               st_cur.advance(kDqGroups), st_nxt.advance(kDqGroups), raw_cur.advance(kDqGroups), raw_nxt.advance(kDqGroups)) {
+        const int s = st_cur.slot, r = raw_cur.slot;
         uint32_t scb[2], zpb[2];
         if (have_next) {
 #pragma unroll
@@ -406,7 +422,7 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           off2[rr] = __float2half2_rn(zbase + zp);
           scale2[rr] = __float2half2_rn(param_from_bits(scb[rr], p.param_dtype));
         }
-        if (!ahead_raw) guarded_wait(bar(kBarRawFull + r), (it / nr) & 1);
+        if (!ahead_raw) guarded_wait(bar(kBarRawFull + r), raw_cur.phase);
         uint4 raw[2][2];
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
@@ -416,11 +432,10 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         }
         // The stage's weight half is free once the MMAs of its previous use have completed (Empty).  Waiting for the
         // activation blocks instead (Full) put a TMA round trip, issued only after Empty, on every stage's critical path.
-        if (!ahead_full) guarded_wait(bar(kBarEmpty + s), ((it / ns) & 1) ^ 1);
+        if (!ahead_full) guarded_wait(bar(kBarEmpty + s), st_cur.phase ^ 1);
         // this group's next stage: its two barriers are tested while this stage is converted
-        const uint32_t nx = it + kDqGroups;
-        ahead_raw = mbar_test_wait(bar(kBarRawFull + nx % nr), (nx / nr) & 1);      // non-blocking: "not yet" is a normal answer
-        ahead_full = mbar_test_wait(bar(kBarEmpty + nx % ns), ((nx / ns) & 1) ^ 1);
+        ahead_raw = mbar_test_wait(bar(kBarRawFull + raw_nxt.slot), raw_nxt.phase);      // non-blocking: "not yet" is a normal answer
+        ahead_full = mbar_test_wait(bar(kBarEmpty + st_nxt.slot), st_nxt.phase ^ 1);
         unsigned char* bt = tiles + (size_t)s * kStageBytes + kABytes;
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
@@ -440,6 +455,7 @@ gemm_w4a16_fused_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           mbar_arrive(bar(kBarRawEmpty + r));            // the packed bytes were consumed by the conversion above
         }
       }
+      it_base += (uint32_t)t.kbn;
     }
   }
   tc_fence_before();
