@@ -119,7 +119,7 @@ def w4a16_linear(
         variant = select_variant(m, n, k, padded_k, int(group_size), activation, residual is not None)
         if variant == "tcgen05" and not two_pass and not _integer_zero_points(zero_points):
             variant = "simt"
-        # the fused single-pass form where it measures faster (few channel tiles, M <= 128); integer zero points only
+        # the fused single-pass form where it measures faster (17 <= M <= 512); integer zero points only
         if variant == "tcgen05" and odt != torch.float32 and lib.xqt_b200_w4a16_fused_preferred(m, n, k, padded_k, int(group_size)) \
                 and _integer_zero_points(zero_points):
             variant = "tcgen05_fused"
