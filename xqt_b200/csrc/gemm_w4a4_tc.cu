@@ -177,7 +177,7 @@ __device__ __noinline__ void w44_drain(const W4A4Params& p, uint32_t tmem_base, 
       const uint32_t npair = pair + 1;
       // A barrier test answers after about 200 cycles even when the phase is complete: ask for the next
       // hand-over now and read the answer after this stage's arithmetic.
-      const bool next_full = mbar_try_wait(bar(kBarPairFull + npair % kPairBufs), (npair / kPairBufs) & 1);
+      const bool next_full = mbar_test_wait(bar(kBarPairFull + npair % kPairBufs), (npair / kPairBufs) & 1);   // non-blocking
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const uint32_t swg = sw + slot * kScaleSlotBytes + h * (kBN * 4);

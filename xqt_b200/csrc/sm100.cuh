@@ -323,8 +323,8 @@ __device__ __forceinline__ unsigned long long f32x2_add(unsigned long long a, un
   return d;
 }
 // One K block of four SS MMA steps (descriptors a0..a3 / b0..b3), its commit to `done_bar`, and --
-// issued first, consumed last -- one poll of `next_bar`: the 150-cycle round trip of the poll runs
-// while the MMAs are being issued.  Returns whether `next_bar` had completed `next_parity`.
+// issued first, consumed last -- one poll of `next_bar` (a non-blocking test_wait: try_wait would suspend the issuer
+// when the next stage has not landed yet): the 150-cycle round trip of the poll runs while the MMAs are being issued.  Returns whether `next_bar` had completed `next_parity`.
 // `first_accumulate` is the accumulate flag of the first step; the other three always accumulate.
 template <bool I8>
 __device__ __forceinline__ bool umma_ss_x4_commit_poll(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t idesc,
@@ -334,7 +334,7 @@ __device__ __forceinline__ bool umma_ss_x4_commit_poll(uint32_t d_tmem, uint64_t
   if (I8) {
     asm volatile(
         "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a, b;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 q, [%6], %7;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%6], %7;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "setp.eq.b32 t, 0, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%1], %2, %3, %8, p;\n\t"
@@ -352,7 +352,7 @@ __device__ __forceinline__ bool umma_ss_x4_commit_poll(uint32_t d_tmem, uint64_t
   } else {
     asm volatile(
         "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a, b;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 q, [%6], %7;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%6], %7;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "setp.eq.b32 t, 0, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %8, p;\n\t"
