@@ -259,3 +259,80 @@ def test_fused_swiglu_decode_epilogue_has_the_bits_of_the_unfused_form(m, monkey
     assert torch.equal(fused(x), plain(x))
     assert torch.equal(fused.gate_up.gated(x), plain._swiglu(plain.gate_up(x)))
     assert native.workspace_status(dev) == 0
+
+
+def test_counted_peer_kernels_on_one_gpu():
+    """The graph-safe (counted) reduction and gather with one GPU playing rank 0 of two: "rank 1" is a local buffer whose
+    flag already carries a large call number, so no wait runs.  Three calls, eagerly and from one captured graph: the
+    kernels take the call number from device memory, alternate between the two slots of every buffer and publish the
+    count; the decode kernel writes its partial through the same word."""
+
+    import ctypes
+
+    from xqt_b200 import native, quantize
+    from xqt_b200.ops.w4a16 import bind_w4a16_decode, prepare_decode
+
+    lib = native.library()
+    dev = torch.device("cuda", 0)
+    stream = native.stream_handle(dev)
+    array = ctypes.c_void_p * 2
+    rows, n, k = 4, 256, 512
+    count, stride = rows * n, 2048                      # elements per partial, elements between the two slots
+    mine = torch.zeros(2 * stride, device=dev)          # rank 0: written by the decode kernel
+    peer = torch.zeros(2 * stride, device=dev)
+    peer[:count] = 10.0                                 # slot 0
+    peer[stride:stride + count] = 20.0                  # slot 1
+    flags = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(2)]
+    flags[0][1] = 1 << 20                               # "rank 1" has signalled every call we are going to make
+    counter = torch.zeros(4, dtype=torch.int32, device=dev)
+    status = torch.zeros(16, dtype=torch.int32).pin_memory()
+    out = torch.zeros(count, dtype=torch.bfloat16, device=dev)
+    layer = quantize.quantize_w4_asymmetric(torch.randn((n, k), generator=seeded(3)) * 0.02, group_size=128)
+    tiled = prepare_decode(layer.qweight.to(dev), layer.scales.to(dev), layer.zero_points.to(dev), group_size=128, nibble_signed=False)
+    run = bind_w4a16_decode(tiled, rows=rows, dtype=torch.bfloat16, out_dtype=torch.float32,
+                            out_select=(counter.data_ptr(), stride * 4))
+    plain = bind_w4a16_decode(tiled, rows=rows, dtype=torch.bfloat16, out_dtype=torch.float32)
+    x = torch.randn((rows, k), generator=seeded(4)).to(torch.bfloat16).to(dev)
+    partials, flag_ptrs = array(mine.data_ptr(), peer.data_ptr()), array(*(t.data_ptr() for t in flags))
+
+    def step():
+        run(x, mine[:count].view(rows, n))
+        assert lib.xqt_b200_peer_allreduce_counted(partials, flag_ptrs, 0, 2, counter.data_ptr(), stride, count, n, None,
+                                                   out.data_ptr(), native.BF16, 1000, status.data_ptr(), native.stream_handle(dev)) == 0
+
+    want = plain(x).reshape(-1)
+    for call in (1, 2, 3):                              # slots 1, 0, 1
+        step()
+        torch.cuda.synchronize()
+        assert int(counter[0].item()) == call and int(counter[1].item()) == 0 and int(status[0]) == 0
+        assert int(flags[1][0].item()) == call          # rank 0 signalled its peer with the device-side call number
+        addend = 20.0 if call & 1 else 10.0
+        assert torch.equal(out.float(), (want + addend).to(torch.bfloat16).float())
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    for call in (4, 5):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert int(counter[0].item()) == call and int(status[0]) == 0
+        assert torch.equal(out.float(), (want + (20.0 if call & 1 else 10.0)).to(torch.bfloat16).float())
+    # the gather: rank 0's bytes are whatever the decode kernel wrote into the slot in use, rank 1's the constants
+    gathered = torch.zeros((2, count), device=dev)
+    gcounter = torch.zeros(4, dtype=torch.int32, device=dev)
+    gflags = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(2)]
+    gflags[0][1] = 1 << 20
+    gflag_ptrs = array(*(t.data_ptr() for t in gflags))
+    mine.zero_()
+    mine[:count] = 1.0
+    mine[stride:stride + count] = 2.0
+    for call in (1, 2):
+        assert lib.xqt_b200_peer_allgather_counted(partials, gflag_ptrs, 0, 2, gcounter.data_ptr(), stride * 4, count * 4,
+                                                   gathered.data_ptr(), 1000, status.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        assert int(gcounter[0].item()) == call and int(status[0]) == 0
+        assert torch.equal(gathered[0], torch.full((count,), 2.0 if call & 1 else 1.0, device=dev))
+        assert torch.equal(gathered[1], torch.full((count,), 20.0 if call & 1 else 10.0, device=dev))
