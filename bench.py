@@ -631,7 +631,7 @@ def measure_other_configs(device, world, rank, barrier) -> list:
     blocks = [W4A16SwiGLUMLP(*(to_dev(pw) for pw in cpu_w), device=device, rank=rank, world=world) for _ in range(copies)]
     weights = 3 * weight_aux_bytes(hidden, inter)
     reduction = "none" if world == 1 else None
-    for m in (1, 16, 512, 4096):
+    for m in (1, 16, 64, 512, 4096):       # 64 is not a named configuration: the mid-M point of the fused GEMM
         x_host = torch.randn((m, hidden), generator=torch.Generator().manual_seed(30 + m)).to(torch.bfloat16).pin_memory()
         x = x_host.to(device)
         activations = 2 * m * (2 * hidden + 6 * inter)      # x, gate|up out + in, gated out + in, y
@@ -647,7 +647,7 @@ def measure_other_configs(device, world, rank, barrier) -> list:
             return blocks[state["i"] % copies](xx)
 
         cpu = None
-        if with_cpu:
+        if with_cpu and m != 64:
             from oracle import mlp as oracle_mlp  # the timed CPU baseline
 
             xc = x_host.clone()
@@ -699,8 +699,10 @@ def measure_other_configs(device, world, rank, barrier) -> list:
             e2e = _e2e_us(x_host, blocks[0], barrier, 5, device) if world == 1 else None
             records.append(_record(
                 f"cfg5_mlp_M{m}", cfg, metric="w4a16_mlp_throughput", unit="TFLOP/s", work=work, us=us, bound="tensor",
-                peak=bf16_peak, peak_source=bf16_kind, kernel="gemm_f16_kernel (after dequant_w4_f16_kernel)",
-                algorithmic="per rank: 2*M*3*inter*hidden / world", clocks=clocks, e2e=e2e, cpu=cpu))
+                peak=bf16_peak, peak_source=bf16_kind,
+                kernel="gemm_w4a16_fused_kernel" if m <= 512 else "gemm_f16_kernel (after dequant_w4_f16_kernel)",
+                algorithmic="per rank: 2*M*3*inter*hidden / world", clocks=clocks, e2e=e2e, cpu=cpu,
+                extra={"hbm_floor_us": round((weights / world + 2 * m * (2 * hidden + 6 * inter)) / hbm_peak / 1e3, 2)}))
             _log(f"mlp m={m}: {us:.1f} us")
     del blocks
     torch.cuda.empty_cache()
