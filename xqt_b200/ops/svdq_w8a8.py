@@ -174,14 +174,47 @@ def bind_svdq_w8a8_linear(packed: PackedSVDQW8A8Linear, workspace: W8A8SVDQWorks
         workspace = allocate_svdq_w8a8_workspace(rows, packed)
     if workspace.padded_rows < rows:
         raise ValueError("workspace row extent does not match rows")
-    k, dtype, device, scale = packed.input_features, packed.dtype, packed.qweight.device, float(lora_scale)
+    k, n, dtype, device, scale = packed.input_features, packed.output_features, packed.dtype, packed.qweight.device, float(lora_scale)
+    # every pointer and code of the library calls is resolved here; a call checks its input, allocates its output and
+    # makes the calls (the general entry's per-call validation costs more host time than the kernels run)
+    lib, dcode = native.library(), native.DTYPE_CODE[dtype]
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    codes, scales = workspace.quantized_activation[:rows], workspace.activation_scales[:rows]
+    la, la16, low = workspace.lora_activation[:rows], workspace.lora_activation16[:rows], workspace.low_rank_output[:rows]
+    la16_head = la16[:, :RANK_PAD]
+    scratch = native.workspace(device, 256, "gemm")
+    quant_tail = (0, codes.data_ptr(), scales.data_ptr(), 0, rows, k, 0, 0, 9, 0, dcode)
+    down_args = (packed.down.data_ptr(), la.data_ptr(), 0, rows, k, dcode)
+    up_args = (la16.data_ptr(), packed.up.data_ptr(), low.data_ptr(), rows, n, UP_PAD, dcode, scratch.data_ptr(), scratch.numel())
+    gemm_head = (codes.data_ptr(), packed.qweight.data_ptr(), scales.data_ptr(), packed.weight_scales.data_ptr(), native.ptr(packed.bias),
+                 low.data_ptr() if packed.rank else 0)
+    gemm_tail = (rows, n, k, dcode, scratch.data_ptr(), scratch.numel())
+    has_rank = bool(packed.rank)
 
     def run(inputs: torch.Tensor) -> torch.Tensor:
-        if inputs.dtype != dtype or inputs.device != device or inputs.ndim != 2 or tuple(inputs.shape) != (rows, k):
-            raise XQTBackendError("bound SVDQ W8A8 call: input shape, dtype or device mismatch")
-        return _forward(inputs, packed, workspace, scale, True)
+        if inputs.dtype != dtype or inputs.device != device or inputs.ndim != 2 or tuple(inputs.shape) != (rows, k) \
+                or not inputs.is_contiguous():
+            raise XQTBackendError("bound SVDQ W8A8 call: input shape, dtype, device or layout mismatch")
+        if torch.cuda.current_device() != index:
+            raise XQTBackendError("bound SVDQ W8A8 call: make the weight's device current before calling")
+        out = torch.empty((rows, n), device=device, dtype=dtype)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        x_ptr = inputs.data_ptr()
+        code = lib.xqt_b200_rotate_quantize(x_ptr, *quant_tail, stream)
+        if code == 0 and has_rank:
+            code = lib.xqt_b200_lowrank_down(x_ptr, *down_args, stream)
+            if code == 0:
+                if scale != 1.0:
+                    la.mul_(scale)
+                la16_head.copy_(la)                          # the rounding to the activation dtype
+                code = lib.xqt_b200_lowrank_up(*up_args, stream)
+        if code == 0:
+            code = lib.xqt_b200_w8a8_gemm_addend(*gemm_head, out.data_ptr(), *gemm_tail, stream)
+        if code != 0:
+            native.check(code, "bound SVDQ W8A8 (quantise / low-rank / GEMM)")
+        return out
 
-    run.keep = (packed, workspace)
+    run.keep = (packed, workspace, scratch)
     return run
 
 
