@@ -368,6 +368,19 @@ def test_gemm_single_pass_variant_shapes(m, n, k):
     assert oracle.rel_l2(out, ref) <= TOL
 
 
+@pytest.mark.parametrize("m,n,k", [(64, 512, 1792), (200, 4096, 3584), (300, 392, 1280)])
+def test_fused_gemm_writes_fp32_partial_sums(m, n, k):
+    """Unrounded fp32 output (the partial sums of a K-sharded layer) from the fused kernel, with and without a K split."""
+
+    dev = torch.device("cuda", 0)
+    x, pw = _synthetic(n, k, m, seed=950 + m)
+    out = w4a16_linear(x.to(dev), pw.qweight.to(dev), pw.scales.to(dev), pw.zero_points.to(dev), group_size=128,
+                       nibble_signed=False, out_dtype=torch.float32, variant="tcgen05_fused")
+    assert out.dtype == torch.float32
+    ref = oracle.gemm(x, pw.qweight, pw.scales, pw.zero_points, group_size=128, signed=False, out_dtype=torch.float32)
+    assert oracle.rel_l2(out.cpu(), ref) <= TOL
+
+
 @pytest.mark.parametrize("group,symmetric", [(64, False), (128, True), (128, False)])
 def test_gemm_two_pass_groups_signed_epilogue(group, symmetric):
     """M >= 256: weights dequantised once into an fp16 scratch, then the dense tcgen05 GEMM."""

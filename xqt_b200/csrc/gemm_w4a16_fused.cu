@@ -483,8 +483,11 @@ bool w4a16_gemm_fused_supported(int m, int n, int k, int padded_k, int group_siz
 // (224 tiles): 71 / 72 / 74 / 89 / 159 us against 110 / 110 / 111 / 129 / 172 us.  So up to 512 tokens (two 256-token
 // chunks, the weights converted once per chunk); beyond that the two-pass form, whose conversion cost does not grow
 // with M, is ahead.
+// Small layers (the shards of a tensor-parallel block) change the balance for two chunks: at M = 512 a 3584 x 4096 layer
+// takes 61 us fused against 45 us two-pass, a 7168 x 4096 layer 47 against 53; below 24 M weights two chunks stay two-pass.
 bool w4a16_gemm_fused_preferred(int m, int n, int k, int padded_k, int group_size) {
-  return w4a16_gemm_fused_supported(m, n, k, padded_k, group_size) && m > 16 && m <= 4 * w4f::kBM;
+  if (!w4a16_gemm_fused_supported(m, n, k, padded_k, group_size) || m <= 16 || m > 4 * w4f::kBM) return false;
+  return m <= 2 * w4f::kBM || (long long)n * k >= 24ll * 1024 * 1024;
 }
 
 struct W4FusedPlan {

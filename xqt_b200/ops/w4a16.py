@@ -114,7 +114,10 @@ def w4a16_linear(
     if odt == torch.float32:
         if not two_pass and not _integer_zero_points(zero_points):
             raise XQTBackendError("fp32 partial sums need the tensor-core GEMM, i.e. integer zero points")
-        variant = "tcgen05"
+        # unrounded partial sums of a K-sharded layer: the fused form where it is preferred (it writes fp32 as well), else two-pass
+        fused_ok = variant in ("auto", "tcgen05_fused") and activation == "none" and residual is None \
+            and _integer_zero_points(zero_points) and lib.xqt_b200_w4a16_fused_preferred(m, n, k, padded_k, int(group_size))
+        variant = "tcgen05_fused" if fused_ok else "tcgen05"
     if variant == "auto":
         variant = select_variant(m, n, k, padded_k, int(group_size), activation, residual is not None)
         if variant == "tcgen05" and not two_pass and not _integer_zero_points(zero_points):
